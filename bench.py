@@ -1,0 +1,420 @@
+#!/usr/bin/env python
+"""Benchmark of the Select-then-Prune decode step (Quest selector -> INT4 estimator -> top-p
+pruner -> sparse paged attention) on synthetic inputs of the Longchat-7B-class configuration:
+B=16 sequences of 32768 tokens, 32 query heads = 32 KV heads, head_dim 128, page size 16,
+Quest budget 8192, top-p 0.95, bf16, 32 attention layers per decoded token.
+
+One "step" decodes one token for the whole batch: 32 layer passes of the hot path.  Only
+``--resident-layers`` distinct layers' caches are held in HBM (one layer is 8 GiB of K/V plus
+1.25 GiB of INT4 K and 0.5 GiB of page metadata); the 32 passes cycle through them, so every
+pass streams data that is far larger than L2 and was last touched several passes ago.
+
+Prints ONE JSON line (rank 0).  ``python bench.py --impl reference`` times the CPU restatement
+of the reference's PyTorch path on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "sparse decode attn tokens/s/GPU @32k ctx; % HBM roofline; avg pruned budget"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--ctx", type=int, default=32768)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=32)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--resident-layers", type=int, default=4)
+    ap.add_argument("--token-budget", type=int, default=8192)
+    ap.add_argument("--top-p", type=float, default=0.95)
+    ap.add_argument("--rho", type=float, default=0.005)
+    ap.add_argument("--recipe", default="literal", choices=["literal", "mid", "calibrated"])
+    ap.add_argument("--variant", type=int, default=0)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--kernel-reps", type=int, default=5)
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx.append(float(parts[1]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, parts[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's PyTorch path
+# ---------------------------------------------------------------------------------------------
+def cpu_reference_inputs(args, heads: int, seqs: int):
+    """Seeded inputs of ``seqs`` sequences for the CPU arm (bf16, sink planted as in the recipe)."""
+    L, D = args.ctx, 128
+    data = []
+    for i in range(seqs):
+        g = torch.Generator().manual_seed(i)
+        q = torch.randn(1, heads, 1, D, generator=g).to(torch.bfloat16)
+        k = torch.randn(1, heads, L, D, generator=g).to(torch.bfloat16)
+        v = torch.randn(1, heads, L, D, generator=g).to(torch.bfloat16)
+        qh = q[:, :, 0].float()
+        qh = qh / qh.norm(dim=-1, keepdim=True) * math.sqrt(D)
+        k[:, :, 0] = (8.0 * qh).to(torch.bfloat16)
+        data.append((q, k, v))
+    return data
+
+
+def cpu_reference_step(args, data):
+    """One layer pass of twilight/pyimpl/attention.py:188-306 over the given sequences on the
+    host cores, dtype-faithful (bf16), one sequence at a time.  Returns seconds."""
+    from oracle import twilight_oracle as O
+    t0 = time.perf_counter()
+    for q, k, v in data:
+        O.decode_step(q, k, v, selector="quest", token_budget=args.token_budget, chunk_size=16,
+                      quant_group=32, threshold=args.top_p)
+    return time.perf_counter() - t0
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    seqs = min(4, args.batch)
+    threads = torch.get_num_threads()
+    data = cpu_reference_inputs(args, args.heads, seqs)
+    for _ in range(args.warmup):
+        cpu_reference_step(args, data)
+    times = [cpu_reference_step(args, data) for _ in range(max(1, args.steps))]
+    t = statistics.mean(times)
+    # `seqs` sequences of one layer measured per step; a decoded token needs `layers` passes
+    value = seqs / (t * args.layers)
+    sample = (f"each step = 1 of {args.layers} layer passes over {seqs} of {args.batch} sequences x {args.heads} "
+              f"heads at ctx {args.ctx}; tokens/s = sequences / (step time x layers)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": len(times), "warmup": args.warmup, "ms_per_step": t * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args, 1),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(args, n):
+    return {"workload": f"Longchat-7B-class decode attention, B={args.batch}/GPU, ctx {args.ctx}, "
+                        f"{args.heads}q/{args.kv_heads}kv heads, d128, page 16, Quest {args.token_budget} + top-p {args.top_p}, "
+                        f"{args.layers} layers/token",
+            "global_batch": args.batch * n, "seq_len": args.ctx, "parallelism": f"(batch,kv-head) shards x{n}",
+            "recipe": args.recipe, "resident_layers": args.resident_layers,
+            "l2": "inputs larger than L2: each layer pass streams >0.8 GB and layers alternate"}
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    from twilight_b200 import _lib
+    from twilight_b200.gen import make_decode_inputs
+    from twilight_b200.kernel import ops
+    from twilight_b200.step import (DecodeWorkspace, SparseConfig, select_prune_attend_step,
+                                    step_algorithmic_bytes)
+    _lib.load()  # fail loudly if the CUDA library is missing
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: there is no CPU path")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg = SparseConfig(selector="quest", token_budget=args.token_budget, weight_pruner="top_p",
+                       threshold=args.top_p)
+    R = max(1, min(args.resident_layers, args.layers))
+    layers = []
+    for l in range(R):
+        q, cache = make_decode_inputs(args.batch, args.heads, args.kv_heads, args.ctx, rho=args.rho,
+                                      dtype=torch.bfloat16, device=dev, seed=1000 * rank + l,
+                                      recipe=args.recipe, shuffle_pages=True)
+        layers.append((q, cache))
+    ws = DecodeWorkspace.for_cache(layers[0][1], args.heads, cfg)
+    gathered = None
+    if world > 1:
+        gathered = torch.empty(world, args.batch, args.heads, 128, dtype=torch.bfloat16, device=dev)
+
+    def layer_pass(i):
+        q, cache = layers[i % R]
+        out = select_prune_attend_step(q, cache, ws, variant=args.variant)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+
+    def token_step():
+        for i in range(args.layers):
+            layer_pass(i)
+
+    # one eager step (also sets function attributes before any capture)
+    token_step()
+    torch.cuda.synchronize()
+    if int(ws.status.item()) != 0:
+        raise RuntimeError(f"device status flags raised: {int(ws.status.item())}")
+    budgets = []
+    for i in range(R):
+        layer_pass(i)
+        budgets.append(ws.budget.clone())
+    avg_budget = float(torch.stack(budgets).float().mean().item())
+
+    graph = None
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                token_step()
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                token_step()
+        except Exception as e:  # fall back to eager launches
+            sys.stderr.write(f"[bench] CUDA graph capture failed ({e}); timing eager launches\n")
+            graph = None
+    run_step = graph.replay if graph is not None else token_step
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        run_step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run_step()
+    e1.record()
+    torch.cuda.synchronize()
+    elapsed_ms = e0.elapsed_time(e1)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    value = args.batch * world / (ms_per_step * 1e-3)
+
+    # ---- per-kernel timings (CUDA events on the launching stream) and the roofline ----------
+    q0, c0 = layers[0]
+    names = ["quest_page_scores", "quest_topk_pages", "estimate_int4", "topp_prune", "sparse_decode_attn"]
+    lib = _lib.load()
+    s = torch.cuda.current_stream().cuda_stream
+
+    def launch(kname, q, cache):
+        b, hq, hkv = args.batch, args.heads, args.kv_heads
+        if kname == "quest_page_scores":
+            return lib.twl_quest_page_scores(q.data_ptr(), 1, cache.kmeta.data_ptr(), cache.kv_indptr.data_ptr(),
+                                             cache.kv_indices.data_ptr(), b, hq, hkv, cache.kmeta.shape[0],
+                                             ws.page_scores.data_ptr(), ws.max_pages, ws.status.data_ptr(), s)
+        if kname == "quest_topk_pages":
+            return lib.twl_quest_topk_pages(ws.page_scores.data_ptr(), ws.max_pages, cache.kv_indptr.data_ptr(), b, hq,
+                                            cfg.token_budget, ws.cand_pages.data_ptr(), ws.cand_npages.data_ptr(),
+                                            ws.cand_pages.shape[-1], s)
+        if kname == "estimate_int4":
+            return lib.twl_estimate_int4(q.data_ptr(), 1, cache.k4_pages.data_ptr(), cache.kv_indptr.data_ptr(),
+                                         cache.kv_indices.data_ptr(), cache.kv_last_page_len.data_ptr(),
+                                         ws.cand_pages.data_ptr(), ws.cand_npages.data_ptr(), ws.cand_pages.shape[-1],
+                                         b, hq, hkv, cache.k4_pages.shape[0], 1 / math.sqrt(128),
+                                         ws.scores.data_ptr(), ws.scores.shape[-1], args.variant,
+                                         ws.status.data_ptr(), s)
+        if kname == "topp_prune":
+            return lib.twl_topp_prune(ws.scores.data_ptr(), ws.scores.shape[-1], cache.kv_indptr.data_ptr(),
+                                      cache.kv_last_page_len.data_ptr(), ws.cand_pages.data_ptr(),
+                                      ws.cand_npages.data_ptr(), ws.cand_pages.shape[-1], b, hq, None, cfg.threshold,
+                                      ws.indices.data_ptr(), ws.indices.shape[-1], ws.budget.data_ptr(),
+                                      ws.threshold.data_ptr(), ws.status.data_ptr(), s)
+        return lib.twl_sparse_decode_attn(q.data_ptr(), 1, cache.k_pages.data_ptr(), cache.v_pages.data_ptr(),
+                                          cache.kv_indptr.data_ptr(), cache.kv_indices.data_ptr(),
+                                          ws.indices.data_ptr(), ws.indices.shape[-1], ws.budget.data_ptr(), b, hq, hkv,
+                                          cache.k_pages.shape[0], 1 / math.sqrt(128), ws.out.data_ptr(),
+                                          ws.attn_ws.data_ptr(), ws.attn_ws.numel(), ws.attn_chunk,
+                                          ws.status.data_ptr(), s)
+
+    ktimes = {n: [] for n in names}
+    for rep in range(args.kernel_reps):
+        for i in range(R):
+            q, cache = layers[i]
+            for n in names:
+                a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                st = launch(n, q, cache)
+                b_.record()
+                if st != 0:
+                    raise RuntimeError(f"{n} returned {st}")
+                ktimes[n].append((a, b_))
+    torch.cuda.synchronize()
+    kavg = {n: statistics.mean(x.elapsed_time(y) for x, y in v[R:]) if len(v) > R else
+            statistics.mean(x.elapsed_time(y) for x, y in v) for n, v in ktimes.items()}
+    bytes_ = step_algorithmic_bytes(c0, args.heads, cfg, torch.stack(budgets).float().mean(0))
+    kbytes = {"quest_page_scores": bytes_["selector"] + c0.max_pages * 4 * args.batch * args.kv_heads,
+              "estimate_int4": bytes_["estimator"],
+              "sparse_decode_attn": bytes_["attention"]}
+    dominant = max(kavg, key=kavg.get)
+    peaks = {}
+    try:
+        peaks = json.load(open(ROOT / "MEASURED_PEAKS.json"))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
+    dom_bytes = kbytes.get(dominant, 0.0)
+    achieved = dom_bytes / (kavg[dominant] * 1e-3) / 1e9 if dom_bytes else 0.0
+    step_gbs = bytes_["total"] * args.layers / (ms_per_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
+                "algorithmic_bytes_per_launch": dom_bytes,
+                "kernels_ms": {k: round(v, 5) for k, v in kavg.items()},
+                "kernels_gbs": {k: round(kbytes[k] / (kavg[k] * 1e-3) / 1e9, 1) for k in kbytes},
+                "step": {"algorithmic_bytes_per_layer_pass": bytes_["total"], "achieved": step_gbs,
+                         "frac": step_gbs / peak, "frac_of_8000_nominal": step_gbs / 8000.0}}
+
+    # ---- end to end: q from pinned host memory in, output to pinned host memory out ------------
+    e2e = None
+    if not args.no_e2e:
+        host_q = [layers[i][0].cpu().pin_memory() for i in range(R)]
+        host_out = torch.empty(args.batch, args.heads, 128, dtype=torch.bfloat16).pin_memory()
+        dq = torch.empty_like(layers[0][0])
+
+        def e2e_step():
+            for i in range(args.layers):
+                dq.copy_(host_q[i % R], non_blocking=True)
+                out = select_prune_attend_step(dq, layers[i % R][1], ws, variant=args.variant)
+                if world > 1:
+                    dist.all_gather_into_tensor(gathered, out)
+                host_out.copy_(out, non_blocking=True)
+            torch.cuda.synchronize()
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        t1 = time.perf_counter()
+        barrier()
+        dt = t1 - t0
+        if world > 1:
+            t = torch.tensor([dt], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        nbytes = args.batch * args.heads * 128 * 2 * args.layers
+        e2e = {"value": args.batch * world * args.steps / dt, "unit": "tokens/s",
+               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        seqs = min(8, args.batch)
+        data = cpu_reference_inputs(args, args.heads, seqs)
+        cpu_reference_step(args, data[:1])
+        t = cpu_reference_step(args, data)
+        cpu_baseline = {"value": seqs / (t * args.layers), "unit": "tokens/s", "cores": torch.get_num_threads(),
+                        "kind": "port",
+                        "sample": f"1 of {args.layers} layer passes over {seqs} of {args.batch} sequences x "
+                                  f"{args.heads} heads at ctx {args.ctx} ({t:.1f} s of CPU work); tokens/s = "
+                                  f"sequences / (time x layers)"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
+            "tokens_per_s_per_gpu": value / world, "tokens_per_s_per_layer_pass": value * args.layers,
+            "avg_pruned_budget": avg_budget, "cuda_graph": graph is not None,
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": ws.kernels_per_step * args.layers * args.steps,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,183 @@
+/*
+ * twilight_b200 -- C ABI of the Select-then-Prune decode path for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle, launches
+ * on that stream and returns; no entry point allocates, frees, synchronises or keeps state
+ * (apart from one-time cudaFuncSetAttribute calls).  All buffers, workspaces included, are
+ * owned by the caller.  Return value: TWL_OK (0) or a negative twl_status; nothing throws.
+ *
+ * The reference project (tsinghua-ideal/Twilight) binds its native code through pybind11
+ * (csrc/src/sampling.cu:65-70).  Each declaration below names the reference interface it
+ * stands in for.
+ *
+ * Shared conventions
+ *   dtype        TWL_F16 or TWL_BF16: element type of q, K/V pages, page metadata and out.
+ *   paged KV     FlashInfer-style CSR page table, the one the reference's GEMV call sites use
+ *                (benchmark/efficiency/bench_gemv.py:437-454): kv_indptr[B+1],
+ *                kv_indices[kv_indptr[B]] physical page ids, kv_last_page_len[B] in 1..16.
+ *                Sequence b has n_b = kv_indptr[b+1]-kv_indptr[b] pages and
+ *                (n_b-1)*16 + kv_last_page_len[b] tokens.  Page size is fixed at 16.
+ *   K/V pages    [num_pages][H_kv][16][128] elements: one (page, kv-head) slab = 4 KiB.
+ *   INT4 K page  [num_pages][H_kv][1280] bytes: bytes 0..1023 = 16 tokens x 64 code bytes
+ *                (byte j of a token holds channel 2j in its low nibble and 2j+1 in its high
+ *                nibble); bytes 1024..1279 = 16 tokens x 4 groups x {fp16 scale, fp16 min}.
+ *                Dequantised value = code*scale + min.  Group = 32 channels, head_dim = 128.
+ *   page meta    [num_pages][H_kv][2][128] elements: channel-wise {min, max} of the page.
+ *   candidates   cand_pages[B][H_q][max_k] logical page numbers (index into the sequence's
+ *                page list), ascending; cand_npages[B][H_q].  Candidate slot s of a row is
+ *                token cand_pages[s/16]*16 + s%16.
+ *   status       optional int32 device word; kernels OR bits of twl_device_flag into it.
+ */
+#ifndef TWILIGHT_B200_H_
+#define TWILIGHT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define TWL_API __attribute__((visibility("default")))
+#else
+#define TWL_API
+#endif
+
+typedef enum {
+  TWL_OK = 0,
+  TWL_ERR_BAD_ARG = -1,      /* null pointer, zero/negative size, inconsistent sizes   */
+  TWL_ERR_MISALIGNED = -2,   /* a pointer or stride breaks the documented alignment     */
+  TWL_ERR_UNSUPPORTED = -3,  /* head_dim != 128, page size != 16, unknown dtype, ...    */
+  TWL_ERR_LAUNCH = -4,       /* the CUDA runtime rejected a launch (see twl_last_cuda_error) */
+  TWL_ERR_TOO_LARGE = -5,    /* a size exceeds what the kernel or a workspace can hold  */
+  TWL_ERR_WORKSPACE = -6     /* workspace pointer null or too small                     */
+} twl_status;
+
+typedef enum { TWL_F16 = 0, TWL_BF16 = 1 } twl_dtype;
+
+typedef enum {
+  TWL_FLAG_ITER_CAP = 1,     /* the top-p search hit its round limit                    */
+  TWL_FLAG_BAD_INDEX = 2,    /* an index/page id was out of range and was skipped       */
+  TWL_FLAG_WAIT_LIMIT = 4    /* a bounded wait on a copy barrier ran out                */
+} twl_device_flag;
+
+#define TWL_PAGE_SIZE 16
+#define TWL_HEAD_DIM 128
+#define TWL_QUANT_GROUP 32
+#define TWL_K4_SLAB_BYTES 1280
+
+TWL_API int twl_version(void);
+TWL_API const char* twl_status_string(int status);
+/* cudaGetErrorString of the last launch error seen by this library on this thread. */
+TWL_API const char* twl_last_cuda_error(void);
+
+/* ---- kernel #2, reference-compatible form ------------------------------------------
+ * Replaces top_p_fp32_return_mask / top_p_fp16_return_mask of csrc/src/sampling.cu:45-63
+ * and :22-43 (launcher csrc/include/sampling.cuh:233-250, kernel :119-231).
+ * probs: [rows][d] contiguous probabilities (rows = batch*num_heads); mask: [rows][d]
+ * bytes, written 0/1; top_p_arr: [rows] fp32 or NULL (then top_p_val is used).
+ * Same search as the reference: low=0, high=probs[row][0], eps=1e-5, mask = probs > low.
+ * The f16 form takes fp16 or bf16 probabilities; low/high/mid/p are rounded to that type
+ * as in the reference, partial sums are kept in fp32. */
+TWL_API int twl_top_p_return_mask_f32(const float* probs, uint8_t* mask, const float* top_p_arr,
+                              float top_p_val, uint32_t rows, uint32_t d, int32_t* status,
+                              void* stream);
+TWL_API int twl_top_p_return_mask_f16(const void* probs, int dtype, uint8_t* mask,
+                              const float* top_p_arr, float top_p_val, uint32_t rows,
+                              uint32_t d, int32_t* status, void* stream);
+
+/* ---- selector: Quest page scores + top-k pages ---------------------------------------
+ * Replaces quest_selector of twilight/pyimpl/quest.py:17-122 using stored page metadata:
+ * score(page) = sum_d max(q_d*kmax_d, q_d*kmin_d) in fp32 (quest.py:37-84), then the
+ * max(1,budget/16)+(budget%16!=0) best pages per query head (quest.py:93-99), ties to the
+ * lower page number.  page_scores: caller scratch [B][H_q][max_pages] fp32 (kept as an
+ * output for inspection).  cand_pages rows are ascending. */
+TWL_API int twl_quest_page_scores(const void* q, int dtype, const void* kmeta,
+                          const int32_t* kv_indptr, const int32_t* kv_indices,
+                          int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                          int32_t num_pages_total, float* page_scores, int32_t max_pages,
+                          int32_t* status, void* stream);
+TWL_API int twl_quest_topk_pages(const float* page_scores, int32_t max_pages,
+                         const int32_t* kv_indptr, int32_t batch, int32_t num_q_heads,
+                         int32_t token_budget, int32_t* cand_pages, int32_t* cand_npages,
+                         int32_t max_k, void* stream);
+
+/* ---- kernel #1: INT4 K-cache q.k estimator --------------------------------------------
+ * Replaces the estimator of twilight/pyimpl/attention.py:247-255 (with quantize.py:4-13
+ * applied once at cache-append time) and the absent ftka op batched_sparse_gemv_int4_k
+ * (call site benchmark/efficiency/bench_gemv.py:445-454).
+ * scores[b][h][s] = sm_scale * sum_d q_d*(code_d*scale_g + min_g), fp32; slots of the last
+ * page past the end of the sequence are -inf; slots past the row's last candidate page are
+ * not written.  score_stride must be a multiple of 16.
+ * cand_pages == NULL: every page of the sequence is a candidate (slot == token position),
+ * K pages are read once per KV head for its whole query-head group.
+ * variant: 0 = library default; 1 = fp32 FMA; 2 = packed-half FMA; 3 = integer dot product. */
+TWL_API int twl_estimate_int4(const void* q, int dtype, const uint8_t* k4_pages,
+                      const int32_t* kv_indptr, const int32_t* kv_indices,
+                      const int32_t* kv_last_page_len, const int32_t* cand_pages,
+                      const int32_t* cand_npages, int32_t max_k, int32_t batch,
+                      int32_t num_q_heads, int32_t num_kv_heads, int32_t num_pages_total,
+                      float sm_scale, float* scores, int32_t score_stride, int32_t variant,
+                      int32_t* status, void* stream);
+
+/* ---- kernel #2: softmax + top-p threshold search + compaction -------------------------
+ * Replaces top_p_unnormalized (twilight/pyimpl/top_p.py:10-15) followed by the mask op and
+ * the AND/count of attention.py:280-285, emitting an index list instead of a dense mask.
+ * scores: [rows][score_stride] fp32 as written by twl_estimate_int4 (rows = B*H_q);
+ * out_indices[row][0..budget) = kept token positions, ascending; out_budget[row].
+ * out_threshold (nullable) [rows][2] = {low, p(token 0)}.  rows with no candidate get 0.
+ * A top_p above 1 skips the search and keeps every candidate whose probability is non-zero
+ * (the reference's pruner "none").  Only slots below 16*(candidate pages of the row) are read. */
+TWL_API int twl_topp_prune(const float* scores, int32_t score_stride, const int32_t* kv_indptr,
+                   const int32_t* kv_last_page_len, const int32_t* cand_pages,
+                   const int32_t* cand_npages, int32_t max_k, int32_t batch,
+                   int32_t num_q_heads, const float* top_p_arr, float top_p_val,
+                   int32_t* out_indices, int32_t index_stride, int32_t* out_budget,
+                   float* out_threshold, int32_t* status, void* stream);
+
+/* ---- kernel #3: sparse paged decode attention ------------------------------------------
+ * Replaces attention.py:188-190 restricted to the kept tokens and :298-306 (masked fp32
+ * softmax, P.V).  Split-KV: each block handles `chunk` indices of one row and the last
+ * block of a row to finish merges the partial (max, sum, acc) triples; no block waits.
+ * workspace: twl_sparse_attn_workspace_bytes(...) bytes, 16-byte aligned; its first
+ * batch*num_q_heads int32 words are arrival counters that must be zero on entry and are
+ * left zero on exit. */
+TWL_API size_t twl_sparse_attn_workspace_bytes(int32_t batch, int32_t num_q_heads,
+                                       int32_t index_stride, int32_t chunk);
+TWL_API int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pages, const void* v_pages,
+                           const int32_t* kv_indptr, const int32_t* kv_indices,
+                           const int32_t* indices, int32_t index_stride,
+                           const int32_t* budget, int32_t batch, int32_t num_q_heads,
+                           int32_t num_kv_heads, int32_t num_pages_total, float sm_scale,
+                           void* out, void* workspace, size_t workspace_bytes, int32_t chunk,
+                           int32_t* status, void* stream);
+
+/* ---- cache-append side ------------------------------------------------------------------
+ * twl_quantize_k_pages: min/max asymmetric 4-bit quantiser of quantize.py:4-13 applied per
+ * group of 32 channels, arithmetic in `dtype` like the reference, packing into INT4 slabs.
+ * n_slabs = num_pages*H_kv.  twl_build_page_meta: channel-wise min/max over the valid
+ * tokens of every page of every sequence (the chunk maxima of quest.py:39-74 in stored
+ * form).  twl_append_kv: writes one new token per sequence (its position is the last
+ * token the page table describes), quantises its K and folds it into the page metadata. */
+TWL_API int twl_quantize_k_pages(const void* k_pages, int dtype, uint8_t* k4_pages, int64_t n_slabs,
+                         void* stream);
+TWL_API int twl_build_page_meta(const void* k_pages, int dtype, void* kmeta, const int32_t* kv_indptr,
+                        const int32_t* kv_indices, const int32_t* kv_last_page_len,
+                        int32_t batch, int32_t num_kv_heads, int32_t num_pages_total,
+                        int32_t max_pages, void* stream);
+TWL_API int twl_append_kv(const void* new_k, const void* new_v, int dtype, void* k_pages,
+                  void* v_pages, uint8_t* k4_pages, void* kmeta, const int32_t* kv_indptr,
+                  const int32_t* kv_indices, const int32_t* kv_last_page_len, int32_t batch,
+                  int32_t num_kv_heads, int32_t num_pages_total, int32_t* status,
+                  void* stream);
+
+/* Index list -> dense byte mask [rows][d] (the mask interface of twilight/pyimpl: selectors
+ * and pruners return bool[B,H,1,L], attention.py:199-281).  mask must be zeroed by the caller. */
+TWL_API int twl_indices_to_mask(const int32_t* indices, int32_t index_stride, const int32_t* budget,
+                        int32_t rows, uint8_t* mask, int32_t d, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TWILIGHT_B200_H_ */

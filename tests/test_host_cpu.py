@@ -1,0 +1,126 @@
+"""CPU checks of the host side: the INT4 slab format, the page table, the config dictionary,
+the budget statistics, and that the C-ABI library loads and exports every declared symbol
+(no kernel is launched here)."""
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from twilight_b200 import _lib
+from twilight_b200.cache import PagedKVCache, pack_k4, unpack_k4, quest_max_k
+from twilight_b200.pyimpl.state import (HistoryBudgetInfo, IndexSelectorType, WeightEstimatorType,
+                                        WeightPrunerType)
+from twilight_b200.step import SparseConfig
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "twilight_b200.h").read_text()
+    declared = set(re.findall(r"TWL_API\s+[\w\s\*]+?\b(twl_\w+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    lib = ctypes.CDLL(str(_lib.lib_path()))
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert _lib.load().twl_version() >= 100
+    assert _lib.load().twl_status_string(-6) == b"workspace missing or too small"
+
+
+def test_bad_arguments_return_codes_without_a_gpu():
+    lib = _lib.load()
+    # null pointers / zero sizes are rejected before anything touches the device
+    assert lib.twl_top_p_return_mask_f32(None, None, None, 0.9, 1, 8, None, None) == -1
+    assert lib.twl_estimate_int4(None, 1, None, None, None, None, None, None, 0, 1, 1, 1, 1, 1.0,
+                                 None, 16, 0, None, None) == -1
+    assert lib.twl_sparse_attn_workspace_bytes(0, 1, 16, 256) == 0
+    assert lib.twl_sparse_attn_workspace_bytes(2, 4, 1024, 256) >= 8 * 4 * (128 + 2) * 4
+    with pytest.raises(_lib.TwilightError, match="bad argument"):
+        _lib.check(-1, "x")
+
+
+def test_k4_slab_nibble_order_and_roundtrip():
+    codes = torch.arange(16 * 128, dtype=torch.int64).reshape(16, 128) % 16
+    codes = ((codes + torch.arange(16)[:, None]) % 16).to(torch.uint8)
+    scale = (torch.arange(64, dtype=torch.float32).reshape(16, 4) * 0.01 + 0.1).to(torch.float16)
+    zmin = (-torch.arange(64, dtype=torch.float32).reshape(16, 4) * 0.5).to(torch.float16)
+    slab = pack_k4(codes, scale, zmin)
+    assert slab.shape == (1280,) and slab.dtype == torch.uint8
+    # byte j of token t: channel 2j low nibble, 2j+1 high nibble
+    t, j = 3, 17
+    assert int(slab[t * 64 + j]) == int(codes[t, 2 * j]) | (int(codes[t, 2 * j + 1]) << 4)
+    # {scale, min} of token t, group g at 1024 + t*16 + g*4
+    raw = slab[1024 + 5 * 16 + 2 * 4: 1024 + 5 * 16 + 2 * 4 + 4].contiguous().view(torch.float16)
+    assert raw[0] == scale[5, 2] and raw[1] == zmin[5, 2]
+    c2, s2, z2 = unpack_k4(slab)
+    assert torch.equal(c2, codes) and torch.equal(s2, scale) and torch.equal(z2, zmin)
+    # every code value in every nibble position survives
+    for v in range(16):
+        full = torch.full((2, 16, 128), v, dtype=torch.uint8)
+        c3, _, _ = unpack_k4(pack_k4(full, torch.ones(2, 16, 4), torch.zeros(2, 16, 4)))
+        assert torch.equal(c3, full)
+
+
+def test_page_table_ragged_and_shuffled():
+    indptr, indices, last, total = PagedKVCache.page_table([1, 16, 17, 100], "cpu")
+    assert indptr.tolist() == [0, 1, 2, 4, 11] and total == 11
+    assert last.tolist() == [1, 16, 1, 4]
+    assert indices.tolist() == list(range(11))
+    _, shuf, _, _ = PagedKVCache.page_table([1, 16, 17, 100], "cpu", shuffle_seed=7)
+    assert sorted(shuf.tolist()) == list(range(11)) and shuf.tolist() != list(range(11))
+
+
+def test_quest_max_k_matches_reference_rule():
+    assert quest_max_k(8192, 2048) == 512
+    assert quest_max_k(16384, 4096) == 1024
+    assert quest_max_k(40, 100) == 3
+    assert quest_max_k(8192, 100) == 100
+
+
+def test_config_dict_of_the_reference_parses():
+    cfg = {  # benchmark/configs/config_quest_twi.json
+        "compressor": {"type": "none"},
+        "selector": {"type": "quest", "token_budget": 8192, "chunk_size": 16},
+        "weight_estimator": {"type": "min_max_quant", "quant_bit": 4},
+        "weight_pruner": {"type": "top_p", "threshold": 0.85},
+        "skip_first_two_layers": True,
+        "use_estimated_weights_in_attn": False,
+    }
+    c = SparseConfig.from_dict(cfg)
+    assert (c.selector, c.token_budget, c.weight_pruner, c.threshold) == ("quest", 8192, "top_p", 0.85)
+    cfg["selector"] = {"type": "sparq", "token_budget": 10}
+    with pytest.raises(_lib.TwilightError):
+        SparseConfig.from_dict(cfg)
+    cfg["selector"] = {"type": "quest", "token_budget": 64, "chunk_size": 32}
+    with pytest.raises(_lib.TwilightError):
+        SparseConfig.from_dict(cfg)
+    assert IndexSelectorType.from_str("quest") is IndexSelectorType.QUEST
+    assert WeightEstimatorType.from_str("min_max_quant") is WeightEstimatorType.MIN_MAX_QUANT
+    assert WeightPrunerType.from_str("top_p") is WeightPrunerType.TOP_P
+    with pytest.raises(KeyError):
+        IndexSelectorType.from_str("nope")
+
+
+def test_history_budget_info_average_skips_first_two_layers():
+    info = HistoryBudgetInfo()
+    for query in range(2):
+        for layer in range(4):
+            mask = torch.zeros(1, 2, 1, 10, dtype=torch.bool)
+            mask[..., : layer + 1 + query] = True
+            info.update(layer, mask)
+    # layers 2,3 only (state.py:217): query 0 -> (3+4)/2, query 1 -> (4+5)/2
+    assert info.get_avg_budget_per_query() == [3.5, 4.5]
+    assert info.get_total_avg_budget() == 4.0
+    info2 = HistoryBudgetInfo()
+    for layer in range(3):
+        info2.update(layer, torch.tensor([[layer, layer + 2]], dtype=torch.int32))
+    assert info2.get_avg_budget_per_query() == [3.0]
+
+
+def test_operators_fail_loudly_without_cuda_tensors():
+    from twilight_b200.kernel import top_p_fp32_return_mask
+    with pytest.raises(_lib.TwilightError, match="CUDA tensor"):
+        top_p_fp32_return_mask(torch.rand(1, 1, 1, 8), 0.9)

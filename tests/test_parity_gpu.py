@@ -1,0 +1,502 @@
+"""GPU parity tests: every CUDA kernel, called through the C ABI, against the CPU oracle on the
+same seeded inputs.  Integer results (codes, page lists, index lists, budgets, masks) must be
+bit-exact, except kept-token sets, where tokens whose probability lies within 1e-4 of the
+threshold are exempt; attention outputs must agree within 2e-2 max-abs / 1e-3 mean-abs."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import twilight_oracle as O
+from tests import util as U
+from twilight_b200 import _lib
+from twilight_b200.cache import PAGE, PagedKVCache, quest_max_k, unpack_k4
+from twilight_b200.gen import make_decode_inputs, ragged_lengths
+from twilight_b200.kernel import ops
+from twilight_b200.step import DecodeWorkspace, SparseConfig, select_prune_attend_step
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+ATOL_MAX, ATOL_MEAN, P_TOL = 2e-2, 1e-3, 1e-4
+
+
+def _status_ok(ws):
+    assert int(ws.status.item()) == 0, f"device status flags {int(ws.status.item())}"
+
+
+# ---- cache-append side -------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_quantizer_codes_bit_exact(dt):
+    g = torch.Generator().manual_seed(0)
+    k = torch.randn(7, 3, PAGE, 128, generator=g) * 1.3
+    k[0, 0, 0, :32] = 0.25          # constant group
+    k[1, 1, 5] *= 20.0              # large-range row
+    k[2, 2, 3, 64:96] = torch.linspace(-1, 1, 32)
+    k = k.to(dt)
+    k4 = ops.quantize_k_pages(k.to(DEV)).cpu()
+    codes, scale, zmin = unpack_k4(k4)
+    deq, ocodes, oscales, ozeros = O.quantize_min_max(k, 4, group=32)
+    const = (k.reshape(7, 3, PAGE, 4, 32).amax(-1) == k.reshape(7, 3, PAGE, 4, 32).amin(-1))
+    ok = ~const.unsqueeze(-1).expand(7, 3, PAGE, 4, 32).reshape(7, 3, PAGE, 128)
+    assert torch.equal(codes[ok], ocodes[ok])
+    assert (codes[~ok] == 0).all()  # constant groups: code 0 (the fp16 reference yields NaN here)
+    assert torch.equal(scale[~const], oscales.to(torch.float16)[~const])
+    assert torch.equal(zmin, (-ozeros).to(torch.float16))
+
+
+def test_page_meta_and_append_match_bulk_build():
+    lens = [1, 15, 16, 17, 33, 100]
+    g = torch.Generator().manual_seed(1)
+    lmax = max(lens)
+    k = torch.randn(len(lens), 2, lmax, 128, generator=g).to(torch.bfloat16)
+    v = torch.randn(len(lens), 2, lmax, 128, generator=g).to(torch.bfloat16)
+    full = PagedKVCache.from_dense(k.to(DEV), v.to(DEV), lens, shuffle_seed=3)
+    for b, n in enumerate(lens):
+        for h in range(2):
+            kmin, kmax = full.dense_meta(b, h)
+            kk = k[b, h, :n]
+            npg = (n + PAGE - 1) // PAGE
+            for pg in range(npg):
+                seg = kk[pg * PAGE: min(n, pg * PAGE + PAGE)]
+                assert torch.equal(kmin[pg].cpu(), seg.amin(0)) and torch.equal(kmax[pg].cpu(), seg.amax(0))
+    # grow a second cache token by token with append_kv and compare everything that is defined
+    grown = PagedKVCache.from_dense(k.to(DEV)[:, :, :1], v.to(DEV)[:, :, :1], [1] * len(lens), build_aux=False)
+    total = full.k_pages.shape[0]
+    grown.k_pages = torch.zeros_like(full.k_pages)
+    grown.v_pages = torch.zeros_like(full.v_pages)
+    grown.k4_pages = torch.zeros_like(full.k4_pages)
+    grown.kmeta = torch.zeros_like(full.kmeta)
+    grown.kv_indices = full.kv_indices
+    grown.kv_indptr = full.kv_indptr.clone()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for t in range(lmax):
+        alive = [b for b, n in enumerate(lens) if t < n]
+        # page table of the sequences that still grow: first t+1 tokens
+        npg = [(min(t + 1, n) + PAGE - 1) // PAGE for n in lens]
+        indptr_full = full.kv_indptr.cpu()
+        sub_indices = torch.cat([full.kv_indices.cpu()[indptr_full[b]: indptr_full[b] + npg[b]] for b in alive])
+        sub_indptr = torch.zeros(len(alive) + 1, dtype=torch.int32)
+        sub_indptr[1:] = torch.tensor([npg[b] for b in alive], dtype=torch.int32).cumsum(0)
+        sub_last = torch.full((len(alive),), t % PAGE + 1, dtype=torch.int32)
+        ops.append_kv(k[alive, :, t].contiguous().to(DEV), v[alive, :, t].contiguous().to(DEV),
+                      grown.k_pages, grown.v_pages, grown.k4_pages, grown.kmeta,
+                      sub_indptr.to(DEV), sub_indices.to(DEV), sub_last.to(DEV), status=status)
+    assert int(status.item()) == 0
+    grown.kv_indptr, grown.seq_lens = full.kv_indptr, lens
+    grown.kv_last_page_len = full.kv_last_page_len
+    for b, n in enumerate(lens):
+        for h in range(2):
+            for a, c in zip(full.dense_kv(b, h), grown.dense_kv(b, h)):
+                assert torch.equal(a, c)
+            for a, c in zip(full.dense_k4(b, h), grown.dense_k4(b, h)):
+                assert torch.equal(a, c)
+            for a, c in zip(full.dense_meta(b, h), grown.dense_meta(b, h)):
+                assert torch.equal(a, c)
+
+
+# ---- selector ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("hq,hkv", [(4, 4), (8, 2), (8, 1)])
+def test_quest_select_vs_oracle(hq, hkv):
+    lens = [100, 1000, 257, 16]
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=torch.bfloat16, device=DEV,
+                                  seed=4, recipe="mid", shuffle_pages=True)
+    budget = 160
+    cand_pages, cand_npages, page_scores = ops.quest_select(
+        q, cache.kmeta, cache.kv_indptr, cache.kv_indices, budget, max_pages=cache.max_pages)
+    torch.cuda.synchronize()
+    g = hq // hkv
+    for b, n in enumerate(lens):
+        npg = (n + PAGE - 1) // PAGE
+        k = quest_max_k(budget, npg)
+        for h in range(hq):
+            want = U.oracle_page_scores(q, cache, b, h, g)
+            got = page_scores[b, h, :npg].cpu().numpy()
+            assert np.allclose(got, want, rtol=1e-5, atol=1e-4)
+            assert int(cand_npages[b, h]) == k
+            pages = cand_pages[b, h, :k].cpu().numpy()
+            assert (np.diff(pages) > 0).all()
+            # selection is exact with respect to the kernel's own scores, ties to lower pages
+            must, tie, thr = U.expected_candidates(got, k)
+            sel = set(pages.tolist())
+            assert must <= sel <= (must | tie)
+            need = k - len(must)
+            assert sorted(sel - must) == sorted(tie)[:need]
+            # and consistent with the oracle's scores up to rounding at the boundary
+            omust, otie, othr = U.expected_candidates(want, k)
+            for pg in sel ^ (omust | set(sorted(otie)[: k - len(omust)])):
+                assert abs(want[pg] - othr) <= 1e-3 * max(1.0, abs(othr))
+
+
+def test_quest_selector_mask_interface_matches_reference_fixture(golden):
+    from twilight_b200.pyimpl import quest_selector
+    q = torch.from_numpy(golden["quest_q"]).to(torch.bfloat16).to(DEV)
+    k = torch.from_numpy(golden["quest_k"]).to(torch.bfloat16).to(DEV)
+    qf, kf = q.float().cpu(), k.float().cpu()
+    scores = O.quest_page_scores(qf.reshape(2, 4, 1, 128), kf, 16)[:, :, 0].numpy()
+    for budget in (32, 40, 1000):
+        m = quest_selector(None, q, k, 16, token_budget=budget).cpu().numpy()
+        ref = golden[f"quest_mask_bf16_{budget}"]
+        assert m.shape == ref.shape
+        kk = quest_max_k(budget, 7)
+        for b in range(2):
+            for h in range(4):
+                diff_pages = set((np.nonzero(m[b, h, 0] != ref[b, h, 0])[0] // 16).tolist())
+                thr = np.sort(scores[b, h])[::-1][kk - 1]
+                # the reference ranks bf16-rounded scores; only pages tied with the k-th after
+                # that rounding may differ
+                for pg in diff_pages:
+                    assert abs(scores[b, h, pg] - thr) <= 2 ** -7 * abs(thr) + 1e-3
+
+
+# ---- estimator -------------------------------------------------------------------------------------
+@pytest.mark.parametrize("variant,tol", [(1, 2e-4), (2, 6e-2), (3, 2e-3)])
+@pytest.mark.parametrize("hq,hkv,dt", [(4, 4, torch.float16), (8, 2, torch.bfloat16), (8, 1, torch.bfloat16),
+                                       (4, 2, torch.float16)])
+def test_estimator_full_context(variant, tol, hq, hkv, dt):
+    lens = [1, 15, 16, 17, 31, 33, 700, 1025]
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=dt, device=DEV, seed=5,
+                                  recipe="literal", shuffle_pages=True)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scores = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices,
+                               cache.kv_last_page_len, max_pages=cache.max_pages, variant=variant,
+                               status=status)
+    assert int(status.item()) == 0
+    g = hq // hkv
+    for b, n in enumerate(lens):
+        npg = (n + PAGE - 1) // PAGE
+        for h in range(hq):
+            want, _ = U.oracle_scores_row(q, cache, b, h, g)
+            got = scores[b, h, : npg * PAGE].cpu().numpy()
+            assert np.array_equal(np.isinf(got), np.isinf(want))
+            fin = np.isfinite(want)
+            scale = max(1.0, float(np.abs(want[fin]).max()))
+            assert np.abs(got[fin] - want[fin]).max() <= tol * scale, (variant, b, h)
+
+
+@pytest.mark.parametrize("variant,tol", [(1, 2e-4), (3, 2e-3)])
+def test_estimator_candidate_lists(variant, tol):
+    lens = [300, 2000, 17]
+    hq, hkv = 8, 2
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.01, dtype=torch.bfloat16, device=DEV,
+                                  seed=6, recipe="mid", shuffle_pages=True)
+    cand_pages, cand_npages, _ = ops.quest_select(q, cache.kmeta, cache.kv_indptr, cache.kv_indices, 512,
+                                                  max_pages=cache.max_pages)
+    scores = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices,
+                               cache.kv_last_page_len, max_pages=cache.max_pages,
+                               cand_pages=cand_pages, cand_npages=cand_npages, variant=variant)
+    for b in range(len(lens)):
+        for h in range(hq):
+            k = int(cand_npages[b, h])
+            pages = cand_pages[b, h, :k].cpu().numpy()
+            want, _ = U.oracle_scores_row(q, cache, b, h, hq // hkv, pages)
+            got = scores[b, h, : k * PAGE].cpu().numpy()
+            assert np.array_equal(np.isinf(got), np.isinf(want))
+            fin = np.isfinite(want)
+            assert np.abs(got[fin] - want[fin]).max() <= tol * max(1.0, float(np.abs(want[fin]).max()))
+
+
+def test_gemv_entry_with_the_reference_call_signature():
+    lens = [64, 64]
+    q, cache = make_decode_inputs(2, 4, 4, lens, dtype=torch.float16, device=DEV, seed=7)
+    o = torch.empty(2, 4, 64, dtype=torch.float32, device=DEV)
+    ops.batched_sparse_gemv_int4_k(q, o, cache.k4_pages, None, None, cache.kv_indices, cache.kv_indptr,
+                                   cache.kv_last_page_len)
+    codes, scale, zmin = (t.cpu() for t in cache.dense_k4(1, 2))
+    want = O.estimate_logits_from_codes(q[1, 2].cpu(), codes, scale, zmin, 32, 1.0).numpy()
+    assert np.abs(o[1, 2].cpu().numpy() - want).max() <= 2e-3 * np.abs(want).max()
+    with pytest.raises(_lib.TwilightError):
+        ops.batched_sparse_gemv_int4_k(q, o, cache.k4_pages, torch.ones(1), None, cache.kv_indices,
+                                       cache.kv_indptr, cache.kv_last_page_len)
+
+
+# ---- pruner ------------------------------------------------------------------------------------------
+def _prune_parity(q, cache, hq, top_p, cand_pages=None, cand_npages=None):
+    scores = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices,
+                               cache.kv_last_page_len, max_pages=cache.max_pages,
+                               cand_pages=cand_pages, cand_npages=cand_npages)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    thr = torch.zeros(cache.batch, hq, 2, device=DEV)
+    indices, budget = ops.topp_prune(scores, cache.kv_indptr, cache.kv_last_page_len, top_p,
+                                     cand_pages=cand_pages, cand_npages=cand_npages, threshold=thr,
+                                     status=status)
+    assert int(status.item()) == 0
+    exempt = 0
+    for b, n in enumerate(cache.seq_lens):
+        npg = (n + PAGE - 1) // PAGE
+        for h in range(hq):
+            if cand_pages is None:
+                pages = np.arange(npg)
+            else:
+                pages = cand_pages[b, h, : int(cand_npages[b, h])].cpu().numpy()
+            row = scores[b, h, : len(pages) * PAGE].cpu().numpy()   # identical input for both sides
+            probs, keep, low = U.oracle_prune_row(row, pages, top_p)
+            bud = int(budget[b, h])
+            got = indices[b, h, :bud].cpu().numpy()
+            assert (np.diff(got) > 0).all()
+            d = U.check_index_parity(got, probs, keep, low, pages, P_TOL)
+            assert abs(bud - int(keep.sum())) <= d
+            exempt += d
+    return exempt, indices, budget
+
+
+@pytest.mark.parametrize("recipe,top_p", [("literal", 0.95), ("mid", 0.95), ("calibrated", 0.9), ("mid", 1.0)])
+def test_prune_full_context_vs_oracle(recipe, top_p):
+    lens = [1, 15, 16, 17, 33, 700, 4096, 9000]
+    hq, hkv = 8, 2
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.01, dtype=torch.bfloat16, device=DEV,
+                                  seed=8, recipe=recipe, shuffle_pages=True)
+    _prune_parity(q, cache, hq, top_p)
+
+
+def test_prune_with_candidates_and_missing_sink():
+    lens = [3000, 5000]
+    hq, hkv = 4, 4
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.01, dtype=torch.float16, device=DEV,
+                                  seed=9, recipe="mid")
+    cand_pages, cand_npages, _ = ops.quest_select(q, cache.kmeta, cache.kv_indptr, cache.kv_indices, 1024,
+                                                  max_pages=cache.max_pages)
+    _prune_parity(q, cache, hq, 0.95, cand_pages, cand_npages)
+    # drop page 0 from every list: token 0 is no longer a candidate, so nothing is pruned
+    cp = cand_pages.clone()
+    first_is_zero = cp[:, :, 0] == 0
+    assert first_is_zero.any()
+    cp[:, :, 0] = torch.where(first_is_zero, cp[:, :, 1], cp[:, :, 0])  # duplicate page 1: still ascending-ish
+    scores = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
+                               max_pages=cache.max_pages, cand_pages=cp, cand_npages=cand_npages)
+    _, budget = ops.topp_prune(scores, cache.kv_indptr, cache.kv_last_page_len, 0.95, cand_pages=cp,
+                               cand_npages=cand_npages)
+    nz = (torch.softmax(scores, -1) > 0).sum(-1)
+    assert torch.equal(budget[first_is_zero].long(), nz[first_is_zero])
+
+
+def test_prune_is_deterministic_and_per_row_threshold():
+    lens = [2048] * 3
+    hq = 4
+    q, cache = make_decode_inputs(3, hq, 4, lens, rho=0.01, dtype=torch.bfloat16, device=DEV, seed=10,
+                                  recipe="calibrated")
+    scores = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
+                               max_pages=cache.max_pages)
+    p_arr = torch.linspace(0.5, 0.99, 12, device=DEV)
+    i1, b1 = ops.topp_prune(scores, cache.kv_indptr, cache.kv_last_page_len, p_arr)
+    i2, b2 = ops.topp_prune(scores, cache.kv_indptr, cache.kv_last_page_len, p_arr)
+    assert torch.equal(b1, b2)
+    for r in range(12):
+        n = int(b1.flatten()[r])
+        assert torch.equal(i1.reshape(12, -1)[r, :n], i2.reshape(12, -1)[r, :n])
+    assert (b1.flatten()[1:] >= b1.flatten()[:-1] - 64).any()
+    for r in (0, 11):
+        row = scores.reshape(12, -1)[r].cpu().numpy()
+        probs, keep, low = U.oracle_prune_row(row, np.arange(128), float(p_arr[r]))
+        U.check_index_parity(i1.reshape(12, -1)[r, : int(b1.flatten()[r])].cpu().numpy(), probs, keep, low,
+                             np.arange(128), P_TOL)
+
+
+# ---- reference-compatible mask operators -----------------------------------------------------------------
+@pytest.mark.parametrize("L", [7, 64, 1000, 4096, 32768, 60000])
+def test_top_p_fp32_return_mask_vs_oracle(L):
+    from twilight_b200.kernel import top_p_fp32_return_mask
+    g = torch.Generator().manual_seed(L)
+    logits = torch.randn(2, 3, 1, L, generator=g) * 2.5
+    logits[..., 0] += 6.0
+    logits[0, 1, 0, 0] = -3.0          # a row whose sink is small
+    probs = torch.softmax(logits, -1)
+    probs[1, 2, 0, 0] = 0.0            # a row whose sink is not a candidate
+    for top_p in (0.9, torch.tensor([0.5, 0.7, 0.8, 0.9, 0.95, 0.99])):
+        m = top_p_fp32_return_mask(probs.to(DEV), top_p if not torch.is_tensor(top_p) else top_p.to(DEV))
+        assert m.dtype == torch.bool and m.shape == probs.shape
+        want = O.top_p_return_mask(probs, top_p)
+        got = m.cpu()
+        rows = probs.reshape(6, L).numpy()
+        for r in range(6):
+            bad = np.nonzero(got.reshape(6, L)[r].numpy() != want.reshape(6, L)[r].numpy())[0]
+            if bad.size:
+                p = float(top_p[r]) if torch.is_tensor(top_p) else top_p
+                low, _ = O.top_p_search(rows[r], p)
+                assert (np.abs(rows[r][bad] - low) <= P_TOL).all()
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+def test_top_p_fp16_return_mask_keeps_the_head_of_the_distribution(dt):
+    from twilight_b200.kernel import top_p_fp16_return_mask
+    g = torch.Generator().manual_seed(11)
+    logits = torch.randn(2, 2, 1, 2048, generator=g) * 3
+    logits[..., 0] += 8
+    probs = torch.softmax(logits, -1).to(dt)
+    m = top_p_fp16_return_mask(probs.to(DEV), 0.9).cpu()
+    pf = probs.float()
+    kept = (pf * m).sum(-1)
+    assert (kept >= 0.9 - 2e-2).all()
+    assert m[..., 0].all()                                   # the sink is always kept
+    thr = torch.where(m, pf, torch.full_like(pf, 9.0)).amin(-1, keepdim=True)
+    assert (~(pf > thr) | m).all()                           # a threshold mask: nothing above it is dropped
+
+
+def test_mask_operator_argument_errors():
+    from twilight_b200.kernel import top_p_fp32_return_mask
+    with pytest.raises(_lib.TwilightError, match="4D"):
+        top_p_fp32_return_mask(torch.rand(4, 8, device=DEV), 0.9)
+    with pytest.raises(_lib.TwilightError, match="contiguous"):
+        top_p_fp32_return_mask(torch.rand(1, 2, 1, 16, device=DEV).transpose(0, 1), 0.9)
+    with pytest.raises(_lib.TwilightError, match="float32"):
+        top_p_fp32_return_mask(torch.rand(1, 2, 1, 16, device=DEV).half(), 0.9)
+
+
+# ---- attention ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("chunk", [32, 256])
+def test_sparse_attention_vs_oracle(dt, chunk):
+    lens = [1, 17, 600, 3000]
+    hq, hkv = 8, 2
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=dt, device=DEV, seed=12,
+                                  recipe="calibrated", shuffle_pages=True)
+    stride = cache.max_pages * PAGE
+    g = torch.Generator().manual_seed(13)
+    indices = torch.zeros(len(lens), hq, stride, dtype=torch.int32)
+    budget = torch.zeros(len(lens), hq, dtype=torch.int32)
+    for b, n in enumerate(lens):
+        for h in range(hq):
+            nb = [0, 1, min(n, 5), min(n, 33), n, min(n, 257), min(n, 1000), n // 2][h] if (b, h) != (0, 0) else 1
+            budget[b, h] = nb
+            indices[b, h, :nb] = torch.sort(torch.randperm(n, generator=g)[:nb])[0].int()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices,
+                                 indices.to(DEV), budget.to(DEV), chunk=chunk, status=status)
+    out2 = ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices,
+                                  indices.to(DEV), budget.to(DEV), chunk=chunk, status=status)
+    assert int(status.item()) == 0
+    errs = []
+    for b, n in enumerate(lens):
+        for h in range(hq):
+            k, v = cache.dense_kv(b, h // (hq // hkv))
+            nb = int(budget[b, h])
+            want = O.sparse_attention_fp32(q[b, h].float().cpu().numpy(), k.float().cpu().numpy(),
+                                           v.float().cpu().numpy(), indices[b, h, :nb].numpy().astype(np.int64),
+                                           U.SM_SCALE)
+            errs.append(np.abs(out[b, h].float().cpu().numpy() - want))
+    errs = np.stack(errs)
+    assert errs.max() <= ATOL_MAX and errs.mean() <= ATOL_MEAN
+    # split-KV merge order may differ between runs only in the last bit of the fp32 partial sums
+    assert (out.float() - out2.float()).abs().max() <= 2e-2
+
+
+def test_attention_workspace_and_bad_index_handling():
+    q, cache = make_decode_inputs(1, 2, 2, [64], dtype=torch.bfloat16, device=DEV, seed=14)
+    indices = torch.tensor([[[0, 5, 9999] + [0] * 61, [1, 2, 3] + [0] * 61]], dtype=torch.int32, device=DEV)
+    budget = torch.tensor([[3, 3]], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices,
+                                 indices, budget, status=status)
+    assert int(status.item()) & ops.FLAG_BAD_INDEX            # the out-of-range token is skipped, not read
+    assert torch.isfinite(out.float()).all()
+    with pytest.raises(_lib.TwilightError, match="workspace"):
+        ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices,
+                               indices, budget, workspace=torch.zeros(16, dtype=torch.uint8, device=DEV))
+
+
+# ---- whole step ------------------------------------------------------------------------------------------------
+def _step_vs_oracle(q, cache, hq, cfg, rows, dtype_faithful_report=False):
+    ws = DecodeWorkspace.for_cache(cache, hq, cfg)
+    out = select_prune_attend_step(q, cache, ws).clone()
+    torch.cuda.synchronize()
+    _status_ok(ws)
+    g = hq // cache.num_kv_heads
+    errs, exempt = [], 0
+    for (b, h) in rows:
+        n = cache.seq_lens[b]
+        npg = (n + PAGE - 1) // PAGE
+        if cfg.selector == "quest":
+            k = int(ws.cand_npages[b, h])
+            assert k == quest_max_k(cfg.token_budget, npg)
+            pages = ws.cand_pages[b, h, :k].cpu().numpy()
+            want_scores = U.oracle_page_scores(q, cache, b, h, g)
+            must, tie, thr = U.expected_candidates(want_scores, k)
+            sel = set(pages.tolist())
+            for pg in (sel ^ (must | set(sorted(tie)[: k - len(must)]))):
+                assert abs(want_scores[pg] - thr) <= 1e-3 * max(1.0, abs(thr))
+        else:
+            pages = np.arange(npg)
+        want_row, _ = U.oracle_scores_row(q, cache, b, h, g, pages)
+        got_row = ws.scores[b, h, : len(pages) * PAGE].cpu().numpy()
+        fin = np.isfinite(want_row)
+        assert np.abs(got_row[fin] - want_row[fin]).max() <= 2e-3 * max(1.0, float(np.abs(want_row[fin]).max()))
+        # pruner on the oracle's own scores (end-to-end chain), tokens near the threshold exempt
+        probs, keep, low = U.oracle_prune_row(want_row, pages, cfg.threshold)
+        bud = int(ws.budget[b, h])
+        got_idx = ws.indices[b, h, :bud].cpu().numpy()
+        d = U.check_index_parity(got_idx, probs, keep, low, pages, P_TOL)
+        assert abs(bud - int(keep.sum())) <= d
+        exempt += d
+        kd, vd = cache.dense_kv(b, h // g)
+        want_out = O.sparse_attention_fp32(q[b, h].float().cpu().numpy(), kd.float().cpu().numpy(),
+                                           vd.float().cpu().numpy(),
+                                           U.slots_to_tokens(pages, np.nonzero(keep)[0]).astype(np.int64), U.SM_SCALE)
+        errs.append(np.abs(out[b, h].float().cpu().numpy() - want_out))
+    errs = np.stack(errs)
+    assert errs.max() <= ATOL_MAX and errs.mean() <= ATOL_MEAN
+    return ws, exempt
+
+
+@pytest.mark.parametrize("recipe", ["literal", "mid", "calibrated"])
+def test_step_config0_fp16_full_candidates(recipe):
+    # B=1, 32 query heads = 32 KV heads, L=4096, fp16, 1% heavy hitters, selector none, top-p 0.95
+    q, cache = make_decode_inputs(1, 32, 32, 4096, rho=0.01, dtype=torch.float16, device=DEV, seed=0, recipe=recipe)
+    cfg = SparseConfig(selector="none", weight_pruner="top_p", threshold=0.95)
+    ws, _ = _step_vs_oracle(q, cache, 32, cfg, [(0, h) for h in range(32)])
+    if recipe == "literal":
+        assert (ws.budget == 1).all()     # all softmax mass sits on the sink
+    if recipe == "mid":
+        assert 20 <= float(ws.budget.float().mean()) <= 80
+    if recipe == "calibrated":
+        assert float(ws.budget.float().mean()) > 1000
+
+
+def test_step_config0_against_dtype_faithful_pyimpl():
+    """The reference's own dtype path (fp16 logits, fp16 fake-quant, dense masked attention):
+    budgets and outputs must be close even though its logits carry fp16 rounding."""
+    q, cache = make_decode_inputs(1, 32, 32, 4096, rho=0.01, dtype=torch.float16, device=DEV, seed=0, recipe="mid")
+    cfg = SparseConfig(selector="none", weight_pruner="top_p", threshold=0.95)
+    ws = DecodeWorkspace.for_cache(cache, 32, cfg)
+    out = select_prune_attend_step(q, cache, ws).float().cpu()
+    kd = torch.stack([cache.dense_kv(0, h)[0] for h in range(32)]).cpu()[None]
+    vd = torch.stack([cache.dense_kv(0, h)[1] for h in range(32)]).cpu()[None]
+    ref = O.decode_step(q.cpu()[:, :, None], kd, vd, selector="none", quant_group=32, threshold=0.95)
+    assert ref["out"].dtype == torch.float16
+    assert (out - ref["out"][:, :, 0].float()).abs().max() <= ATOL_MAX
+    diff = (ws.budget.cpu().flatten().float() - ref["budget"].float()).abs()
+    assert ((diff <= 2) | (diff / ref["budget"].float() <= 0.15)).all()
+
+
+@pytest.mark.parametrize("hq,hkv,sel", [(8, 8, "quest"), (8, 2, "quest"), (8, 2, "none")])
+def test_step_ragged_gqa(hq, hkv, sel):
+    lens = ragged_lengths(6, 500, 3000, seed=3) + [16, 17]
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=(0.001, 0.05), dtype=torch.bfloat16, device=DEV,
+                                  seed=15, recipe="mid", shuffle_pages=True)
+    cfg = SparseConfig(selector=sel, token_budget=1024, weight_pruner="top_p", threshold=0.9)
+    rows = [(b, h) for b in range(len(lens)) for h in range(0, hq, 3)]
+    _step_vs_oracle(q, cache, hq, cfg, rows)
+
+
+def test_step_repeatable_and_graph_capturable():
+    q, cache = make_decode_inputs(2, 8, 8, 2048, rho=0.01, dtype=torch.bfloat16, device=DEV, seed=16, recipe="mid")
+    cfg = SparseConfig(selector="quest", token_budget=512, threshold=0.95)
+    ws = DecodeWorkspace.for_cache(cache, 8, cfg)
+    o1 = select_prune_attend_step(q, cache, ws).clone()
+    b1, i1 = ws.budget.clone(), ws.indices.clone()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        select_prune_attend_step(q, cache, ws)
+    torch.cuda.current_stream().wait_stream(s)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        select_prune_attend_step(q, cache, ws)
+    ws.out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(ws.budget, b1)
+    for r in range(16):
+        n = int(b1.flatten()[r])
+        assert torch.equal(ws.indices.reshape(16, -1)[r, :n], i1.reshape(16, -1)[r, :n])
+    assert (ws.out.float() - o1.float()).abs().max() <= 1e-2
+    _status_ok(ws)

@@ -1,0 +1,145 @@
+// Shared device/host helpers for the twilight_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/twilight_b200.h"
+
+namespace twl {
+
+constexpr int kPage = TWL_PAGE_SIZE;        // tokens per page
+constexpr int kD = TWL_HEAD_DIM;            // head dimension
+constexpr int kGroup = TWL_QUANT_GROUP;     // channels per quantisation group
+constexpr int kSlab = TWL_K4_SLAB_BYTES;    // bytes of one INT4 (page, kv-head) slab
+constexpr int kSlabCodes = kPage * kD / 2;  // 1024 code bytes, then 256 bytes of scale/min
+constexpr int kNumSMs = 148;
+
+// Records the last CUDA launch error for twl_last_cuda_error().
+void set_last_cuda_error(cudaError_t e);
+
+#define TWL_CHECK_LAUNCH()                         \
+  do {                                             \
+    cudaError_t e__ = cudaGetLastError();          \
+    if (e__ != cudaSuccess) {                      \
+      ::twl::set_last_cuda_error(e__);             \
+      return TWL_ERR_LAUNCH;                       \
+    }                                              \
+  } while (0)
+
+#define TWL_CUDA_TRY(expr)                         \
+  do {                                             \
+    cudaError_t e__ = (expr);                      \
+    if (e__ != cudaSuccess) {                      \
+      ::twl::set_last_cuda_error(e__);             \
+      return TWL_ERR_LAUNCH;                       \
+    }                                              \
+  } while (0)
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// ---- element type traits ---------------------------------------------------------------
+template <typename T>
+struct Elem;
+template <>
+struct Elem<__half> {
+  using T2 = __half2;
+  static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+  static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
+  static __device__ __forceinline__ float2 to_f2(uint32_t u) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&u));
+  }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  using T2 = __nv_bfloat162;
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
+  static __device__ __forceinline__ float2 to_f2(uint32_t u) {
+    // bf16 -> fp32 is a 16-bit shift
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+  }
+};
+
+// ---- warp / block reductions -------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Block-wide exclusive prefix sum of one int per thread; *total gets the block sum.
+// wsum: 33 ints of shared scratch.  Ends with a barrier, so it can be called in a loop.
+template <int THREADS>
+__device__ __forceinline__ int block_excl_scan(int v, int* total, int* wsum) {
+  constexpr int NW = THREADS / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) wsum[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int w = lane < NW ? wsum[lane] : 0;
+    int winc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int t = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += t;
+    }
+    if (lane < NW) wsum[lane] = winc - w;
+    if (lane == 31) wsum[32] = winc;
+  }
+  __syncthreads();
+  const int r = wsum[warp] + inc - v;
+  *total = wsum[32];
+  __syncthreads();
+  return r;
+}
+
+__device__ __forceinline__ void raise_flag(int32_t* status, int flag) {
+  if (status != nullptr) atomicOr(status, flag);
+}
+
+// 128-bit read-only global load that does not allocate in L1 (streamed once).
+__device__ __forceinline__ uint4 ldg_stream_u4(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ uint2 ldg_stream_u2(const void* p) {
+  uint2 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];"
+               : "=r"(r.x), "=r"(r.y)
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ uint32_t ldg_stream_u32(const void* p) {
+  uint32_t r;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(r) : "l"(p));
+  return r;
+}
+
+}  // namespace twl

@@ -1,0 +1,284 @@
+// Selector: Quest page scores from stored (min,max) page metadata, then top-k pages.
+//
+// Stands in for quest_selector of twilight/pyimpl/quest.py:17-122.  The reference rebuilds
+// the per-page channel maxima of sign(q)*K from the whole K cache on every step
+// (quest.py:37-74); here the channel-wise min and max of every page are kept as metadata and
+//   score(page) = sum_d max(q_d*kmax_d, q_d*kmin_d)            (== |q| . max_t sign(q)*K_t)
+// is evaluated in fp32.  The page count kept is quest.py:93-98; ties at the last kept score
+// go to the lower page number (torch.topk, quest.py:99, leaves them unspecified).
+#include "common.cuh"
+
+namespace twl {
+
+constexpr int kSelThreads = 256;
+constexpr int kSelPagesPerBlock = 128;  // 64 KiB of metadata per block
+
+struct ScoreParams {
+  const void* q;
+  const void* kmeta;
+  const int32_t* indptr;
+  const int32_t* indices;
+  float* page_scores;
+  int32_t* status;
+  int B, Hq, Hkv, num_pages_total, max_pages;
+};
+
+// Eight lanes share a page: lane `sub` reads 16-byte pieces sub and sub+8 of the 256-byte min
+// row and of the max row (channels 8*sub..8*sub+7 and 64+8*sub..), so a warp step covers four
+// pages = 2 KiB contiguous per page pair of rows.  G query heads share the loaded metadata.
+template <typename T, int G>
+__global__ void __launch_bounds__(kSelThreads)
+quest_page_scores_kernel(const ScoreParams p) {
+  const int row = blockIdx.y;  // (b, kv head)
+  const int b = row / p.Hkv, kvh = row % p.Hkv;
+  const int page_base = p.indptr[b];
+  const int n_pages = min(p.indptr[b + 1] - page_base, p.max_pages);
+  const int first = blockIdx.x * kSelPagesPerBlock;
+  if (first >= n_pages) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane & 7, pg_in_step = lane >> 3;
+  const int h0 = kvh * G;
+
+  float qf[G][16];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const T* qrow = reinterpret_cast<const T*>(p.q) + (size_t)(b * p.Hq + h0 + g) * kD;
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(qrow) + sub + 8 * part);
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = Elem<T>::to_f2(u[k]);
+        qf[g][8 * part + 2 * k] = f.x;
+        qf[g][8 * part + 2 * k + 1] = f.y;
+      }
+    }
+  }
+
+  const int last = min(first + kSelPagesPerBlock, n_pages);
+  for (int lp0 = first + warp * 4; lp0 < last; lp0 += (kSelThreads / 32) * 4) {
+    const int lp = lp0 + pg_in_step;
+    const bool live = lp < last;
+    uint4 mn[2], mx[2];
+    bool ok = false;
+    if (live) {
+      const int phys = p.indices[page_base + lp];
+      ok = phys >= 0 && phys < p.num_pages_total;
+      if (ok) {
+        const T* slab = reinterpret_cast<const T*>(p.kmeta) + ((size_t)phys * p.Hkv + kvh) * 2 * kD;
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          mn[part] = ldg_stream_u4(reinterpret_cast<const uint4*>(slab) + sub + 8 * part);
+          mx[part] = ldg_stream_u4(reinterpret_cast<const uint4*>(slab + kD) + sub + 8 * part);
+        }
+      } else {
+        raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+      }
+    }
+    float acc[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) acc[g] = 0.f;
+    if (ok) {
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        const uint32_t un[4] = {mn[part].x, mn[part].y, mn[part].z, mn[part].w};
+        const uint32_t ux[4] = {mx[part].x, mx[part].y, mx[part].z, mx[part].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 lo = Elem<T>::to_f2(un[k]), hi = Elem<T>::to_f2(ux[k]);
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const float q0 = qf[g][8 * part + 2 * k], q1 = qf[g][8 * part + 2 * k + 1];
+            acc[g] += fmaxf(q0 * hi.x, q0 * lo.x);
+            acc[g] += fmaxf(q1 * hi.y, q1 * lo.y);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 1);
+      acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 2);
+      acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 4);
+      if (live && (g & 7) == sub)
+        p.page_scores[(size_t)(b * p.Hq + h0 + g) * p.max_pages + lp] = ok ? acc[g] : -INFINITY;
+    }
+  }
+}
+
+// ---- top-k pages of one (batch, query head) row ---------------------------------------------
+__device__ __forceinline__ uint32_t order_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);  // larger float <=> larger key
+}
+
+constexpr int kTopkThreads = 256;
+
+__global__ void __launch_bounds__(kTopkThreads)
+quest_topk_pages_kernel(const float* __restrict__ page_scores, int max_pages,
+                        const int32_t* __restrict__ indptr, int Hq, int token_budget,
+                        int32_t* __restrict__ cand_pages, int32_t* __restrict__ cand_npages,
+                        int max_k) {
+  extern __shared__ __align__(16) uint32_t keys[];  // max_pages keys
+  __shared__ int hist[256];
+  __shared__ int wsum[33];
+  __shared__ uint32_t sh_prefix;
+  __shared__ int sh_krem;
+
+  const int row = blockIdx.x, b = row / Hq;
+  const int n = min(indptr[b + 1] - indptr[b], max_pages);
+  int k = max(1, token_budget / kPage) + ((token_budget % kPage) != 0 ? 1 : 0);  // quest.py:93-95
+  k = min(min(k, n), max_k);                                                     // quest.py:98
+  int32_t* out = cand_pages + (size_t)row * max_k;
+  if (threadIdx.x == 0) cand_npages[row] = k;
+  if (k <= 0) return;
+  if (k == n) {  // every page is kept
+    for (int i = threadIdx.x; i < n; i += kTopkThreads) out[i] = i;
+    return;
+  }
+  const float* src = page_scores + (size_t)row * max_pages;
+  for (int i = threadIdx.x; i < n; i += kTopkThreads) keys[i] = order_key(src[i]);
+  if (threadIdx.x == 0) {
+    sh_prefix = 0;
+    sh_krem = k;
+  }
+  __syncthreads();
+  // MSB-first radix select of the k-th largest key, 8 bits per pass
+  uint32_t mask = 0;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    hist[threadIdx.x] = 0;  // kTopkThreads == 256 bins
+    __syncthreads();
+    const uint32_t prefix = sh_prefix;
+    for (int i = threadIdx.x; i < n; i += kTopkThreads) {
+      const uint32_t key = keys[i];
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFF], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      // lane l owns bins 255-8l .. 248-8l (descending); find where the running count reaches k
+      const int lane = threadIdx.x;
+      const int krem = sh_krem;  // read by every lane before the scan's shuffles, written after
+      int local = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) local += hist[255 - 8 * lane - j];
+      int inc = local;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+      }
+      const int before = inc - local;
+      if (before < krem && krem <= inc) {
+        int run = before;
+        for (int j = 0; j < 8; ++j) {
+          const int bin = 255 - 8 * lane - j;
+          if (run + hist[bin] >= krem) {
+            sh_prefix = prefix | ((uint32_t)bin << shift);
+            sh_krem = krem - run;
+            break;
+          }
+          run += hist[bin];
+        }
+      }
+    }
+    mask |= 0xFFu << shift;
+    __syncthreads();
+  }
+  const uint32_t thr = sh_prefix;  // k-th largest key
+  const int take_eq = sh_krem;     // how many keys equal to it are kept (lowest pages first)
+  // ordered compaction, 4 consecutive pages per thread per tile
+  int base_gt = 0, base_eq = 0;
+  for (int t0 = 0; t0 < n; t0 += kTopkThreads * 4) {
+    const int i0 = t0 + threadIdx.x * 4;
+    int gt[4], eq[4], cg = 0, ce = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bool in = i0 + j < n;
+      const uint32_t key = in ? keys[i0 + j] : 0u;
+      gt[j] = in && key > thr;
+      eq[j] = in && key == thr;
+      cg += gt[j];
+      ce += eq[j];
+    }
+    int total;
+    const int packed = block_excl_scan<kTopkThreads>(cg | (ce << 16), &total, wsum);
+    int ng = base_gt + (packed & 0xFFFF), ne = base_eq + (packed >> 16);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (gt[j]) {
+        out[ng + min(ne, take_eq)] = i0 + j;
+        ++ng;
+      } else if (eq[j]) {
+        if (ne < take_eq) out[ng + ne] = i0 + j;
+        ++ne;
+      }
+    }
+    base_gt += total & 0xFFFF;
+    base_eq += total >> 16;
+  }
+}
+
+template <typename T, int G>
+static int launch_scores(const ScoreParams& p, cudaStream_t st) {
+  const int rows = p.B * p.Hkv;
+  if (rows > 65535) return TWL_ERR_TOO_LARGE;
+  dim3 grid((p.max_pages + kSelPagesPerBlock - 1) / kSelPagesPerBlock, rows);
+  quest_page_scores_kernel<T, G><<<grid, kSelThreads, 0, st>>>(p);
+  TWL_CHECK_LAUNCH();
+  return TWL_OK;
+}
+
+template <typename T>
+static int launch_scores_g(const ScoreParams& p, cudaStream_t st) {
+  switch (p.Hq / p.Hkv) {
+    case 1: return launch_scores<T, 1>(p, st);
+    case 2: return launch_scores<T, 2>(p, st);
+    case 4: return launch_scores<T, 4>(p, st);
+    case 8: return launch_scores<T, 8>(p, st);
+    default: return TWL_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace twl
+
+extern "C" int twl_quest_page_scores(const void* q, int dtype, const void* kmeta,
+                                     const int32_t* kv_indptr, const int32_t* kv_indices,
+                                     int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                     int32_t num_pages_total, float* page_scores,
+                                     int32_t max_pages, int32_t* status, void* stream) {
+  using namespace twl;
+  if (!q || !kmeta || !kv_indptr || !kv_indices || !page_scores) return TWL_ERR_BAD_ARG;
+  if (batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_pages_total <= 0 ||
+      max_pages <= 0 || num_q_heads % num_kv_heads != 0)
+    return TWL_ERR_BAD_ARG;
+  if (!aligned(q, 16) || !aligned(kmeta, 16)) return TWL_ERR_MISALIGNED;
+  ScoreParams p;
+  p.q = q; p.kmeta = kmeta; p.indptr = kv_indptr; p.indices = kv_indices;
+  p.page_scores = page_scores; p.status = status; p.B = batch; p.Hq = num_q_heads;
+  p.Hkv = num_kv_heads; p.num_pages_total = num_pages_total; p.max_pages = max_pages;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == TWL_F16) return launch_scores_g<__half>(p, st);
+  if (dtype == TWL_BF16) return launch_scores_g<__nv_bfloat16>(p, st);
+  return TWL_ERR_UNSUPPORTED;
+}
+
+extern "C" int twl_quest_topk_pages(const float* page_scores, int32_t max_pages,
+                                    const int32_t* kv_indptr, int32_t batch, int32_t num_q_heads,
+                                    int32_t token_budget, int32_t* cand_pages,
+                                    int32_t* cand_npages, int32_t max_k, void* stream) {
+  using namespace twl;
+  if (!page_scores || !kv_indptr || !cand_pages || !cand_npages) return TWL_ERR_BAD_ARG;
+  if (batch <= 0 || num_q_heads <= 0 || max_pages <= 0 || max_k <= 0 || token_budget < 0)
+    return TWL_ERR_BAD_ARG;
+  if (max_pages > 48 * 1024) return TWL_ERR_TOO_LARGE;  // keys of a row live in shared memory
+  const size_t smem = (size_t)max_pages * sizeof(uint32_t);
+  TWL_CUDA_TRY(cudaFuncSetAttribute(quest_topk_pages_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024 * 4));
+  quest_topk_pages_kernel<<<batch * num_q_heads, kTopkThreads, smem,
+                            reinterpret_cast<cudaStream_t>(stream)>>>(
+      page_scores, max_pages, kv_indptr, num_q_heads, token_budget, cand_pages, cand_npages,
+      max_k);
+  TWL_CHECK_LAUNCH();
+  return TWL_OK;
+}

@@ -1,0 +1,400 @@
+// Kernel #2: top-p pruner.
+//
+// Two forms share one search routine:
+//  * twl_top_p_return_mask_{f32,f16}: the reference operator (dense probabilities in,
+//    dense 0/1 mask out), csrc/include/sampling.cuh:119-231.
+//  * twl_topp_prune: fp32 softmax over the estimator's scores (twilight/pyimpl/top_p.py:11),
+//    the same search, then an ordered compaction into a token index list and a budget
+//    (replacing the mask AND/sum of twilight/pyimpl/attention.py:280-285).
+//
+// The search keeps the reference's decisions: low=0, high=x[0] (attention sink), each round
+// mid=(low+high)/2, S=sum{x>mid}, a=min({x>low},high), b=max({x<=high},low), low=mid if
+// S>=p else high=min(mid,b), until b-a<=1e-5; kept = x>low.  Unlike the reference, which
+// re-reads the row from global memory every round with one 1024-thread block, the row is
+// staged once into shared memory (it stays there for all rounds and for the compaction),
+// the three reductions of a round are fused into one pass, and a round limit replaces the
+// open-ended loop.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace twl {
+
+constexpr int kSearchRoundCap = 128;
+constexpr float kSearchEps = 1e-5f;
+// floats of a row that fit in shared memory next to the reduction scratch
+constexpr int kRowCap = 56 * 1024;
+
+template <typename T>
+struct Prec;  // rounding of the search scalars to the probability type, as the reference does
+template <>
+struct Prec<float> {
+  static __device__ __forceinline__ float rnd(float x) { return x; }
+  static __device__ __forceinline__ float load(const float* p, size_t i) { return p[i]; }
+};
+template <>
+struct Prec<__half> {
+  static __device__ __forceinline__ float rnd(float x) { return __half2float(__float2half_rn(x)); }
+  static __device__ __forceinline__ float load(const __half* p, size_t i) { return __half2float(p[i]); }
+};
+template <>
+struct Prec<__nv_bfloat16> {
+  static __device__ __forceinline__ float rnd(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+  static __device__ __forceinline__ float load(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }
+};
+
+struct Red3 {
+  float s, a, b;
+};
+
+// Block-wide (sum, min, max) in one barrier.  `buf` holds 3*32 floats and must not be the
+// buffer used by the previous call (callers alternate two buffers).
+template <int THREADS>
+__device__ __forceinline__ Red3 block_red3(float s, float a, float b, float* buf) {
+  constexpr int NW = THREADS / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  s = warp_sum(s);
+  a = warp_min(a);
+  b = warp_max(b);
+  if (lane == 0) {
+    buf[warp] = s;
+    buf[32 + warp] = a;
+    buf[64 + warp] = b;
+  }
+  __syncthreads();
+  float s2 = lane < NW ? buf[lane] : 0.f;
+  float a2 = lane < NW ? buf[32 + lane] : INFINITY;
+  float b2 = lane < NW ? buf[64 + lane] : -INFINITY;
+  Red3 r;
+  r.s = warp_sum(s2);
+  r.a = warp_min(a2);
+  r.b = warp_max(b2);
+  return r;
+}
+
+// Runs the pivot search over x[0..n) (shared or global memory), returns `low`.
+// PT = type whose rounding the scalars follow.  red = 2*96 floats of shared scratch.
+template <int THREADS, typename PT, typename F>
+__device__ float topp_search(F load, int n, float x0, float p_in, float* red, int32_t* status) {
+  const float p = Prec<PT>::rnd(p_in);
+  const float eps = Prec<PT>::rnd(kSearchEps);
+  float low = 0.f, high = x0;
+  int round = 0;
+  while (true) {
+    const float mid = Prec<PT>::rnd(Prec<PT>::rnd(low + high) * 0.5f);
+    float s = 0.f, a = high, b = low;
+    for (int i = threadIdx.x; i < n; i += THREADS) {
+      const float x = load(i);
+      s += (x > mid) ? x : 0.f;
+      a = (x > low) ? fminf(a, x) : a;
+      b = (x <= high) ? fmaxf(b, x) : b;
+    }
+    Red3 r = block_red3<THREADS>(s, a, b, red + (round & 1) * 96);
+    if (Prec<PT>::rnd(r.s) >= p) {
+      low = mid;
+    } else {
+      high = fminf(mid, r.b);
+    }
+    ++round;
+    if (!(Prec<PT>::rnd(r.b - r.a) > eps)) break;
+    if (round >= kSearchRoundCap) {
+      if (threadIdx.x == 0) raise_flag(status, TWL_FLAG_ITER_CAP);
+      break;
+    }
+  }
+  return low;
+}
+
+// Same search with the row in shared memory and 4 elements per access.
+template <int THREADS>
+__device__ float topp_search_smem4(const float* x, int n4, float x0, float p, float* red,
+                                   int32_t* status) {
+  const float4* x4 = reinterpret_cast<const float4*>(x);
+  float low = 0.f, high = x0;
+  int round = 0;
+  while (true) {
+    const float mid = (low + high) * 0.5f;
+    float s = 0.f, a = high, b = low;
+    for (int i = threadIdx.x; i < n4; i += THREADS) {
+      const float4 v = x4[i];
+      const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        s += (e[k] > mid) ? e[k] : 0.f;
+        a = (e[k] > low) ? fminf(a, e[k]) : a;
+        b = (e[k] <= high) ? fmaxf(b, e[k]) : b;
+      }
+    }
+    Red3 r = block_red3<THREADS>(s, a, b, red + (round & 1) * 96);
+    if (r.s >= p) {
+      low = mid;
+    } else {
+      high = fminf(mid, r.b);
+    }
+    ++round;
+    if (!(r.b - r.a > kSearchEps)) break;
+    if (round >= kSearchRoundCap) {
+      if (threadIdx.x == 0) raise_flag(status, TWL_FLAG_ITER_CAP);
+      break;
+    }
+  }
+  return low;
+}
+
+// ---- dense mask form ------------------------------------------------------------------------
+template <int THREADS, typename T, bool IN_SMEM>
+__global__ void __launch_bounds__(THREADS)
+top_p_mask_kernel(const T* __restrict__ probs, uint8_t* __restrict__ mask,
+                  const float* __restrict__ top_p_arr, float top_p_val, uint32_t d,
+                  int32_t* status) {
+  extern __shared__ __align__(16) float smem[];
+  float* red = smem;        // 192 floats
+  float* row = smem + 192;  // d floats when IN_SMEM
+  const size_t base = (size_t)blockIdx.x * d;
+  const float p = top_p_arr ? top_p_arr[blockIdx.x] : top_p_val;
+  const T* src = probs + base;
+  if (IN_SMEM) {
+    for (uint32_t i = threadIdx.x; i < d; i += THREADS) row[i] = Prec<T>::load(src, i);
+    __syncthreads();
+  }
+  const float x0 = IN_SMEM ? row[0] : Prec<T>::load(src, 0);
+  float low;
+  if (IN_SMEM) {
+    low = topp_search<THREADS, T>([&](int i) { return row[i]; }, (int)d, x0, p, red, status);
+  } else {
+    low = topp_search<THREADS, T>([&](int i) { return Prec<T>::load(src, i); }, (int)d, x0, p, red, status);
+  }
+  uint8_t* dst = mask + base;
+  if ((d & 3u) == 0 && ((reinterpret_cast<uintptr_t>(dst) & 3u) == 0)) {
+    uint32_t* dst4 = reinterpret_cast<uint32_t*>(dst);
+    for (uint32_t i = threadIdx.x; i < d / 4; i += THREADS) {
+      uint32_t m = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float x = IN_SMEM ? row[4 * i + k] : Prec<T>::load(src, 4 * i + k);
+        m |= (x > low ? 1u : 0u) << (8 * k);
+      }
+      dst4[i] = m;
+    }
+  } else {
+    for (uint32_t i = threadIdx.x; i < d; i += THREADS) {
+      const float x = IN_SMEM ? row[i] : Prec<T>::load(src, i);
+      dst[i] = x > low ? 1 : 0;
+    }
+  }
+}
+
+template <typename T>
+static int launch_mask(const T* probs, uint8_t* mask, const float* top_p_arr, float top_p_val,
+                       uint32_t rows, uint32_t d, int32_t* status, cudaStream_t st) {
+  constexpr int THREADS = 1024;
+  if (d <= (uint32_t)kRowCap) {
+    const size_t smem = (192 + (size_t)d) * sizeof(float);
+    auto kern = top_p_mask_kernel<THREADS, T, true>;
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<rows, THREADS, smem, st>>>(probs, mask, top_p_arr, top_p_val, d, status);
+  } else {
+    auto kern = top_p_mask_kernel<THREADS, T, false>;
+    kern<<<rows, THREADS, 192 * sizeof(float), st>>>(probs, mask, top_p_arr, top_p_val, d, status);
+  }
+  TWL_CHECK_LAUNCH();
+  return TWL_OK;
+}
+
+// ---- fused softmax + search + compaction ---------------------------------------------------
+struct PruneParams {
+  const float* scores;
+  const int32_t* indptr;
+  const int32_t* last_len;
+  const int32_t* cand_pages;
+  const int32_t* cand_npages;
+  const float* top_p_arr;
+  int32_t* out_indices;
+  int32_t* out_budget;
+  float* out_threshold;
+  int32_t* status;
+  int stride, max_k, B, Hq, index_stride;
+  float top_p_val;
+};
+
+template <int THREADS, bool IN_SMEM>
+__global__ void __launch_bounds__(THREADS)
+topp_prune_kernel(const PruneParams p) {
+  extern __shared__ __align__(16) float smem[];
+  float* red = smem;                                  // 192 floats
+  int* wsum = reinterpret_cast<int*>(smem + 192);     // 64 ints
+  float* row = smem + 256;                            // probabilities when IN_SMEM
+  const int r = blockIdx.x;
+  const int b = r / p.Hq;
+  const bool has_cand = p.cand_pages != nullptr;
+  const int n_seq_pages = p.indptr[b + 1] - p.indptr[b];
+  int n_pages = has_cand ? min(p.cand_npages[r], p.max_k) : n_seq_pages;
+  n_pages = min(n_pages, p.stride / kPage);
+  const int n = n_pages * kPage;  // candidate slots; slots past the sequence end hold -inf
+  const int32_t* cand = has_cand ? p.cand_pages + (size_t)r * p.max_k : nullptr;
+  const float* src = p.scores + (size_t)r * p.stride;
+  if (n == 0) {
+    if (threadIdx.x == 0) {
+      p.out_budget[r] = 0;
+      if (p.out_threshold) {
+        p.out_threshold[2 * r] = 0.f;
+        p.out_threshold[2 * r + 1] = 0.f;
+      }
+    }
+    return;
+  }
+  // pass 1: row maximum (and stage the scores)
+  float m = -INFINITY;
+  {
+    const float4* s4 = reinterpret_cast<const float4*>(src);  // stride and n are multiples of 16
+    float4* r4 = reinterpret_cast<float4*>(row);
+    for (int i = threadIdx.x; i < n / 4; i += THREADS) {
+      const float4 v = s4[i];
+      if (IN_SMEM) r4[i] = v;
+      m = fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+    }
+  }
+  Red3 r1 = block_red3<THREADS>(0.f, 0.f, m, red);
+  m = r1.b;
+  __syncthreads();
+  // pass 2: exponentials and their sum
+  float z = 0.f;
+  if (IN_SMEM) {
+    for (int i = threadIdx.x; i < n; i += THREADS) {
+      const float e = expf(row[i] - m);
+      row[i] = e;
+      z += e;
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += THREADS) z += expf(src[i] - m);
+  }
+  Red3 r2 = block_red3<THREADS>(z, 0.f, 0.f, red + 96);
+  z = r2.s;
+  __syncthreads();
+  if (IN_SMEM) {
+    for (int i = threadIdx.x; i < n; i += THREADS) row[i] = row[i] / z;
+    __syncthreads();
+  }
+  auto prob = [&](int i) -> float { return IN_SMEM ? row[i] : expf(src[i] - m) / z; };
+  // probability of sequence token 0: slot 0 when page 0 is a candidate, else it is not in the row
+  const bool sink_present = has_cand ? (cand[0] == 0) : true;
+  const float x0 = sink_present ? prob(0) : 0.f;
+  const float top_p = p.top_p_arr ? p.top_p_arr[r] : p.top_p_val;
+  float low;
+  if (top_p > 1.f) {
+    low = 0.f;  // no pruning asked for: keep every candidate with non-zero probability
+  } else if (IN_SMEM) {
+    low = topp_search_smem4<THREADS>(row, n / 4, x0, top_p, red, p.status);
+  } else {
+    low = topp_search<THREADS, float>(prob, n, x0, top_p, red, p.status);
+  }
+  __syncthreads();
+  // ordered compaction: 4 consecutive slots per thread per tile
+  int32_t* out = p.out_indices + (size_t)r * p.index_stride;
+  int base = 0;
+  for (int t0 = 0; t0 < n; t0 += THREADS * 4) {
+    const int i0 = t0 + threadIdx.x * 4;
+    int keep[4], cnt = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      keep[k] = (i0 + k < n) && (prob(i0 + k) > low);
+      cnt += keep[k];
+    }
+    int total;
+    int off = base + block_excl_scan<THREADS>(cnt, &total, wsum);
+    if (cnt) {
+      const int page = has_cand ? cand[i0 / kPage] : (i0 / kPage);  // i0 % 4 == 0: one page
+      const int tok0 = page * kPage + (i0 % kPage);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (keep[k]) {
+          if (off < p.index_stride) out[off] = tok0 + k;
+          ++off;
+        }
+      }
+    }
+    base += total;
+  }
+  if (threadIdx.x == 0) {
+    if (base > p.index_stride) {
+      raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+      base = p.index_stride;
+    }
+    p.out_budget[r] = base;
+    if (p.out_threshold) {
+      p.out_threshold[2 * r] = low;
+      p.out_threshold[2 * r + 1] = x0;
+    }
+  }
+}
+
+template <int THREADS>
+static int launch_prune(const PruneParams& p, int rows, int n_max, cudaStream_t st) {
+  if (n_max <= kRowCap) {
+    const size_t smem = (256 + (size_t)n_max) * sizeof(float);
+    auto kern = topp_prune_kernel<THREADS, true>;
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<rows, THREADS, smem, st>>>(p);
+  } else {
+    auto kern = topp_prune_kernel<THREADS, false>;
+    kern<<<rows, THREADS, 256 * sizeof(float), st>>>(p);
+  }
+  TWL_CHECK_LAUNCH();
+  return TWL_OK;
+}
+
+}  // namespace twl
+
+extern "C" int twl_top_p_return_mask_f32(const float* probs, uint8_t* mask,
+                                         const float* top_p_arr, float top_p_val, uint32_t rows,
+                                         uint32_t d, int32_t* status, void* stream) {
+  if (!probs || !mask || rows == 0 || d == 0) return TWL_ERR_BAD_ARG;
+  if (d > 0x7fffffffu) return TWL_ERR_TOO_LARGE;
+  return twl::launch_mask<float>(probs, mask, top_p_arr, top_p_val, rows, d, status,
+                                 reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int twl_top_p_return_mask_f16(const void* probs, int dtype, uint8_t* mask,
+                                         const float* top_p_arr, float top_p_val, uint32_t rows,
+                                         uint32_t d, int32_t* status, void* stream) {
+  if (!probs || !mask || rows == 0 || d == 0) return TWL_ERR_BAD_ARG;
+  if (d > 0x7fffffffu) return TWL_ERR_TOO_LARGE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == TWL_F16)
+    return twl::launch_mask<__half>(static_cast<const __half*>(probs), mask, top_p_arr, top_p_val,
+                                    rows, d, status, st);
+  if (dtype == TWL_BF16)
+    return twl::launch_mask<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(probs), mask,
+                                           top_p_arr, top_p_val, rows, d, status, st);
+  return TWL_ERR_UNSUPPORTED;
+}
+
+extern "C" int twl_topp_prune(const float* scores, int32_t score_stride,
+                              const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                              const int32_t* cand_pages, const int32_t* cand_npages,
+                              int32_t max_k, int32_t batch, int32_t num_q_heads,
+                              const float* top_p_arr, float top_p_val, int32_t* out_indices,
+                              int32_t index_stride, int32_t* out_budget, float* out_threshold,
+                              int32_t* status, void* stream) {
+  using namespace twl;
+  if (!scores || !kv_indptr || !out_indices || !out_budget) return TWL_ERR_BAD_ARG;
+  if (batch <= 0 || num_q_heads <= 0 || score_stride <= 0 || index_stride <= 0)
+    return TWL_ERR_BAD_ARG;
+  if (score_stride % kPage != 0) return TWL_ERR_BAD_ARG;
+  if (cand_pages && (!cand_npages || max_k <= 0)) return TWL_ERR_BAD_ARG;
+  if (!aligned(scores, 16)) return TWL_ERR_MISALIGNED;
+  (void)kv_last_page_len;
+  PruneParams p;
+  p.scores = scores; p.indptr = kv_indptr; p.last_len = kv_last_page_len;
+  p.cand_pages = cand_pages; p.cand_npages = cand_npages; p.top_p_arr = top_p_arr;
+  p.out_indices = out_indices; p.out_budget = out_budget; p.out_threshold = out_threshold;
+  p.status = status; p.stride = score_stride; p.max_k = max_k; p.B = batch; p.Hq = num_q_heads;
+  p.index_stride = index_stride; p.top_p_val = top_p_val;
+  const int rows = batch * num_q_heads;
+  const int n_max = cand_pages ? (int)std::min<int64_t>((int64_t)max_k * kPage, score_stride)
+                               : score_stride;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (n_max <= 8192) return launch_prune<256>(p, rows, n_max, st);
+  if (n_max <= 16384) return launch_prune<512>(p, rows, n_max, st);
+  return launch_prune<1024>(p, rows, n_max, st);
+}

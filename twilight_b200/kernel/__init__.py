@@ -1,0 +1,16 @@
+"""``twilight_b200.kernel``: the operator API (same role and names as ``twilight.kernel`` of the
+reference, twilight/kernel/__init__.py:1)."""
+from .ops import (  # noqa: F401
+    top_p_fp16_return_mask,
+    top_p_fp32_return_mask,
+    quest_select,
+    estimate_int4,
+    topp_prune,
+    sparse_decode_attn,
+    sparse_attn_workspace_bytes,
+    quantize_k_pages,
+    build_page_meta,
+    append_kv,
+    indices_to_mask,
+    batched_sparse_gemv_int4_k,
+)

@@ -1,0 +1,293 @@
+"""Operator API of the Select-then-Prune decode path.
+
+``top_p_fp32_return_mask`` / ``top_p_fp16_return_mask`` keep the names, arguments and result of
+the reference's ``twilight.kernel`` (twilight/kernel/cuda/sampling.py:118-133).  The other
+operators are the index-list forms the decode step is built from.  Every operator launches
+hand-written sm_100a kernels through the C ABI on the current CUDA stream; none of them has a
+PyTorch or CPU fallback.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple, Union
+
+import torch
+
+from .. import _lib
+
+PAGE = 16
+HEAD_DIM = 128
+K4_SLAB_BYTES = 1280
+
+FLAG_ITER_CAP, FLAG_BAD_INDEX, FLAG_WAIT_LIMIT = 1, 2, 4
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float16:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise _lib.TwilightError(f"unsupported dtype {t.dtype}: the kernels take float16 or bfloat16")
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _cuda_contig(t: torch.Tensor, name: str) -> None:
+    # same checks as CHECK_INPUT in csrc/src/pytorch_extension_utils.h:220-233
+    if not t.is_cuda:
+        raise _lib.TwilightError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise _lib.TwilightError(f"{name} must be contiguous")
+
+
+def _q3(q: torch.Tensor) -> torch.Tensor:
+    """Accepts q as [B,H,D] or the reference's [B,H,1,D]."""
+    if q.dim() == 4:
+        if q.shape[2] != 1:
+            raise _lib.TwilightError("decode step only: q_len must be 1")
+        q = q[:, :, 0, :]
+    if q.dim() != 3 or q.shape[-1] != HEAD_DIM:
+        raise _lib.TwilightError(f"q must be [B,H,{HEAD_DIM}]")
+    _cuda_contig(q, "q")
+    return q
+
+
+# ---------------------------------------------------------------------------------------------
+# reference-compatible mask operators
+# ---------------------------------------------------------------------------------------------
+def _top_p_return_mask(probs: torch.Tensor, top_p: Union[torch.Tensor, float], half: bool
+                       ) -> torch.Tensor:
+    _cuda_contig(probs, "probs")
+    if probs.dim() != 4:
+        raise _lib.TwilightError("probs must be a 4D tensor")  # CHECK_DIM(4, probs)
+    lib = _lib.load()
+    b, h, _, d = probs.shape
+    arr, val = (top_p, 0.0) if isinstance(top_p, torch.Tensor) else (None, float(top_p))
+    if arr is not None:
+        arr = arr.to(device=probs.device, dtype=torch.float32).contiguous()
+        if arr.numel() != b * h:
+            raise _lib.TwilightError("top_p tensor must have batch*num_heads elements")
+    with torch.cuda.device(probs.device):
+        mask = torch.zeros_like(probs, dtype=torch.bool)
+        if half:
+            st = lib.twl_top_p_return_mask_f16(probs.data_ptr(), _dtype_code(probs), mask.data_ptr(),
+                                               _p(arr), val, b * h, d, None, _stream(probs.device))
+        else:
+            if probs.dtype != torch.float32:
+                raise _lib.TwilightError("top_p_fp32_return_mask takes float32 probabilities")
+            st = lib.twl_top_p_return_mask_f32(probs.data_ptr(), mask.data_ptr(), _p(arr), val,
+                                               b * h, d, None, _stream(probs.device))
+    _lib.check(st, "top_p_return_mask")
+    return mask
+
+
+def top_p_fp32_return_mask(probs: torch.Tensor, top_p: Union[torch.Tensor, float]) -> torch.Tensor:
+    """probs ``[B,H,1,L]`` fp32 -> bool mask of the tokens the top-p search keeps
+    (twilight/kernel/cuda/sampling.py:127-133, csrc/src/sampling.cu:45-63)."""
+    return _top_p_return_mask(probs, top_p, half=False)
+
+
+def top_p_fp16_return_mask(probs: torch.Tensor, top_p: Union[torch.Tensor, float]) -> torch.Tensor:
+    """fp16/bf16 form (twilight/kernel/cuda/sampling.py:118-124, csrc/src/sampling.cu:22-43)."""
+    return _top_p_return_mask(probs, top_p, half=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# index-list operators
+# ---------------------------------------------------------------------------------------------
+def quest_select(q, kmeta, kv_indptr, kv_indices, token_budget: int, *, max_pages: int,
+                 page_scores=None, cand_pages=None, cand_npages=None, status=None
+                 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Quest selector on stored page metadata (twilight/pyimpl/quest.py:17-122).
+
+    Returns ``(cand_pages[B,H,max_k] int32 ascending, cand_npages[B,H] int32, page_scores)``."""
+    lib = _lib.load()
+    q = _q3(q)
+    b, hq, _ = q.shape
+    n_total, hkv = kmeta.shape[0], kmeta.shape[1]
+    max_k = max(1, token_budget // PAGE) + (1 if token_budget % PAGE else 0)
+    max_k = min(max_k, max_pages)
+    dev = q.device
+    if page_scores is None:
+        page_scores = torch.empty(b, hq, max_pages, dtype=torch.float32, device=dev)
+    if cand_pages is None:
+        cand_pages = torch.empty(b, hq, max_k, dtype=torch.int32, device=dev)
+    if cand_npages is None:
+        cand_npages = torch.empty(b, hq, dtype=torch.int32, device=dev)
+    s = _stream(dev)
+    _lib.check(lib.twl_quest_page_scores(q.data_ptr(), _dtype_code(q), kmeta.data_ptr(),
+                                         kv_indptr.data_ptr(), kv_indices.data_ptr(), b, hq, hkv,
+                                         n_total, page_scores.data_ptr(), max_pages, _p(status), s),
+               "quest_page_scores")
+    _lib.check(lib.twl_quest_topk_pages(page_scores.data_ptr(), max_pages, kv_indptr.data_ptr(), b,
+                                        hq, token_budget, cand_pages.data_ptr(),
+                                        cand_npages.data_ptr(), cand_pages.shape[-1], s),
+               "quest_topk_pages")
+    return cand_pages, cand_npages, page_scores
+
+
+def estimate_int4(q, k4_pages, kv_indptr, kv_indices, kv_last_page_len, *, max_pages: int,
+                  cand_pages=None, cand_npages=None, sm_scale: Optional[float] = None,
+                  scores=None, variant: int = 0, status=None) -> torch.Tensor:
+    """INT4 K-cache estimator (twilight/pyimpl/attention.py:247-255): fp32 scores
+    ``[B,H,stride]``; slot s of a row is token ``cand_pages[s//16]*16+s%16`` (or token s when
+    no candidate list is given)."""
+    lib = _lib.load()
+    q = _q3(q)
+    b, hq, _ = q.shape
+    n_total, hkv = k4_pages.shape[0], k4_pages.shape[1]
+    max_k = 0 if cand_pages is None else cand_pages.shape[-1]
+    stride = (max_k if cand_pages is not None else max_pages) * PAGE
+    if scores is None:
+        scores = torch.empty(b, hq, stride, dtype=torch.float32, device=q.device)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(HEAD_DIM)
+    _lib.check(lib.twl_estimate_int4(q.data_ptr(), _dtype_code(q), k4_pages.data_ptr(),
+                                     kv_indptr.data_ptr(), kv_indices.data_ptr(),
+                                     kv_last_page_len.data_ptr(), _p(cand_pages), _p(cand_npages),
+                                     max_k, b, hq, hkv, n_total, sm_scale, scores.data_ptr(),
+                                     scores.shape[-1], variant, _p(status), _stream(q.device)),
+               "estimate_int4")
+    return scores
+
+
+def topp_prune(scores, kv_indptr, kv_last_page_len, top_p: Union[torch.Tensor, float], *,
+               cand_pages=None, cand_npages=None, indices=None, budget=None, threshold=None,
+               status=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """fp32 softmax + top-p search + compaction (twilight/pyimpl/top_p.py:10-15 and
+    attention.py:280-285).  Returns ``(indices[B,H,stride] int32, budget[B,H] int32)``; the first
+    ``budget`` entries of a row are the kept token positions in ascending order."""
+    lib = _lib.load()
+    _cuda_contig(scores, "scores")
+    b, hq, stride = scores.shape
+    dev = scores.device
+    if indices is None:
+        indices = torch.empty(b, hq, stride, dtype=torch.int32, device=dev)
+    if budget is None:
+        budget = torch.empty(b, hq, dtype=torch.int32, device=dev)
+    arr, val = (top_p, 0.0) if isinstance(top_p, torch.Tensor) else (None, float(top_p))
+    if arr is not None:
+        arr = arr.to(device=dev, dtype=torch.float32).contiguous()
+    max_k = 0 if cand_pages is None else cand_pages.shape[-1]
+    _lib.check(lib.twl_topp_prune(scores.data_ptr(), stride, kv_indptr.data_ptr(),
+                                  kv_last_page_len.data_ptr(), _p(cand_pages), _p(cand_npages),
+                                  max_k, b, hq, _p(arr), val, indices.data_ptr(),
+                                  indices.shape[-1], budget.data_ptr(), _p(threshold), _p(status),
+                                  _stream(dev)), "topp_prune")
+    return indices, budget
+
+
+def sparse_attn_workspace_bytes(batch: int, num_q_heads: int, index_stride: int, chunk: int = 256
+                                ) -> int:
+    return int(_lib.load().twl_sparse_attn_workspace_bytes(batch, num_q_heads, index_stride, chunk))
+
+
+def sparse_decode_attn(q, k_pages, v_pages, kv_indptr, kv_indices, indices, budget, *,
+                       sm_scale: Optional[float] = None, out=None, workspace=None,
+                       chunk: int = 256, status=None) -> torch.Tensor:
+    """Attention of each (batch, query head) over its kept tokens
+    (twilight/pyimpl/attention.py:188-190, :298-306).  Returns ``[B,H,D]`` in q's dtype.
+    ``workspace``: zero-initialised uint8 tensor of ``sparse_attn_workspace_bytes`` bytes."""
+    lib = _lib.load()
+    q = _q3(q)
+    b, hq, _ = q.shape
+    n_total, hkv = k_pages.shape[0], k_pages.shape[1]
+    stride = indices.shape[-1]
+    if out is None:
+        out = torch.empty(b, hq, HEAD_DIM, dtype=q.dtype, device=q.device)
+    if workspace is None:
+        workspace = torch.zeros(sparse_attn_workspace_bytes(b, hq, stride, chunk), dtype=torch.uint8,
+                                device=q.device)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(HEAD_DIM)
+    _lib.check(lib.twl_sparse_decode_attn(q.data_ptr(), _dtype_code(q), k_pages.data_ptr(),
+                                          v_pages.data_ptr(), kv_indptr.data_ptr(),
+                                          kv_indices.data_ptr(), indices.data_ptr(), stride,
+                                          budget.data_ptr(), b, hq, hkv, n_total, sm_scale,
+                                          out.data_ptr(), workspace.data_ptr(), workspace.numel(),
+                                          chunk, _p(status), _stream(q.device)),
+               "sparse_decode_attn")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# cache-append side
+# ---------------------------------------------------------------------------------------------
+def quantize_k_pages(k_pages: torch.Tensor, k4_pages: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """K pages ``[P,Hkv,16,128]`` -> INT4 slabs ``[P,Hkv,1280]`` uint8, group 32
+    (twilight/pyimpl/quantize.py:4-13 per group, arithmetic in the cache dtype)."""
+    lib = _lib.load()
+    _cuda_contig(k_pages, "k_pages")
+    p, hkv = k_pages.shape[0], k_pages.shape[1]
+    if k4_pages is None:
+        k4_pages = torch.empty(p, hkv, K4_SLAB_BYTES, dtype=torch.uint8, device=k_pages.device)
+    _lib.check(lib.twl_quantize_k_pages(k_pages.data_ptr(), _dtype_code(k_pages),
+                                        k4_pages.data_ptr(), p * hkv, _stream(k_pages.device)),
+               "quantize_k_pages")
+    return k4_pages
+
+
+def build_page_meta(k_pages, kv_indptr, kv_indices, kv_last_page_len, *, max_pages: int,
+                    kmeta: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Channel-wise (min,max) of every page ``[P,Hkv,2,128]`` (stored form of the chunk maxima of
+    twilight/pyimpl/quest.py:39-74)."""
+    lib = _lib.load()
+    _cuda_contig(k_pages, "k_pages")
+    p, hkv = k_pages.shape[0], k_pages.shape[1]
+    b = kv_indptr.numel() - 1
+    if kmeta is None:
+        kmeta = torch.zeros(p, hkv, 2, HEAD_DIM, dtype=k_pages.dtype, device=k_pages.device)
+    _lib.check(lib.twl_build_page_meta(k_pages.data_ptr(), _dtype_code(k_pages), kmeta.data_ptr(),
+                                       kv_indptr.data_ptr(), kv_indices.data_ptr(),
+                                       kv_last_page_len.data_ptr(), b, hkv, p, max_pages,
+                                       _stream(k_pages.device)), "build_page_meta")
+    return kmeta
+
+
+def append_kv(new_k, new_v, k_pages, v_pages, k4_pages, kmeta, kv_indptr, kv_indices,
+              kv_last_page_len, status=None) -> None:
+    """Writes one token per sequence (``new_k/new_v [B,Hkv,128]``) at the last position the page
+    table describes, with its INT4 codes and the page metadata update."""
+    lib = _lib.load()
+    _cuda_contig(new_k, "new_k")
+    _cuda_contig(new_v, "new_v")
+    b, hkv, _ = new_k.shape
+    _lib.check(lib.twl_append_kv(new_k.data_ptr(), new_v.data_ptr(), _dtype_code(new_k),
+                                 k_pages.data_ptr(), v_pages.data_ptr(), _p(k4_pages), _p(kmeta),
+                                 kv_indptr.data_ptr(), kv_indices.data_ptr(),
+                                 kv_last_page_len.data_ptr(), b, hkv, k_pages.shape[0], _p(status),
+                                 _stream(new_k.device)), "append_kv")
+
+
+def indices_to_mask(indices, budget, seq_len: int) -> torch.Tensor:
+    """Index lists -> the reference's mask layout ``bool[B,H,1,L]`` (attention.py:199-281)."""
+    lib = _lib.load()
+    b, hq, stride = indices.shape
+    mask = torch.zeros(b, hq, 1, seq_len, dtype=torch.bool, device=indices.device)
+    _lib.check(lib.twl_indices_to_mask(indices.data_ptr(), stride, budget.data_ptr(), b * hq,
+                                       mask.data_ptr(), seq_len, _stream(indices.device)),
+               "indices_to_mask")
+    return mask
+
+
+def batched_sparse_gemv_int4_k(q, o, k_cache_int4, quant_scales, quant_zeros, kv_page_indices,
+                               kv_page_indptr, kv_last_page_len):
+    """Same name and argument order as the absent ``ftka.cuda_ops.gemv`` op called at
+    benchmark/efficiency/bench_gemv.py:445-454: raw ``q.k`` (no 1/sqrt(D)) of every token of
+    every sequence written into ``o [B,H,L]``.  Differences, all forced by the group-32 cache:
+    ``k_cache_int4`` is the slab tensor ``[P,Hkv,1280]`` that already carries scale and minimum,
+    so ``quant_scales``/``quant_zeros`` must be ``None``; page size is 16; ``o`` is fp32 and its
+    last dimension a multiple of 16."""
+    if quant_scales is not None or quant_zeros is not None:
+        raise _lib.TwilightError("scale/min live inside the INT4 slabs; pass None for both")
+    if o.dtype != torch.float32 or o.shape[-1] % PAGE:
+        raise _lib.TwilightError("o must be float32 with a last dimension that is a multiple of 16")
+    estimate_int4(q, k_cache_int4, kv_page_indptr, kv_page_indices, kv_last_page_len,
+                  max_pages=o.shape[-1] // PAGE, sm_scale=1.0, scores=o)
+    return o
