@@ -4,19 +4,23 @@
 // kept tokens) and :298-306 (masked fp32 softmax, P.V).  The reference computes the dense
 // [L] row and masks it; here a row's cost is its budget.
 //
-// Split-KV: block (c, row) handles indices [c*chunk, (c+1)*chunk) of one (batch, query head)
-// row.  A warp takes 32 indices at a time: each lane resolves one token to its K/V row
+// Split-KV: the indices of one (batch, query head) row are cut into chunks of `chunk`; up to
+// kMaxSplits blocks share a row, block x taking chunks x, x+splits, ... and carrying one running
+// (max, sum, acc) across them.  A warp takes 32 indices at a time: each lane resolves one token to its K/V row
 // through the page table, then the warp walks the 32 rows four at a time, every lane owning
 // 4 of the 128 channels (one 8-byte load per K row and per V row), with an online softmax
 // (running max, sum, 4 accumulators per lane).  Warps merge through shared memory; blocks of
 // a row merge through the caller's workspace, and the block that arrives last (an atomic
 // ticket, nobody waits) writes the output.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace twl {
 
 constexpr int kAttThreads = 128;
 constexpr int kAttWarps = kAttThreads / 32;
+constexpr int kMaxSplits = 8;        // blocks per row
 constexpr float kNegBig = -3.0e38f;  // finite stand-in for -inf so that exp(m_old-m_new) is defined
 
 struct AttParams {
@@ -48,12 +52,13 @@ sparse_decode_attn_kernel(const AttParams p) {
   const int kvh = h / (p.Hq / p.Hkv);
   const int budget = min(p.budget[row], p.index_stride);
   const int n_chunks = (budget + p.chunk - 1) / p.chunk;
+  const int n_parts = min(n_chunks, (int)gridDim.x);  // blocks of this row that have work
   T* out = reinterpret_cast<T*>(p.out) + (size_t)row * kD;
   if (budget <= 0) {
     if (c == 0) out[threadIdx.x] = Elem<T>::from_f(0.f);
     return;
   }
-  if (c >= n_chunks) return;
+  if (c >= n_parts) return;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int page_base = p.indptr[b];
@@ -72,7 +77,8 @@ sparse_decode_attn_kernel(const AttParams p) {
   }
 
   float m = kNegBig, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-  const int begin = c * p.chunk, end = min(budget, begin + p.chunk);
+  for (int cc = c; cc < n_chunks; cc += gridDim.x) {
+  const int begin = cc * p.chunk, end = min(budget, begin + p.chunk);
   for (int t0 = begin + warp * 32; t0 < end; t0 += kAttWarps * 32) {
     // each lane resolves one token -> row number inside the K/V page arrays (-1 = skip)
     long long ro = -1;
@@ -136,6 +142,7 @@ sparse_decode_attn_kernel(const AttParams p) {
       m = m_new;
     }
   }
+  }
 
   // merge the warps of this block
   if (lane == 0) {
@@ -156,7 +163,7 @@ sparse_decode_attn_kernel(const AttParams p) {
     bl += f * sm_l[w];
     bo += f * sm_o[w][d];
   }
-  if (n_chunks == 1) {
+  if (n_parts == 1) {
     out[d] = Elem<T>::from_f(bl > 0.f ? bo / bl : 0.f);
     return;
   }
@@ -171,13 +178,13 @@ sparse_decode_attn_kernel(const AttParams p) {
   __syncthreads();
   if (threadIdx.x == 0) sm_ticket = atomicAdd(&p.counters[row], 1);
   __syncthreads();
-  if (sm_ticket != n_chunks - 1) return;
+  if (sm_ticket != n_parts - 1) return;
   __threadfence();
   float gm = kNegBig;
-  for (int cc = 0; cc < n_chunks; ++cc)
+  for (int cc = 0; cc < n_parts; ++cc)
     gm = fmaxf(gm, __ldcg(&p.part_ml[((size_t)row * p.max_chunks + cc) * 2]));
   float gl = 0.f, go = 0.f;
-  for (int cc = 0; cc < n_chunks; ++cc) {
+  for (int cc = 0; cc < n_parts; ++cc) {
     const size_t s2 = (size_t)row * p.max_chunks + cc;
     const float f = __expf(__ldcg(&p.part_ml[s2 * 2]) - gm);
     gl += f * __ldcg(&p.part_ml[s2 * 2 + 1]);
@@ -195,7 +202,8 @@ extern "C" size_t twl_sparse_attn_workspace_bytes(int32_t batch, int32_t num_q_h
                                                   int32_t index_stride, int32_t chunk) {
   if (batch <= 0 || num_q_heads <= 0 || index_stride <= 0 || chunk <= 0) return 0;
   const size_t rows = (size_t)batch * num_q_heads;
-  const size_t max_chunks = ((size_t)index_stride + chunk - 1) / chunk;
+  const size_t max_chunks =
+      std::min<size_t>(((size_t)index_stride + chunk - 1) / chunk, twl::kMaxSplits);
   size_t bytes = twl::align_up(rows * sizeof(int32_t), 256);
   bytes += twl::align_up(rows * max_chunks * 2 * sizeof(float), 256);
   bytes += rows * max_chunks * twl::kD * sizeof(float);
@@ -225,7 +233,7 @@ extern "C" int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pa
   if (!aligned(workspace, 16)) return TWL_ERR_MISALIGNED;
   const size_t rows = (size_t)batch * num_q_heads;
   if (rows > 65535) return TWL_ERR_TOO_LARGE;
-  const size_t max_chunks = ((size_t)index_stride + chunk - 1) / chunk;
+  const size_t max_chunks = std::min<size_t>(((size_t)index_stride + chunk - 1) / chunk, kMaxSplits);
   AttParams p;
   p.q = q; p.k = k_pages; p.v = v_pages; p.indptr = kv_indptr; p.indices = kv_indices;
   p.idx = indices; p.budget = budget; p.out = out; p.status = status;

@@ -17,8 +17,8 @@ namespace twl {
 
 constexpr int kEstThreads = 256;
 constexpr int kEstWarps = kEstThreads / 32;
-constexpr int kPagesPerBlock = 32;  // 512 tokens, 40 KiB of INT4 cache per block
-constexpr int kUnroll = 4;
+constexpr int kPagesPerBlock = 64;  // 1024 tokens, 80 KiB of INT4 cache per block
+constexpr int kUnroll = 8;
 
 enum { VAR_F32 = 1, VAR_H2 = 2, VAR_DP4A = 3 };
 
@@ -185,9 +185,18 @@ __device__ __forceinline__ void load_q_group(const T* q, float* qf) {
 }
 
 // G = query heads that share the block's pages (1 when a candidate list is given).
+//
+// Prologue: one thread per page resolves candidate slot -> sequence page -> physical page and
+// parks it in shared memory, so the streaming loop has no dependent index loads; 4*G threads
+// convert q once (one per head and 32-channel group) and every thread copies the registers of
+// its group from shared memory.
 template <typename T, int G, int VARIANT>
 __global__ void __launch_bounds__(kEstThreads)
 estimate_int4_kernel(const EstParams p) {
+  __shared__ int sm_phys[kPagesPerBlock];   // physical page id, -1 = skip
+  __shared__ int sm_ntok[kPagesPerBlock];   // valid tokens of the page
+  __shared__ QRegs<VARIANT> sm_q[G][4];
+
   const int row = blockIdx.y;
   const bool has_cand = p.cand_pages != nullptr;
   int b, kvh, h0;
@@ -210,52 +219,50 @@ estimate_int4_kernel(const EstParams p) {
   const int first = blockIdx.x * kPagesPerBlock;
   if (first >= n_pages) return;
   const int n_here = min(kPagesPerBlock, n_pages - first);
-  const int last_len = p.last_len[b];
 
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int grp = lane & 3, tok_in_step = lane >> 2;
-
-  QRegs<VARIANT> qr[G];
-  {
-    float qf[32];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      load_q_group<T>(reinterpret_cast<const T*>(p.q) + ((size_t)(b * p.Hq + h0 + g)) * kD + grp * kGroup, qf);
-      qr[g].init(qf);
+  const int tid = threadIdx.x;
+  if (tid < n_here) {
+    const int32_t* cand = has_cand ? p.cand_pages + (size_t)(b * p.Hq + h0) * p.max_k : nullptr;
+    const int seq_page = has_cand ? cand[first + tid] : first + tid;
+    int phys = -1;
+    if (seq_page >= 0 && seq_page < n_seq_pages) {
+      phys = p.indices[page_base + seq_page];
+      if (phys < 0 || phys >= p.num_pages_total) phys = -1;
     }
+    if (phys < 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+    sm_phys[tid] = phys;
+    sm_ntok[tid] = (seq_page == n_seq_pages - 1) ? p.last_len[b] : kPage;
+  } else if (tid >= kEstThreads - 4 * G) {
+    const int j = tid - (kEstThreads - 4 * G);
+    const int g = j >> 2, grp_j = j & 3;
+    float qf[32];
+    load_q_group<T>(reinterpret_cast<const T*>(p.q) + ((size_t)(b * p.Hq + h0 + g)) * kD + grp_j * kGroup, qf);
+    sm_q[g][grp_j].init(qf);
   }
+  __syncthreads();
 
-  const int32_t* cand = has_cand ? p.cand_pages + (size_t)(b * p.Hq + h0) * p.max_k : nullptr;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int grp = lane & 3, tok_in_step = lane >> 2;
+  QRegs<VARIANT> qr[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) qr[g] = sm_q[g][grp];
+
   const int n_steps = n_here * 2;  // half a page per warp step
   for (int s0 = warp; s0 < n_steps; s0 += kEstWarps * kUnroll) {
     uint4 w[kUnroll];
     uint32_t sz[kUnroll];
-    int slot[kUnroll];
-    bool live[kUnroll], valid[kUnroll];
+    bool valid[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int s = s0 + u * kEstWarps;
-      live[u] = s < n_steps;
       valid[u] = false;
       w[u] = make_uint4(0, 0, 0, 0);
       sz[u] = 0;
-      slot[u] = 0;
-      if (live[u]) {
-        const int lp = first + (s >> 1);
-        const int half = s & 1;
-        const int seq_page = has_cand ? cand[lp] : lp;
-        slot[u] = lp * kPage + half * 8 + tok_in_step;
-        bool ok = seq_page >= 0 && seq_page < n_seq_pages;
-        int phys = 0;
-        if (ok) {
-          phys = p.indices[page_base + seq_page];
-          ok = phys >= 0 && phys < p.num_pages_total;
-        }
-        if (!ok) {
-          raise_flag(p.status, TWL_FLAG_BAD_INDEX);
-        } else {
-          const int t = half * 8 + tok_in_step;
-          valid[u] = (seq_page != n_seq_pages - 1) || (t < last_len);
+      if (s < n_steps) {
+        const int pg = s >> 1, half = s & 1;
+        const int phys = sm_phys[pg];
+        if (phys >= 0) {
+          valid[u] = (half * 8 + tok_in_step) < sm_ntok[pg];
           const uint8_t* slab = p.k4 + ((size_t)phys * p.Hkv + kvh) * kSlab;
           w[u] = ldg_stream_u4(slab + half * 512 + lane * 16);
           sz[u] = ldg_stream_u32(slab + kSlabCodes + half * 128 + lane * 4);
@@ -264,7 +271,9 @@ estimate_int4_kernel(const EstParams p) {
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      if (!live[u]) continue;  // warp-uniform
+      const int s = s0 + u * kEstWarps;
+      if (s >= n_steps) break;  // warp-uniform
+      const int slot = (first + (s >> 1)) * kPage + (s & 1) * 8 + tok_in_step;
       const float2 szf = __half22float2(*reinterpret_cast<const __half2*>(&sz[u]));
       float part[G];
 #pragma unroll
@@ -278,31 +287,234 @@ estimate_int4_kernel(const EstParams p) {
       for (int g = 0; g < G; ++g) {
         if ((g & 3) == grp) {
           const float v = valid[u] ? part[g] * p.sm_scale : -INFINITY;
-          p.scores[(size_t)(b * p.Hq + h0 + g) * p.stride + slot[u]] = v;
+          p.scores[(size_t)(b * p.Hq + h0 + g) * p.stride + slot] = v;
         }
       }
     }
   }
 }
 
+// ---- bulk-async-copy (TMA) staged variant -------------------------------------------------------
+// One extra warp is the producer: its first lane issues one cp.async.bulk of 1280 bytes per page
+// (a whole (page, kv-head) slab is contiguous and 16-byte aligned) into a ring of shared-memory
+// stages, each guarded by a "full" mbarrier (transaction bytes) and an "empty" mbarrier (one
+// arrival per consumer warp).  Bytes in flight are set by the ring (kStages * kStagePages *
+// 1280 B per block), not by registers.  Every wait is bounded: when it runs out the block raises
+// TWL_FLAG_WAIT_LIMIT, stops consuming, drains the copies it still has in flight (bounded again)
+// and returns.
+constexpr int kStagePages = 8;                       // 10 KiB per stage
+constexpr int kStages = 4;                           // 40 KiB ring per block
+constexpr int kTmaPagesPerBlock = 128;               // 160 KiB of INT4 cache per block
+constexpr int kTmaThreads = kEstThreads + 32;        // 8 consumer warps + 1 producer warp
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+// Bounded wait for the phase with the given parity to complete; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
 template <typename T, int G, int VARIANT>
-static int launch_one(const EstParams& p, int rows, int max_row_pages, cudaStream_t st) {
+__global__ void __launch_bounds__(kTmaThreads)
+estimate_int4_tma_kernel(const EstParams p) {
+  extern __shared__ __align__(128) uint8_t sm_ring[];  // kStages * kStagePages * kSlab bytes
+  __shared__ __align__(8) uint64_t sm_full[kStages];
+  __shared__ __align__(8) uint64_t sm_empty[kStages];
+  __shared__ int sm_phys[kTmaPagesPerBlock];
+  __shared__ int sm_ntok[kTmaPagesPerBlock];
+  __shared__ QRegs<VARIANT> sm_q[G][4];
+
+  const int row = blockIdx.y;
+  const bool has_cand = p.cand_pages != nullptr;
+  int b, kvh, h0;
+  if (has_cand) {
+    b = row / p.Hq;
+    h0 = row % p.Hq;
+    kvh = h0 / (p.Hq / p.Hkv);
+  } else {
+    b = row / p.Hkv;
+    kvh = row % p.Hkv;
+    h0 = kvh * G;
+  }
+  const int page_base = p.indptr[b];
+  const int n_seq_pages = p.indptr[b + 1] - page_base;
+  int n_pages = has_cand ? min(p.cand_npages[b * p.Hq + h0], p.max_k) : n_seq_pages;
+  if (n_pages > p.stride / kPage) {
+    n_pages = p.stride / kPage;
+    if (threadIdx.x == 0 && blockIdx.x == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+  }
+  const int first = blockIdx.x * kTmaPagesPerBlock;
+  if (first >= n_pages) return;
+  const int n_here = min(kTmaPagesPerBlock, n_pages - first);
+  const int n_stages_total = (n_here + kStagePages - 1) / kStagePages;
+
+  const int tid = threadIdx.x;
+  if (tid < n_here) {
+    const int32_t* cand = has_cand ? p.cand_pages + (size_t)(b * p.Hq + h0) * p.max_k : nullptr;
+    const int seq_page = has_cand ? cand[first + tid] : first + tid;
+    int phys = -1;
+    if (seq_page >= 0 && seq_page < n_seq_pages) {
+      phys = p.indices[page_base + seq_page];
+      if (phys < 0 || phys >= p.num_pages_total) phys = -1;
+    }
+    if (phys < 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+    sm_phys[tid] = phys;
+    sm_ntok[tid] = (seq_page == n_seq_pages - 1) ? p.last_len[b] : kPage;
+  } else if (tid >= kEstThreads - 4 * G && tid < kEstThreads) {
+    const int j = tid - (kEstThreads - 4 * G);
+    const int g = j >> 2, grp_j = j & 3;
+    float qf[32];
+    load_q_group<T>(reinterpret_cast<const T*>(p.q) + ((size_t)(b * p.Hq + h0 + g)) * kD + grp_j * kGroup, qf);
+    sm_q[g][grp_j].init(qf);
+  }
+  if (tid == kEstThreads) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&sm_full[s], 1);
+      mbar_init(&sm_empty[s], kEstWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int lane = tid & 31, warp = tid >> 5;
+  if (warp == kEstWarps) {
+    // ---- producer ----
+    if (lane == 0) {
+      int issued = 0;
+      bool ok = true;
+      for (int st = 0; st < n_stages_total && ok; ++st) {
+        const int slot = st % kStages;
+        if (st >= kStages) ok = mbar_wait(&sm_empty[slot], ((st / kStages) - 1) & 1);
+        if (!ok) break;
+        const int pg0 = st * kStagePages, pg1 = min(n_here, pg0 + kStagePages);
+        uint32_t bytes = 0;
+        for (int pg = pg0; pg < pg1; ++pg) bytes += sm_phys[pg] >= 0 ? kSlab : 0;
+        mbar_arrive_expect_tx(&sm_full[slot], bytes);
+        for (int pg = pg0; pg < pg1; ++pg) {
+          const int phys = sm_phys[pg];
+          if (phys >= 0)
+            bulk_copy_g2s(sm_ring + ((size_t)slot * kStagePages + (pg - pg0)) * kSlab,
+                          p.k4 + ((size_t)phys * p.Hkv + kvh) * kSlab, kSlab, &sm_full[slot]);
+        }
+        issued = st + 1;
+      }
+      if (!ok) {
+        raise_flag(p.status, TWL_FLAG_WAIT_LIMIT);
+        // drain: every stage issued so far completes its transaction count sooner or later
+        for (int st = max(0, issued - kStages); st < issued; ++st)
+          mbar_wait(&sm_full[st % kStages], (st / kStages) & 1);
+      }
+    }
+    return;
+  }
+
+  // ---- consumers ----
+  const int grp = lane & 3, tok_in_step = lane >> 2;
+  QRegs<VARIANT> qr[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) qr[g] = sm_q[g][grp];
+
+  for (int st = 0; st < n_stages_total; ++st) {
+    const int slot = st % kStages;
+    if (!mbar_wait(&sm_full[slot], (st / kStages) & 1)) {
+      if (lane == 0) raise_flag(p.status, TWL_FLAG_WAIT_LIMIT);
+      return;  // the producer drains what it issued
+    }
+    const int pg0 = st * kStagePages;
+    const int n_steps = (min(n_here, pg0 + kStagePages) - pg0) * 2;
+    const uint8_t* stage = sm_ring + (size_t)slot * kStagePages * kSlab;
+    for (int s = warp; s < n_steps; s += kEstWarps) {
+      const int pgl = s >> 1, half = s & 1;
+      const int pg = pg0 + pgl;
+      const bool present = sm_phys[pg] >= 0;
+      const bool valid = present && (half * 8 + tok_in_step) < sm_ntok[pg];
+      uint4 w = make_uint4(0, 0, 0, 0);
+      uint32_t sz = 0;
+      if (present) {
+        const uint8_t* slab = stage + pgl * kSlab;
+        w = *reinterpret_cast<const uint4*>(slab + half * 512 + lane * 16);
+        sz = *reinterpret_cast<const uint32_t*>(slab + kSlabCodes + half * 128 + lane * 4);
+      }
+      const int slot_out = (first + pg) * kPage + half * 8 + tok_in_step;
+      const float2 szf = __half22float2(*reinterpret_cast<const __half2*>(&sz));
+      float part[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        part[g] = fmaf(szf.x, qr[g].dot(w), szf.y * qr[g].qsum);
+        part[g] += __shfl_xor_sync(0xffffffffu, part[g], 1);
+        part[g] += __shfl_xor_sync(0xffffffffu, part[g], 2);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        if ((g & 3) == grp) {
+          const float v = valid ? part[g] * p.sm_scale : -INFINITY;
+          p.scores[(size_t)(b * p.Hq + h0 + g) * p.stride + slot_out] = v;
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm_empty[slot]);
+  }
+}
+
+template <typename T, int G, int VARIANT>
+static int launch_one(const EstParams& p, int rows, int max_row_pages, bool ldg, cudaStream_t st) {
   if (rows > 65535) return TWL_ERR_TOO_LARGE;
-  dim3 grid((max_row_pages + kPagesPerBlock - 1) / kPagesPerBlock, rows);
-  estimate_int4_kernel<T, G, VARIANT><<<grid, kEstThreads, 0, st>>>(p);
+  if (ldg) {
+    dim3 grid((max_row_pages + kPagesPerBlock - 1) / kPagesPerBlock, rows);
+    estimate_int4_kernel<T, G, VARIANT><<<grid, kEstThreads, 0, st>>>(p);
+  } else {
+    constexpr int kRingBytes = kStages * kStagePages * kSlab;
+    auto kern = estimate_int4_tma_kernel<T, G, VARIANT>;
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes));
+    dim3 grid((max_row_pages + kTmaPagesPerBlock - 1) / kTmaPagesPerBlock, rows);
+    kern<<<grid, kTmaThreads, kRingBytes, st>>>(p);
+  }
   TWL_CHECK_LAUNCH();
   return TWL_OK;
 }
 
 template <typename T, int VARIANT>
-static int launch_variant(const EstParams& p, bool has_cand, int max_row_pages, cudaStream_t st) {
-  if (has_cand) return launch_one<T, 1, VARIANT>(p, p.B * p.Hq, max_row_pages, st);
+static int launch_variant(const EstParams& p, bool has_cand, int max_row_pages, bool ldg,
+                          cudaStream_t st) {
+  if (has_cand) return launch_one<T, 1, VARIANT>(p, p.B * p.Hq, max_row_pages, ldg, st);
   const int g = p.Hq / p.Hkv;
   switch (g) {
-    case 1: return launch_one<T, 1, VARIANT>(p, p.B * p.Hkv, max_row_pages, st);
-    case 2: return launch_one<T, 2, VARIANT>(p, p.B * p.Hkv, max_row_pages, st);
-    case 4: return launch_one<T, 4, VARIANT>(p, p.B * p.Hkv, max_row_pages, st);
-    case 8: return launch_one<T, 8, VARIANT>(p, p.B * p.Hkv, max_row_pages, st);
+    case 1: return launch_one<T, 1, VARIANT>(p, p.B * p.Hkv, max_row_pages, ldg, st);
+    case 2: return launch_one<T, 2, VARIANT>(p, p.B * p.Hkv, max_row_pages, ldg, st);
+    case 4: return launch_one<T, 4, VARIANT>(p, p.B * p.Hkv, max_row_pages, ldg, st);
+    case 8: return launch_one<T, 8, VARIANT>(p, p.B * p.Hkv, max_row_pages, ldg, st);
     default: return TWL_ERR_UNSUPPORTED;
   }
 }
@@ -310,11 +522,12 @@ static int launch_variant(const EstParams& p, bool has_cand, int max_row_pages, 
 template <typename T>
 static int launch_dtype(const EstParams& p, bool has_cand, int max_row_pages, int variant,
                         cudaStream_t st) {
-  switch (variant) {
-    case VAR_F32: return launch_variant<T, VAR_F32>(p, has_cand, max_row_pages, st);
-    case VAR_H2: return launch_variant<T, VAR_H2>(p, has_cand, max_row_pages, st);
+  const bool ldg = (variant & 16) != 0;  // +16: direct global loads instead of the staged ring
+  switch (variant & 15) {
+    case VAR_F32: return launch_variant<T, VAR_F32>(p, has_cand, max_row_pages, ldg, st);
+    case VAR_H2: return launch_variant<T, VAR_H2>(p, has_cand, max_row_pages, ldg, st);
     case 0:
-    case VAR_DP4A: return launch_variant<T, VAR_DP4A>(p, has_cand, max_row_pages, st);
+    case VAR_DP4A: return launch_variant<T, VAR_DP4A>(p, has_cand, max_row_pages, ldg, st);
     default: return TWL_ERR_BAD_ARG;
   }
 }
