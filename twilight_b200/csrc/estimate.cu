@@ -11,6 +11,8 @@
 // of a token are combined with two shuffles.  q lives in registers, already converted to
 // the form the arithmetic variant wants; sum_d q_d*(c_d*s+m) = s*sum(q_d c_d) + m*sum(q_d)
 // so the inner loop touches only codes.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace twl {
@@ -32,7 +34,7 @@ struct EstParams {
   const int32_t* cand_npages;
   float* scores;
   int32_t* status;
-  int max_k, B, Hq, Hkv, num_pages_total, stride;
+  int max_k, B, Hq, Hkv, num_pages_total, stride, pages_per_block, debug;
   float sm_scale;
 };
 
@@ -115,9 +117,22 @@ struct QRegs<VAR_H2> {
   }
 };
 
+__device__ __forceinline__ int dp4a_u8_s8(uint32_t a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t dp4a_u8_u8(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
 template <>
 struct QRegs<VAR_DP4A> {
-  // q_d ~= (256*qh_d + ql_d) * inv, qh signed byte, ql unsigned byte
+  // q_d ~= (256*qh_d + ql_d) * inv with |256*qh+ql| < 2^13, qh a signed byte, ql an unsigned
+  // byte.  Even channels sit in the low nibbles, odd channels in the high nibbles; the odd ones
+  // are used unshifted (16*code), which the final >>4 undoes exactly.
   uint32_t qh_even[4], qh_odd[4], ql_even[4], ql_odd[4];
   float inv, qsum;
   __device__ __forceinline__ void init(const float* qf) {
@@ -128,7 +143,7 @@ struct QRegs<VAR_DP4A> {
       qsum += qf[i];
       amax = fmaxf(amax, fabsf(qf[i]));
     }
-    int e = (amax > 0.f) ? (14 - ilogbf(amax)) : 0;  // amax * 2^e in [2^14, 2^15)
+    int e = (amax > 0.f) ? (12 - ilogbf(amax)) : 0;  // amax * 2^e in [2^12, 2^13)
     e = max(-60, min(60, e));
     const float f = ldexpf(1.f, e);
     inv = ldexpf(1.f, -e);
@@ -150,20 +165,25 @@ struct QRegs<VAR_DP4A> {
       ql_odd[j] = lo;
     }
   }
-  __device__ __forceinline__ float dot(const uint4& w) const {
+  // integer sum_d code_d * q_int_d  (|result| < 2^22)
+  __device__ __forceinline__ int idot(const uint4& w) const {
     const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
-    int acc_h = 0;
-    unsigned acc_l = 0;
+    int he = 0, ho = 0;
+    uint32_t le = 0, lo = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const uint32_t even = ws[j] & 0x0F0F0F0Fu;         // channels 8j+0,2,4,6
-      const uint32_t odd = (ws[j] >> 4) & 0x0F0F0F0Fu;   // channels 8j+1,3,5,7
-      acc_h = __dp4a((int)even, (int)qh_even[j], acc_h);
-      acc_h = __dp4a((int)odd, (int)qh_odd[j], acc_h);
-      acc_l = __dp4a(even, ql_even[j], acc_l);
-      acc_l = __dp4a(odd, ql_odd[j], acc_l);
+      const uint32_t even = ws[j] & 0x0F0F0F0Fu;    // channels 8j+0,2,4,6
+      const uint32_t odd16 = ws[j] & 0xF0F0F0F0u;   // 16 * channels 8j+1,3,5,7
+      he = dp4a_u8_s8(even, qh_even[j], he);
+      ho = dp4a_u8_s8(odd16, qh_odd[j], ho);
+      le = dp4a_u8_u8(even, ql_even[j], le);
+      lo = dp4a_u8_u8(odd16, ql_odd[j], lo);
     }
-    return (float)(acc_h * 256 + (int)acc_l) * inv;
+    return (he + (ho >> 4)) * 256 + (int)(le + (lo >> 4));
+  }
+  __device__ __forceinline__ float dot(const uint4& w) const {
+    // exact int -> float for |x| < 2^22 without the conversion unit
+    return (__int_as_float(0x4B400000 + idot(w)) - 12582912.f) * inv;
   }
 };
 
@@ -304,9 +324,11 @@ estimate_int4_kernel(const EstParams p) {
 // and returns.
 constexpr int kStagePages = 8;                       // 10 KiB per stage
 constexpr int kStages = 4;                           // 40 KiB ring per block
-constexpr int kTmaPagesPerBlock = 128;               // 160 KiB of INT4 cache per block
+constexpr int kTmaMaxPagesPerBlock = 512;            // capacity of the per-block page list
+constexpr int kTmaPagesPerBlockDefault = 128;        // 160 KiB of INT4 cache per block
 constexpr int kTmaThreads = kEstThreads + 32;        // 8 consumer warps + 1 producer warp
-constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr uint32_t kWaitLimit = 1u << 20;
+constexpr uint32_t kSuspendHintNs = 20000;  // a waiting thread may sleep this long per try
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -328,10 +350,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
-        : "r"(addr), "r"(parity)
+        : "r"(addr), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     if (done) return true;
   }
@@ -351,8 +373,8 @@ estimate_int4_tma_kernel(const EstParams p) {
   extern __shared__ __align__(128) uint8_t sm_ring[];  // kStages * kStagePages * kSlab bytes
   __shared__ __align__(8) uint64_t sm_full[kStages];
   __shared__ __align__(8) uint64_t sm_empty[kStages];
-  __shared__ int sm_phys[kTmaPagesPerBlock];
-  __shared__ int sm_ntok[kTmaPagesPerBlock];
+  __shared__ int sm_phys[kTmaMaxPagesPerBlock];
+  __shared__ int sm_ntok[kTmaMaxPagesPerBlock];
   __shared__ QRegs<VARIANT> sm_q[G][4];
 
   const int row = blockIdx.y;
@@ -374,29 +396,31 @@ estimate_int4_tma_kernel(const EstParams p) {
     n_pages = p.stride / kPage;
     if (threadIdx.x == 0 && blockIdx.x == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
   }
-  const int first = blockIdx.x * kTmaPagesPerBlock;
+  const int first = blockIdx.x * p.pages_per_block;
   if (first >= n_pages) return;
-  const int n_here = min(kTmaPagesPerBlock, n_pages - first);
+  const int n_here = min(p.pages_per_block, n_pages - first);
   const int n_stages_total = (n_here + kStagePages - 1) / kStagePages;
 
   const int tid = threadIdx.x;
-  if (tid < n_here) {
-    const int32_t* cand = has_cand ? p.cand_pages + (size_t)(b * p.Hq + h0) * p.max_k : nullptr;
-    const int seq_page = has_cand ? cand[first + tid] : first + tid;
-    int phys = -1;
-    if (seq_page >= 0 && seq_page < n_seq_pages) {
-      phys = p.indices[page_base + seq_page];
-      if (phys < 0 || phys >= p.num_pages_total) phys = -1;
-    }
-    if (phys < 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
-    sm_phys[tid] = phys;
-    sm_ntok[tid] = (seq_page == n_seq_pages - 1) ? p.last_len[b] : kPage;
-  } else if (tid >= kEstThreads - 4 * G && tid < kEstThreads) {
+  if (tid >= kEstThreads - 4 * G && tid < kEstThreads) {
     const int j = tid - (kEstThreads - 4 * G);
     const int g = j >> 2, grp_j = j & 3;
     float qf[32];
     load_q_group<T>(reinterpret_cast<const T*>(p.q) + ((size_t)(b * p.Hq + h0 + g)) * kD + grp_j * kGroup, qf);
     sm_q[g][grp_j].init(qf);
+  } else {
+    const int32_t* cand = has_cand ? p.cand_pages + (size_t)(b * p.Hq + h0) * p.max_k : nullptr;
+    for (int i = tid; i < n_here; i += kEstThreads - 4 * G) {
+      const int seq_page = has_cand ? cand[first + i] : first + i;
+      int phys = -1;
+      if (seq_page >= 0 && seq_page < n_seq_pages) {
+        phys = p.indices[page_base + seq_page];
+        if (phys < 0 || phys >= p.num_pages_total) phys = -1;
+      }
+      if (phys < 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+      sm_phys[i] = phys;
+      sm_ntok[i] = (seq_page == n_seq_pages - 1) ? p.last_len[b] : kPage;
+    }
   }
   if (tid == kEstThreads) {
     for (int s = 0; s < kStages; ++s) {
@@ -419,11 +443,11 @@ estimate_int4_tma_kernel(const EstParams p) {
         if (!ok) break;
         const int pg0 = st * kStagePages, pg1 = min(n_here, pg0 + kStagePages);
         uint32_t bytes = 0;
-        for (int pg = pg0; pg < pg1; ++pg) bytes += sm_phys[pg] >= 0 ? kSlab : 0;
+        for (int pg = pg0; pg < pg1; ++pg) bytes += (sm_phys[pg] >= 0 && !(p.debug & 2)) ? kSlab : 0;
         mbar_arrive_expect_tx(&sm_full[slot], bytes);
         for (int pg = pg0; pg < pg1; ++pg) {
           const int phys = sm_phys[pg];
-          if (phys >= 0)
+          if (phys >= 0 && !(p.debug & 2))
             bulk_copy_g2s(sm_ring + ((size_t)slot * kStagePages + (pg - pg0)) * kSlab,
                           p.k4 + ((size_t)phys * p.Hkv + kvh) * kSlab, kSlab, &sm_full[slot]);
         }
@@ -445,6 +469,7 @@ estimate_int4_tma_kernel(const EstParams p) {
 #pragma unroll
   for (int g = 0; g < G; ++g) qr[g] = sm_q[g][grp];
 
+  float* const out_rows = p.scores + (size_t)(b * p.Hq + h0) * p.stride + (size_t)first * kPage + tok_in_step;
   for (int st = 0; st < n_stages_total; ++st) {
     const int slot = st % kStages;
     if (!mbar_wait(&sm_full[slot], (st / kStages) & 1)) {
@@ -454,7 +479,7 @@ estimate_int4_tma_kernel(const EstParams p) {
     const int pg0 = st * kStagePages;
     const int n_steps = (min(n_here, pg0 + kStagePages) - pg0) * 2;
     const uint8_t* stage = sm_ring + (size_t)slot * kStagePages * kSlab;
-    for (int s = warp; s < n_steps; s += kEstWarps) {
+    for (int s = warp; s < n_steps && !(p.debug & 1); s += kEstWarps) {
       const int pgl = s >> 1, half = s & 1;
       const int pg = pg0 + pgl;
       const bool present = sm_phys[pg] >= 0;
@@ -466,7 +491,7 @@ estimate_int4_tma_kernel(const EstParams p) {
         w = *reinterpret_cast<const uint4*>(slab + half * 512 + lane * 16);
         sz = *reinterpret_cast<const uint32_t*>(slab + kSlabCodes + half * 128 + lane * 4);
       }
-      const int slot_out = (first + pg) * kPage + half * 8 + tok_in_step;
+      const int slot_out = pg * kPage + half * 8;
       const float2 szf = __half22float2(*reinterpret_cast<const __half2*>(&sz));
       float part[G];
 #pragma unroll
@@ -479,7 +504,7 @@ estimate_int4_tma_kernel(const EstParams p) {
       for (int g = 0; g < G; ++g) {
         if ((g & 3) == grp) {
           const float v = valid ? part[g] * p.sm_scale : -INFINITY;
-          p.scores[(size_t)(b * p.Hq + h0 + g) * p.stride + slot_out] = v;
+          out_rows[(size_t)g * p.stride + slot_out] = v;
         }
       }
     }
@@ -488,17 +513,175 @@ estimate_int4_tma_kernel(const EstParams p) {
   }
 }
 
+// ---- warp-private cp.async ring, one lane per token (single query head per row) ------------------
+// Every warp streams its own page pairs (32 tokens = 2560 bytes) through a private ring in shared
+// memory with 16-byte cp.async copies, so there is no block-level barrier and no register staging:
+// bytes in flight are kRingDepth-1 stages per warp.  Inside a stage lane t owns token t and all four
+// 32-channel groups, so no shuffle is needed and the 32 scores go out as one 128-byte store.  A
+// token's four 16-byte code chunks are stored rotated by (t>>1) so that the 8 lanes of a quarter
+// warp hit 8 different bank groups when all of them read "their chunk j".
+constexpr int kRingDepth = 4;
+constexpr int kWarpStageBytes = 2 * kSlab;   // two pages
+constexpr int kWarpPagesPerBlock = 128;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <typename T, int VARIANT>
+__global__ void __launch_bounds__(kEstThreads)
+estimate_int4_warp_kernel(const EstParams p) {
+  extern __shared__ __align__(128) uint8_t sm_ring[];  // kEstWarps * kRingDepth * kWarpStageBytes
+  __shared__ int sm_phys[kWarpPagesPerBlock];
+  __shared__ int sm_ntok[kWarpPagesPerBlock];
+  __shared__ QRegs<VARIANT> sm_q[4];
+
+  const int row = blockIdx.y;
+  const bool has_cand = p.cand_pages != nullptr;
+  int b, kvh, h;
+  if (has_cand) {
+    b = row / p.Hq;
+    h = row % p.Hq;
+    kvh = h / (p.Hq / p.Hkv);
+  } else {  // one query head per KV head
+    b = row / p.Hkv;
+    kvh = row % p.Hkv;
+    h = kvh;
+  }
+  const int page_base = p.indptr[b];
+  const int n_seq_pages = p.indptr[b + 1] - page_base;
+  int n_pages = has_cand ? min(p.cand_npages[b * p.Hq + h], p.max_k) : n_seq_pages;
+  if (n_pages > p.stride / kPage) {
+    n_pages = p.stride / kPage;
+    if (threadIdx.x == 0 && blockIdx.x == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+  }
+  const int first = blockIdx.x * kWarpPagesPerBlock;
+  if (first >= n_pages) return;
+  const int n_here = min(kWarpPagesPerBlock, n_pages - first);
+
+  const int tid = threadIdx.x;
+  if (tid >= kEstThreads - 4) {
+    const int grp_j = tid - (kEstThreads - 4);
+    float qf[32];
+    load_q_group<T>(reinterpret_cast<const T*>(p.q) + ((size_t)(b * p.Hq + h)) * kD + grp_j * kGroup, qf);
+    sm_q[grp_j].init(qf);
+  } else if (tid < kWarpPagesPerBlock) {
+    int phys = -1, ntok = 0;
+    if (tid < n_here) {
+      const int seq_page = has_cand ? p.cand_pages[(size_t)(b * p.Hq + h) * p.max_k + first + tid] : first + tid;
+      if (seq_page >= 0 && seq_page < n_seq_pages) {
+        phys = p.indices[page_base + seq_page];
+        if (phys < 0 || phys >= p.num_pages_total) phys = -1;
+      }
+      if (phys < 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+      ntok = (seq_page == n_seq_pages - 1) ? p.last_len[b] : kPage;
+    }
+    sm_phys[tid] = phys;
+    sm_ntok[tid] = phys < 0 ? 0 : ntok;
+  }
+  __syncthreads();
+
+  const int lane = tid & 31, warp = tid >> 5;
+  QRegs<VARIANT> qr[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) qr[g] = sm_q[g];
+
+  uint8_t* const ring = sm_ring + (size_t)warp * kRingDepth * kWarpStageBytes;
+  const uint32_t ring_u32 = smem_u32(ring);
+  const int n_pairs = (n_here + 1) >> 1;
+  const int my_pairs = (n_pairs > warp) ? (n_pairs - warp + kEstWarps - 1) / kEstWarps : 0;
+
+  // Per-lane constants of the five 16-byte copies of a stage: chunk c = c5*32+lane of the pair,
+  // i.e. page c/80 and chunk r = c%80 of its slab (0..63 codes, 64..79 scale/min).
+  uint32_t src16[5], dst_off[5];
+  bool second[5];
+#pragma unroll
+  for (int c5 = 0; c5 < 5; ++c5) {
+    const int c = c5 * 32 + lane;
+    const int pgl = c >= 80 ? 1 : 0;
+    const int r = c - pgl * 80;
+    second[c5] = pgl != 0;
+    src16[c5] = r;
+    if (r < 64) {
+      const int t = pgl * 16 + (r >> 2), g = r & 3;
+      dst_off[c5] = t * 64 + (((g + (t >> 1)) & 3) << 4);
+    } else {
+      dst_off[c5] = 2048 + (pgl * 16 + (r - 64)) * 16;
+    }
+  }
+  const uint4* const k4_head16 = reinterpret_cast<const uint4*>(p.k4 + (size_t)kvh * kSlab);
+  const uint32_t page_stride16 = (uint32_t)(p.Hkv * (kSlab / 16));
+
+  // issue the copies of this warp's i-th pair into ring slot i % kRingDepth
+  auto issue = [&](int i) {
+    if (i < my_pairs) {
+      const int pg0 = (warp + i * kEstWarps) * 2;
+      const uint32_t dst0 = ring_u32 + (i % kRingDepth) * kWarpStageBytes;
+      const int phys0 = sm_phys[pg0], phys1 = sm_phys[pg0 + 1];  // missing pages hold -1
+#pragma unroll
+      for (int c5 = 0; c5 < 5; ++c5) {
+        const int phys = second[c5] ? phys1 : phys0;
+        if (phys >= 0)
+          cp_async16(dst0 + dst_off[c5], k4_head16 + ((size_t)phys * page_stride16 + src16[c5]));
+      }
+    }
+    cp_async_commit();  // always commit so that group counting stays uniform
+  };
+
+#pragma unroll
+  for (int i = 0; i < kRingDepth - 1; ++i) issue(i);
+
+  uint32_t rd_off[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) rd_off[g] = lane * 64 + (((g + (lane >> 1)) & 3) << 4);
+  float* const out_row = p.scores + (size_t)(b * p.Hq + h) * p.stride + (size_t)first * kPage;
+  for (int i = 0; i < my_pairs; ++i) {
+    cp_async_wait<kRingDepth - 2>();  // pair i has landed (this thread's copies)
+    __syncwarp();                     // ... and every other lane's
+    const int pg0 = (warp + i * kEstWarps) * 2;
+    const uint8_t* stage = ring + (i % kRingDepth) * kWarpStageBytes;
+    const int pgl = lane >> 4, tl = lane & 15;
+    const int ntok = sm_ntok[pg0 + pgl];
+    const bool present = sm_phys[pg0 + pgl] >= 0;
+    const uint4 sz = *reinterpret_cast<const uint4*>(stage + 2048 + lane * 16);
+    const uint32_t szw[4] = {sz.x, sz.y, sz.z, sz.w};
+    float acc = 0.f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const uint4 w = *reinterpret_cast<const uint4*>(stage + rd_off[g]);
+      const float2 szf = __half22float2(*reinterpret_cast<const __half2*>(&szw[g]));
+      acc = fmaf(szf.x, qr[g].dot(w), acc);
+      acc = fmaf(szf.y, qr[g].qsum, acc);
+    }
+    __syncwarp();      // all lanes are done reading the slot that the next issue overwrites
+    issue(i + kRingDepth - 1);
+    if (present) out_row[(pg0 + pgl) * kPage + tl] = (tl < ntok) ? acc * p.sm_scale : -INFINITY;
+  }
+  cp_async_wait<0>();
+}
+
 template <typename T, int G, int VARIANT>
 static int launch_one(const EstParams& p, int rows, int max_row_pages, bool ldg, cudaStream_t st) {
   if (rows > 65535) return TWL_ERR_TOO_LARGE;
   if (ldg) {
     dim3 grid((max_row_pages + kPagesPerBlock - 1) / kPagesPerBlock, rows);
     estimate_int4_kernel<T, G, VARIANT><<<grid, kEstThreads, 0, st>>>(p);
+  } else if (G == 1 && !(p.debug & 4)) {
+    constexpr int kBytes = kEstWarps * kRingDepth * kWarpStageBytes;
+    auto kern = estimate_int4_warp_kernel<T, VARIANT>;
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+    dim3 grid((max_row_pages + kWarpPagesPerBlock - 1) / kWarpPagesPerBlock, rows);
+    kern<<<grid, kEstThreads, kBytes, st>>>(p);
   } else {
     constexpr int kRingBytes = kStages * kStagePages * kSlab;
     auto kern = estimate_int4_tma_kernel<T, G, VARIANT>;
     TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes));
-    dim3 grid((max_row_pages + kTmaPagesPerBlock - 1) / kTmaPagesPerBlock, rows);
+    dim3 grid((max_row_pages + p.pages_per_block - 1) / p.pages_per_block, rows);
     kern<<<grid, kTmaThreads, kRingBytes, st>>>(p);
   }
   TWL_CHECK_LAUNCH();
@@ -522,6 +705,7 @@ static int launch_variant(const EstParams& p, bool has_cand, int max_row_pages, 
 template <typename T>
 static int launch_dtype(const EstParams& p, bool has_cand, int max_row_pages, int variant,
                         cudaStream_t st) {
+  const_cast<EstParams&>(p).debug = (variant >> 5) & 7;
   const bool ldg = (variant & 16) != 0;  // +16: direct global loads instead of the staged ring
   switch (variant & 15) {
     case VAR_F32: return launch_variant<T, VAR_F32>(p, has_cand, max_row_pages, ldg, st);
@@ -559,6 +743,15 @@ extern "C" int twl_estimate_int4(const void* q, int dtype, const uint8_t* k4_pag
   p.scores = scores; p.status = status; p.max_k = max_k; p.B = batch; p.Hq = num_q_heads;
   p.Hkv = num_kv_heads; p.num_pages_total = num_pages_total; p.stride = score_stride;
   p.sm_scale = sm_scale;
+  {
+    // tuning hook: pages per block of the staged kernel (power of two, 16..512)
+    static const int ppb = [] {
+      const char* e = getenv("TWL_EST_PAGES_PER_BLOCK");
+      int v = e ? atoi(e) : kTmaPagesPerBlockDefault;
+      return (v >= 16 && v <= kTmaMaxPagesPerBlock) ? v : kTmaPagesPerBlockDefault;
+    }();
+    p.pages_per_block = ppb;
+  }
   // rows never hold more pages than the score row has room for
   const int max_row_pages = has_cand ? max_k : score_stride / kPage;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
