@@ -138,11 +138,14 @@ TWL_API int twl_topp_prune(const float* scores, int32_t score_stride, const int3
 
 /* ---- kernel #3: sparse paged decode attention ------------------------------------------
  * Replaces attention.py:188-190 restricted to the kept tokens and :298-306 (masked fp32
- * softmax, P.V).  Split-KV: each block handles `chunk` indices of one row and the last
- * block of a row to finish merges the partial (max, sum, acc) triples; no block waits.
+ * softmax, P.V).  A row's kept tokens are cut into chunks of `chunk` tokens (a multiple of 32;
+ * <= 0 selects 256; the chunk grows for rows that would need more than 32 of them) and the
+ * (row, chunk) work items are dealt round-robin to a grid that fills the GPU once, so heads
+ * with large budgets do not serialise.  The block that finishes a row's last chunk merges the
+ * partial (max, sum, acc) triples; no block waits for another.
  * workspace: twl_sparse_attn_workspace_bytes(...) bytes, 16-byte aligned; its first
  * batch*num_q_heads int32 words are arrival counters that must be zero on entry and are
- * left zero on exit. */
+ * left zero on exit.  Rows with budget 0 produce zeros. */
 TWL_API size_t twl_sparse_attn_workspace_bytes(int32_t batch, int32_t num_q_heads,
                                        int32_t index_stride, int32_t chunk);
 TWL_API int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pages, const void* v_pages,

@@ -4,14 +4,17 @@
 // kept tokens) and :298-306 (masked fp32 softmax, P.V).  The reference computes the dense
 // [L] row and masks it; here a row's cost is its budget.
 //
-// Split-KV: the indices of one (batch, query head) row are cut into chunks of `chunk`; up to
-// kMaxSplits blocks share a row, block x taking chunks x, x+splits, ... and carrying one running
-// (max, sum, acc) across them.  A warp takes 32 indices at a time: each lane resolves one token to its K/V row
-// through the page table, then the warp walks the 32 rows four at a time, every lane owning
-// 4 of the 128 channels (one 8-byte load per K row and per V row), with an online softmax
-// (running max, sum, 4 accumulators per lane).  Warps merge through shared memory; blocks of
-// a row merge through the caller's workspace, and the block that arrives last (an atomic
-// ticket, nobody waits) writes the output.
+// Budgets differ by orders of magnitude between heads, so work is balanced on the device: the
+// kept tokens of a (batch, query head) row are cut into chunks of `chunk` tokens, every block
+// first prefix-sums the rows' chunk counts in shared memory (all blocks compute the same
+// table, nothing is exchanged), and block x then takes work items x, x+grid, ... of the
+// flattened (row, chunk) list.  A warp takes 32 indices at a time: each lane resolves one token
+// to its K/V row through the page table (one group ahead of use); every lane owns 4 of the 128
+// channels and requests its 8 bytes of the K and V rows of 16 tokens before using any of them;
+// a transpose-reduce leaves the dot product of token u in lane u; softmax is online (running
+// max, sum, 4 accumulators per lane).  Warps merge through shared memory; chunks of a
+// row merge through the caller's workspace, and the block that finishes a row's last chunk
+// (an atomic ticket, nobody waits) writes the output.
 #include <algorithm>
 
 #include "common.cuh"
@@ -20,8 +23,9 @@ namespace twl {
 
 constexpr int kAttThreads = 128;
 constexpr int kAttWarps = kAttThreads / 32;
-constexpr int kMaxSplits = 8;        // blocks per row
-constexpr float kNegBig = -3.0e38f;  // finite stand-in for -inf so that exp(m_old-m_new) is defined
+constexpr int kMaxChunksPerRow = 32;     // partial slots per row in the workspace
+constexpr int kAttBlocksPerSM = 5;
+constexpr float kNegBig = -3.0e38f;      // finite stand-in for -inf so that exp(m_old-m_new) is defined
 
 struct AttParams {
   const void* q;
@@ -33,165 +37,222 @@ struct AttParams {
   const int32_t* budget;
   void* out;
   int32_t* counters;  // [rows]
-  float* part_ml;     // [rows][max_chunks][2]
-  float* part_o;      // [rows][max_chunks][128]
+  float* part_ml;     // [rows][kMaxChunksPerRow][2]
+  float* part_o;      // [rows][kMaxChunksPerRow][128]
   int32_t* status;
-  int index_stride, B, Hq, Hkv, num_pages_total, chunk, max_chunks;
+  int index_stride, rows, Hq, Hkv, num_pages_total, chunk;
   float sm_scale;
 };
+
+// chunk length actually used for a row: `chunk`, grown so that a row never needs more than
+// kMaxChunksPerRow partial slots
+__device__ __forceinline__ int row_chunk_len(int budget, int chunk) {
+  int len = chunk;
+  while ((budget + len - 1) / len > kMaxChunksPerRow) len *= 2;
+  return len;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kAttThreads)
 sparse_decode_attn_kernel(const AttParams p) {
+  extern __shared__ int sm_prefix[];  // rows + 1 exclusive prefix sums of chunk counts
   __shared__ float sm_o[kAttWarps][kD];
   __shared__ float sm_m[kAttWarps], sm_l[kAttWarps];
+  __shared__ int sm_scan[33];
   __shared__ int sm_ticket;
 
-  const int row = blockIdx.y, c = blockIdx.x;
-  const int b = row / p.Hq, h = row % p.Hq;
-  const int kvh = h / (p.Hq / p.Hkv);
-  const int budget = min(p.budget[row], p.index_stride);
-  const int n_chunks = (budget + p.chunk - 1) / p.chunk;
-  const int n_parts = min(n_chunks, (int)gridDim.x);  // blocks of this row that have work
-  T* out = reinterpret_cast<T*>(p.out) + (size_t)row * kD;
-  if (budget <= 0) {
-    if (c == 0) out[threadIdx.x] = Elem<T>::from_f(0.f);
-    return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // ---- schedule: chunk counts of all rows, prefix-summed (identical in every block) ----
+  {
+    int carry = 0;
+    for (int r0 = 0; r0 < p.rows; r0 += kAttThreads) {
+      const int r = r0 + tid;
+      int n = 0;
+      if (r < p.rows) {
+        const int bud = min(max(p.budget[r], 0), p.index_stride);
+        const int len = row_chunk_len(bud, p.chunk);
+        n = (bud + len - 1) / len;
+      }
+      int total;
+      const int excl = block_excl_scan<kAttThreads>(n, &total, sm_scan);
+      if (r < p.rows) sm_prefix[r] = carry + excl;
+      carry += total;
+    }
+    if (tid == 0) sm_prefix[p.rows] = carry;
+    __syncthreads();
   }
-  if (c >= n_parts) return;
+  const int n_items = sm_prefix[p.rows];
+  // rows without kept tokens produce zeros (the reference never meets this case)
+  for (int r = blockIdx.x * kAttThreads + tid; r < p.rows; r += gridDim.x * kAttThreads) {
+    if (sm_prefix[r + 1] == sm_prefix[r]) {
+      T* o = reinterpret_cast<T*>(p.out) + (size_t)r * kD;
+      for (int d = 0; d < kD; ++d) o[d] = Elem<T>::from_f(0.f);
+    }
+  }
 
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int page_base = p.indptr[b];
-  const int n_seq_pages = p.indptr[b + 1] - page_base;
-  const int32_t* idx = p.idx + (size_t)row * p.index_stride;
   const T* kbase = reinterpret_cast<const T*>(p.k);
   const T* vbase = reinterpret_cast<const T*>(p.v);
 
-  // this lane's 4 channels of q, pre-multiplied by the softmax scale
-  float qf[4];
-  {
-    uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const T*>(p.q) + (size_t)row * kD) + lane);
-    float2 a = Elem<T>::to_f2(u.x), bq = Elem<T>::to_f2(u.y);
-    qf[0] = a.x * p.sm_scale; qf[1] = a.y * p.sm_scale;
-    qf[2] = bq.x * p.sm_scale; qf[3] = bq.y * p.sm_scale;
-  }
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    // row of this item: last r with prefix[r] <= item
+    int lo = 0, hi = p.rows;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (sm_prefix[mid] <= item) lo = mid; else hi = mid;
+    }
+    const int row = lo, c = item - sm_prefix[row];
+    const int n_parts = sm_prefix[row + 1] - sm_prefix[row];
+    const int b = row / p.Hq, h = row % p.Hq;
+    const int kvh = h / (p.Hq / p.Hkv);
+    const int budget = min(p.budget[row], p.index_stride);
+    const int clen = row_chunk_len(budget, p.chunk);
+    const int begin = c * clen, end = min(budget, begin + clen);
+    const int page_base = p.indptr[b];
+    const int n_seq_pages = p.indptr[b + 1] - page_base;
+    const int32_t* idx = p.idx + (size_t)row * p.index_stride;
+    T* out = reinterpret_cast<T*>(p.out) + (size_t)row * kD;
 
-  float m = kNegBig, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int cc = c; cc < n_chunks; cc += gridDim.x) {
-  const int begin = cc * p.chunk, end = min(budget, begin + p.chunk);
-  for (int t0 = begin + warp * 32; t0 < end; t0 += kAttWarps * 32) {
-    // each lane resolves one token -> row number inside the K/V page arrays (-1 = skip)
-    long long ro = -1;
-    if (t0 + lane < end) {
-      const int tok = idx[t0 + lane];
+    // this lane's 4 channels of q, pre-multiplied by the softmax scale
+    float qf[4];
+    {
+      uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const T*>(p.q) + (size_t)row * kD) + lane);
+      float2 a = Elem<T>::to_f2(u.x), bq = Elem<T>::to_f2(u.y);
+      qf[0] = a.x * p.sm_scale; qf[1] = a.y * p.sm_scale;
+      qf[2] = bq.x * p.sm_scale; qf[3] = bq.y * p.sm_scale;
+    }
+
+    // token index -> row number inside the K/V page arrays (-1 = nothing to read).  Lookups run
+    // one 32-token group ahead and index loads two groups ahead, so the streaming loop never
+    // waits on them; bad indices are only remembered here and reported after the loop.
+    bool bad = false;
+    auto load_tok = [&](int t) -> int { return (t < end) ? idx[t] : -1; };
+    auto lookup = [&](int tok, int t) -> int {
+      int ro = -1;
       const int pg = tok >> 4;
       if (tok >= 0 && pg < n_seq_pages) {
         const int phys = p.indices[page_base + pg];
-        if (phys >= 0 && phys < p.num_pages_total)
-          ro = ((long long)phys * p.Hkv + kvh) * kPage + (tok & 15);
+        if (phys >= 0 && phys < p.num_pages_total) ro = (phys * p.Hkv + kvh) * kPage + (tok & 15);
       }
-      if (ro < 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
-    }
-    const int n_here = min(32, end - t0);
-    for (int j = 0; j < n_here; j += 4) {
-      uint2 kk[4], vv[4];
-      bool ok[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const long long r = __shfl_sync(0xffffffffu, ro, (j + u) & 31);
-        ok[u] = (j + u < n_here) && r >= 0;
-        if (ok[u]) {
-          kk[u] = ldg_stream_u2(kbase + r * kD + lane * 4);
-          vv[u] = ldg_stream_u2(vbase + r * kD + lane * 4);
-        } else {
-          kk[u] = make_uint2(0, 0);
-          vv[u] = make_uint2(0, 0);
-        }
-      }
-      float s[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const float2 k0 = Elem<T>::to_f2(kk[u].x), k1 = Elem<T>::to_f2(kk[u].y);
-        s[u] = qf[0] * k0.x + qf[1] * k0.y + qf[2] * k1.x + qf[3] * k1.y;
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
-      }
-      float m_new = m;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        s[u] = ok[u] ? s[u] : -INFINITY;
-        m_new = fmaxf(m_new, s[u]);
-      }
-      const float scale = __expf(m - m_new);
-      l *= scale;
-#pragma unroll
-      for (int d = 0; d < 4; ++d) acc[d] *= scale;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const float pw = __expf(s[u] - m_new);
-        l += pw;
-        const float2 v0 = Elem<T>::to_f2(vv[u].x), v1 = Elem<T>::to_f2(vv[u].y);
-        acc[0] = fmaf(pw, v0.x, acc[0]);
-        acc[1] = fmaf(pw, v0.y, acc[1]);
-        acc[2] = fmaf(pw, v1.x, acc[2]);
-        acc[3] = fmaf(pw, v1.y, acc[3]);
-      }
-      m = m_new;
-    }
-  }
-  }
+      bad = bad || (t < end && ro < 0);
+      return ro;
+    };
 
-  // merge the warps of this block
-  if (lane == 0) {
-    sm_m[warp] = m;
-    sm_l[warp] = l;
-  }
+    float m = kNegBig, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const int t_first = begin + warp * 32, t_step = kAttWarps * 32;
+    int ro_next = lookup(load_tok(t_first + lane), t_first + lane);
+    int tok_next = load_tok(t_first + t_step + lane);
+    for (int t0 = t_first; t0 < end; t0 += t_step) {
+      const int ro = ro_next;
+      ro_next = lookup(tok_next, t0 + t_step + lane);
+      tok_next = load_tok(t0 + 2 * t_step + lane);
 #pragma unroll
-  for (int d = 0; d < 4; ++d) sm_o[warp][lane * 4 + d] = acc[d];
-  __syncthreads();
-  float bm = kNegBig;
+      for (int half = 0; half < 2; ++half) {
+        const int n_here = min(16, end - t0 - half * 16);
+        if (n_here <= 0) break;  // warp-uniform
+        // K and V rows of 16 tokens are all requested before any is used
+        int rr[16];
+        uint2 kk[16], vv[16];
 #pragma unroll
-  for (int w = 0; w < kAttWarps; ++w) bm = fmaxf(bm, sm_m[w]);
-  float bl = 0.f, bo = 0.f;
-  const int d = threadIdx.x;  // thread d owns channel d from here on
+        for (int u = 0; u < 16; ++u) {
+          // tokens that are absent or invalid read row 0 (always mapped) and get weight 0 below,
+          // so that the 32 loads carry no branch and overlap freely
+          rr[u] = max(__shfl_sync(0xffffffffu, ro, half * 16 + u), 0);
+          kk[u] = ldg_stream_u2(kbase + (size_t)rr[u] * kD + lane * 4);
+          vv[u] = ldg_stream_u2(vbase + (size_t)rr[u] * kD + lane * 4);
+        }
+        float s[16];
 #pragma unroll
-  for (int w = 0; w < kAttWarps; ++w) {
-    const float f = __expf(sm_m[w] - bm);
-    bl += f * sm_l[w];
-    bo += f * sm_o[w][d];
+        for (int u = 0; u < 16; ++u) {
+          const float2 k0 = Elem<T>::to_f2(kk[u].x), k1 = Elem<T>::to_f2(kk[u].y);
+          s[u] = qf[0] * k0.x + qf[1] * k0.y + qf[2] * k1.x + qf[3] * k1.y;
+        }
+        // the two 16-lane halves first add up, then 15 exchanges leave the dot product of token
+        // u in lanes u and u+16
+#pragma unroll
+        for (int u = 0; u < 16; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], 16);
+#pragma unroll
+        for (int o = 8; o >= 1; o >>= 1) {
+          const bool upper = (lane & o) != 0;
+#pragma unroll
+          for (int i = 0; i < o; ++i) {
+            const float send = upper ? s[i] : s[i + o];
+            const float keep = upper ? s[i + o] : s[i];
+            s[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+          }
+        }
+        const int my_r = __shfl_sync(0xffffffffu, ro, half * 16 + (lane & 15));
+        const float mine = (my_r >= 0 && lane < 16) ? s[0] : -INFINITY;  // one copy per token
+        const float m_new = fmaxf(m, warp_max(mine));
+        const float scale = __expf(m - m_new);
+        const float pw = __expf(mine - m_new);
+        l = l * scale + warp_sum(pw);
+#pragma unroll
+        for (int d = 0; d < 4; ++d) acc[d] *= scale;
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const float pu = __shfl_sync(0xffffffffu, pw, u);
+          const float2 v0 = Elem<T>::to_f2(vv[u].x), v1 = Elem<T>::to_f2(vv[u].y);
+          acc[0] = fmaf(pu, v0.x, acc[0]);
+          acc[1] = fmaf(pu, v0.y, acc[1]);
+          acc[2] = fmaf(pu, v1.x, acc[2]);
+          acc[3] = fmaf(pu, v1.y, acc[3]);
+        }
+        m = m_new;
+      }
+    }
+    if (__any_sync(0xffffffffu, bad) && lane == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+
+    // merge the warps of this block
+    if (lane == 0) {
+      sm_m[warp] = m;
+      sm_l[warp] = l;
+    }
+#pragma unroll
+    for (int d = 0; d < 4; ++d) sm_o[warp][lane * 4 + d] = acc[d];
+    __syncthreads();
+    float bm = kNegBig;
+#pragma unroll
+    for (int w = 0; w < kAttWarps; ++w) bm = fmaxf(bm, sm_m[w]);
+    float bl = 0.f, bo = 0.f;
+    const int d = tid;  // thread d owns channel d from here on
+#pragma unroll
+    for (int w = 0; w < kAttWarps; ++w) {
+      const float f = __expf(sm_m[w] - bm);
+      bl += f * sm_l[w];
+      bo += f * sm_o[w][d];
+    }
+    if (n_parts == 1) {
+      out[d] = Elem<T>::from_f(bl > 0.f ? bo / bl : 0.f);
+    } else {
+      // publish this chunk's partial, then take a ticket
+      const size_t slot = (size_t)row * kMaxChunksPerRow + c;
+      p.part_o[slot * kD + d] = bo;
+      if (d == 0) {
+        p.part_ml[slot * 2] = bm;
+        p.part_ml[slot * 2 + 1] = bl;
+      }
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) sm_ticket = atomicAdd(&p.counters[row], 1);
+      __syncthreads();
+      if (sm_ticket == n_parts - 1) {  // every chunk of the row has been published
+        __threadfence();
+        float gm = kNegBig;
+        for (int cc = 0; cc < n_parts; ++cc)
+          gm = fmaxf(gm, __ldcg(&p.part_ml[((size_t)row * kMaxChunksPerRow + cc) * 2]));
+        float gl = 0.f, go = 0.f;
+        for (int cc = 0; cc < n_parts; ++cc) {
+          const size_t s2 = (size_t)row * kMaxChunksPerRow + cc;
+          const float f = __expf(__ldcg(&p.part_ml[s2 * 2]) - gm);
+          gl += f * __ldcg(&p.part_ml[s2 * 2 + 1]);
+          go += f * __ldcg(&p.part_o[s2 * kD + d]);
+        }
+        out[d] = Elem<T>::from_f(gl > 0.f ? go / gl : 0.f);
+        if (tid == 0) p.counters[row] = 0;  // leave the workspace ready for the next call
+      }
+    }
+    __syncthreads();  // shared merge buffers are reused by the next item
   }
-  if (n_parts == 1) {
-    out[d] = Elem<T>::from_f(bl > 0.f ? bo / bl : 0.f);
-    return;
-  }
-  // publish this block's partial, then take a ticket
-  const size_t slot = (size_t)row * p.max_chunks + c;
-  p.part_o[slot * kD + d] = bo;
-  if (d == 0) {
-    p.part_ml[slot * 2] = bm;
-    p.part_ml[slot * 2 + 1] = bl;
-  }
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) sm_ticket = atomicAdd(&p.counters[row], 1);
-  __syncthreads();
-  if (sm_ticket != n_parts - 1) return;
-  __threadfence();
-  float gm = kNegBig;
-  for (int cc = 0; cc < n_parts; ++cc)
-    gm = fmaxf(gm, __ldcg(&p.part_ml[((size_t)row * p.max_chunks + cc) * 2]));
-  float gl = 0.f, go = 0.f;
-  for (int cc = 0; cc < n_parts; ++cc) {
-    const size_t s2 = (size_t)row * p.max_chunks + cc;
-    const float f = __expf(__ldcg(&p.part_ml[s2 * 2]) - gm);
-    gl += f * __ldcg(&p.part_ml[s2 * 2 + 1]);
-    go += f * __ldcg(&p.part_o[s2 * kD + d]);
-  }
-  out[d] = Elem<T>::from_f(gl > 0.f ? go / gl : 0.f);
-  if (threadIdx.x == 0) p.counters[row] = 0;  // leave the workspace ready for the next call
 }
 
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -202,11 +263,9 @@ extern "C" size_t twl_sparse_attn_workspace_bytes(int32_t batch, int32_t num_q_h
                                                   int32_t index_stride, int32_t chunk) {
   if (batch <= 0 || num_q_heads <= 0 || index_stride <= 0 || chunk <= 0) return 0;
   const size_t rows = (size_t)batch * num_q_heads;
-  const size_t max_chunks =
-      std::min<size_t>(((size_t)index_stride + chunk - 1) / chunk, twl::kMaxSplits);
   size_t bytes = twl::align_up(rows * sizeof(int32_t), 256);
-  bytes += twl::align_up(rows * max_chunks * 2 * sizeof(float), 256);
-  bytes += rows * max_chunks * twl::kD * sizeof(float);
+  bytes += twl::align_up(rows * twl::kMaxChunksPerRow * 2 * sizeof(float), 256);
+  bytes += rows * twl::kMaxChunksPerRow * twl::kD * sizeof(float);
   return bytes;
 }
 
@@ -232,8 +291,9 @@ extern "C" int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pa
   if (!workspace || workspace_bytes < need) return TWL_ERR_WORKSPACE;
   if (!aligned(workspace, 16)) return TWL_ERR_MISALIGNED;
   const size_t rows = (size_t)batch * num_q_heads;
-  if (rows > 65535) return TWL_ERR_TOO_LARGE;
-  const size_t max_chunks = std::min<size_t>(((size_t)index_stride + chunk - 1) / chunk, kMaxSplits);
+  // the schedule table lives in shared memory; K/V row numbers are 32-bit
+  if (rows > 48 * 1024) return TWL_ERR_TOO_LARGE;
+  if ((int64_t)num_pages_total * num_kv_heads * kPage >= (int64_t)1 << 31) return TWL_ERR_TOO_LARGE;
   AttParams p;
   p.q = q; p.k = k_pages; p.v = v_pages; p.indptr = kv_indptr; p.indices = kv_indices;
   p.idx = indices; p.budget = budget; p.out = out; p.status = status;
@@ -241,17 +301,25 @@ extern "C" int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pa
   p.counters = reinterpret_cast<int32_t*>(ws);
   ws += align_up(rows * sizeof(int32_t), 256);
   p.part_ml = reinterpret_cast<float*>(ws);
-  ws += align_up(rows * max_chunks * 2 * sizeof(float), 256);
+  ws += align_up(rows * kMaxChunksPerRow * 2 * sizeof(float), 256);
   p.part_o = reinterpret_cast<float*>(ws);
-  p.index_stride = index_stride; p.B = batch; p.Hq = num_q_heads; p.Hkv = num_kv_heads;
-  p.num_pages_total = num_pages_total; p.chunk = chunk; p.max_chunks = (int)max_chunks;
-  p.sm_scale = sm_scale;
-  dim3 grid((unsigned)max_chunks, (unsigned)rows);
+  p.index_stride = index_stride; p.rows = (int)rows; p.Hq = num_q_heads; p.Hkv = num_kv_heads;
+  p.num_pages_total = num_pages_total; p.chunk = chunk; p.sm_scale = sm_scale;
+  // enough blocks to give every row its own block when budgets are small, never more than the
+  // machine holds at once
+  const size_t max_items =
+      rows * std::min<size_t>(kMaxChunksPerRow, ((size_t)index_stride + chunk - 1) / chunk);
+  const unsigned grid = (unsigned)std::min<size_t>(max_items, (size_t)kNumSMs * kAttBlocksPerSM);
+  const size_t smem = (rows + 1) * sizeof(int);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == TWL_F16) {
-    sparse_decode_attn_kernel<__half><<<grid, kAttThreads, 0, st>>>(p);
+    auto kern = sparse_decode_attn_kernel<__half>;
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    kern<<<grid, kAttThreads, smem, st>>>(p);
   } else if (dtype == TWL_BF16) {
-    sparse_decode_attn_kernel<__nv_bfloat16><<<grid, kAttThreads, 0, st>>>(p);
+    auto kern = sparse_decode_attn_kernel<__nv_bfloat16>;
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    kern<<<grid, kAttThreads, smem, st>>>(p);
   } else {
     return TWL_ERR_UNSUPPORTED;
   }

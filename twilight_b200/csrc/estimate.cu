@@ -520,7 +520,7 @@ estimate_int4_tma_kernel(const EstParams p) {
 // 32-channel groups, so no shuffle is needed and the 32 scores go out as one 128-byte store.  A
 // token's four 16-byte code chunks are stored rotated by (t>>1) so that the 8 lanes of a quarter
 // warp hit 8 different bank groups when all of them read "their chunk j".
-constexpr int kRingDepth = 4;
+constexpr int kRingDepth = 5;
 constexpr int kWarpStageBytes = 2 * kSlab;   // two pages
 constexpr int kWarpPagesPerBlock = 128;
 

@@ -24,6 +24,8 @@ constexpr int kSearchRoundCap = 128;
 constexpr float kSearchEps = 1e-5f;
 // floats of a row that fit in shared memory next to the reduction scratch
 constexpr int kRowCap = 56 * 1024;
+// rows of the fused pruner also need a working list of a quarter of the row
+constexpr int kPruneRowCap = 44 * 1024;
 
 template <typename T>
 struct Prec;  // rounding of the search scalars to the probability type, as the reference does
@@ -105,29 +107,91 @@ __device__ float topp_search(F load, int n, float x0, float p_in, float* red, in
   return low;
 }
 
-// Same search with the row in shared memory and 4 elements per access.
+struct Red4 {
+  float s, a, b;
+  int c;
+};
+
+// Block-wide (sum, min, max, count) in one barrier; `buf` = 128 words, alternate two buffers.
 template <int THREADS>
-__device__ float topp_search_smem4(const float* x, int n4, float x0, float p, float* red,
-                                   int32_t* status) {
+__device__ __forceinline__ Red4 block_red4(float s, float a, float b, int c, float* buf) {
+  constexpr int NW = THREADS / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  s = warp_sum(s);
+  a = warp_min(a);
+  b = warp_max(b);
+  c = warp_sum_i(c);
+  if (lane == 0) {
+    buf[warp] = s;
+    buf[32 + warp] = a;
+    buf[64 + warp] = b;
+    reinterpret_cast<int*>(buf)[96 + warp] = c;
+  }
+  __syncthreads();
+  Red4 r;
+  r.s = warp_sum(lane < NW ? buf[lane] : 0.f);
+  r.a = warp_min(lane < NW ? buf[32 + lane] : INFINITY);
+  r.b = warp_max(lane < NW ? buf[64 + lane] : -INFINITY);
+  r.c = warp_sum_i(lane < NW ? reinterpret_cast<int*>(buf)[96 + lane] : 0);
+  return r;
+}
+
+// The same search with the row in shared memory and a shrinking working set.
+//
+// Once `low` has risen, elements <= low can no longer change any of the three reductions of a
+// round: S sums x > mid > low, a = min{x > low}, and b = max({x <= high} U {low}) is at least low
+// anyway.  So whenever a round raises low and few elements remain above it, every warp squeezes
+// its share of the current working set (its slice of the row, later its own segment of the list)
+// into a private segment of `list`, and the following rounds walk the list only.  Ordering inside
+// a segment is fixed by lane order, so results do not depend on scheduling.
+//   x: n floats (n % 4 == 0); list: NW segments of seg_cap floats; red: 256 words.
+template <int THREADS>
+__device__ float topp_search_narrowing(const float* x, int n, float* list, int seg_cap, int* seg_cnt,
+                                       float x0, float p, float* red, int32_t* status) {
+  constexpr int NW = THREADS / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float4* x4 = reinterpret_cast<const float4*>(x);
+  const int n4 = n >> 2;
+  // slice of the row owned by this warp when the row is squeezed for the first time
+  const int slice = ((n + NW - 1) / NW + 31) & ~31;
+  float* const my_seg = list + warp * seg_cap;
+  bool in_list = false;
+  int my_cnt = 0;    // elements in this warp's segment (valid when in_list)
+  int total = n;     // size of the working set
   float low = 0.f, high = x0;
   int round = 0;
   while (true) {
     const float mid = (low + high) * 0.5f;
     float s = 0.f, a = high, b = low;
-    for (int i = threadIdx.x; i < n4; i += THREADS) {
-      const float4 v = x4[i];
-      const float e[4] = {v.x, v.y, v.z, v.w};
+    int c = 0;
+    if (!in_list) {
+      for (int i = threadIdx.x; i < n4; i += THREADS) {
+        const float4 v = x4[i];
+        const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        s += (e[k] > mid) ? e[k] : 0.f;
-        a = (e[k] > low) ? fminf(a, e[k]) : a;
-        b = (e[k] <= high) ? fmaxf(b, e[k]) : b;
+        for (int k = 0; k < 4; ++k) {
+          const bool gt = e[k] > mid;
+          s += gt ? e[k] : 0.f;
+          c += gt ? 1 : 0;
+          a = (e[k] > low) ? fminf(a, e[k]) : a;
+          b = (e[k] <= high) ? fmaxf(b, e[k]) : b;
+        }
+      }
+    } else {
+      for (int i = lane; i < my_cnt; i += 32) {
+        const float e = my_seg[i];
+        const bool gt = e > mid;
+        s += gt ? e : 0.f;
+        c += gt ? 1 : 0;
+        a = (e > low) ? fminf(a, e) : a;
+        b = (e <= high) ? fmaxf(b, e) : b;
       }
     }
-    Red3 r = block_red3<THREADS>(s, a, b, red + (round & 1) * 96);
+    const Red4 r = block_red4<THREADS>(s, a, b, c, red + (round & 1) * 128);
+    bool rose = false;
     if (r.s >= p) {
       low = mid;
+      rose = true;
     } else {
       high = fminf(mid, r.b);
     }
@@ -136,6 +200,43 @@ __device__ float topp_search_smem4(const float* x, int n4, float x0, float p, fl
     if (round >= kSearchRoundCap) {
       if (threadIdx.x == 0) raise_flag(status, TWL_FLAG_ITER_CAP);
       break;
+    }
+    // r.c elements exceed the new low; squeeze when that at least halves the working set and the
+    // segments have room for twice the average share
+    if (rose && 2 * r.c <= total && r.c * 2 <= seg_cap * NW) {
+      int cnt = 0;
+      if (!in_list) {
+        const int begin = warp * slice, end = min(n, begin + slice);
+        for (int i0 = begin; i0 < end; i0 += 32) {
+          const float e = (i0 + lane < end) ? x[i0 + lane] : 0.f;
+          const bool keep = e > low;
+          const unsigned m = __ballot_sync(0xffffffffu, keep);
+          const int pos = cnt + __popc(m & ((1u << lane) - 1));
+          if (keep && pos < seg_cap) my_seg[pos] = e;
+          cnt += __popc(m);
+        }
+      } else {
+        for (int i0 = 0; i0 < my_cnt; i0 += 32) {
+          const float e = (i0 + lane < my_cnt) ? my_seg[i0 + lane] : 0.f;
+          const bool keep = e > low;
+          const unsigned m = __ballot_sync(0xffffffffu, keep);
+          const int pos = cnt + __popc(m & ((1u << lane) - 1));
+          __syncwarp();  // every lane has read its element before the front is overwritten
+          if (keep) my_seg[pos] = e;
+          cnt += __popc(m);
+        }
+      }
+      if (lane == 0) seg_cnt[warp] = cnt;
+      __syncthreads();
+      bool fits = true;
+#pragma unroll 1
+      for (int w = 0; w < NW; ++w) fits = fits && (seg_cnt[w] <= seg_cap);
+      __syncthreads();  // seg_cnt is rewritten by the next squeeze
+      if (fits) {       // (a list-to-list squeeze always fits)
+        in_list = true;
+        my_cnt = cnt;
+        total = r.c;
+      }
     }
   }
   return low;
@@ -213,7 +314,7 @@ struct PruneParams {
   int32_t* out_budget;
   float* out_threshold;
   int32_t* status;
-  int stride, max_k, B, Hq, index_stride;
+  int stride, max_k, B, Hq, index_stride, row_cap, list_cap;
   float top_p_val;
 };
 
@@ -221,9 +322,9 @@ template <int THREADS, bool IN_SMEM>
 __global__ void __launch_bounds__(THREADS)
 topp_prune_kernel(const PruneParams p) {
   extern __shared__ __align__(16) float smem[];
-  float* red = smem;                                  // 192 floats
-  int* wsum = reinterpret_cast<int*>(smem + 192);     // 64 ints
-  float* row = smem + 256;                            // probabilities when IN_SMEM
+  float* red = smem;                                  // 256 words
+  int* wsum = reinterpret_cast<int*>(smem + 256);     // 96 ints: 33 of scan scratch, 32 segment counts
+  float* row = smem + 352;                            // probabilities when IN_SMEM, then the list
   const int r = blockIdx.x;
   const int b = r / p.Hq;
   const bool has_cand = p.cand_pages != nullptr;
@@ -257,25 +358,41 @@ topp_prune_kernel(const PruneParams p) {
   Red3 r1 = block_red3<THREADS>(0.f, 0.f, m, red);
   m = r1.b;
   __syncthreads();
-  // pass 2: exponentials and their sum
+  // pass 2: exponentials and their sum.  exp(s-m) = 2^(s*log2e - m*log2e), one FMA and one
+  // ex2.approx (2 ulp, subnormal results kept so that "probability > 0" means what it says).
+  const float kLog2e = 1.4426950408889634f;
+  const float m2 = m * kLog2e;
+  auto fexp = [&](float sc) -> float {
+    float y;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(fmaf(sc, kLog2e, -m2)));
+    return y;
+  };
   float z = 0.f;
   if (IN_SMEM) {
-    for (int i = threadIdx.x; i < n; i += THREADS) {
-      const float e = expf(row[i] - m);
-      row[i] = e;
-      z += e;
+    float4* r4 = reinterpret_cast<float4*>(row);
+    for (int i = threadIdx.x; i < n / 4; i += THREADS) {
+      float4 v = r4[i];
+      v.x = fexp(v.x); v.y = fexp(v.y); v.z = fexp(v.z); v.w = fexp(v.w);
+      r4[i] = v;
+      z += (v.x + v.y) + (v.z + v.w);
     }
   } else {
-    for (int i = threadIdx.x; i < n; i += THREADS) z += expf(src[i] - m);
+    for (int i = threadIdx.x; i < n; i += THREADS) z += fexp(src[i]);
   }
   Red3 r2 = block_red3<THREADS>(z, 0.f, 0.f, red + 96);
   z = r2.s;
+  const float inv_z = 1.f / z;
   __syncthreads();
   if (IN_SMEM) {
-    for (int i = threadIdx.x; i < n; i += THREADS) row[i] = row[i] / z;
+    float4* r4 = reinterpret_cast<float4*>(row);
+    for (int i = threadIdx.x; i < n / 4; i += THREADS) {
+      float4 v = r4[i];
+      v.x *= inv_z; v.y *= inv_z; v.z *= inv_z; v.w *= inv_z;
+      r4[i] = v;
+    }
     __syncthreads();
   }
-  auto prob = [&](int i) -> float { return IN_SMEM ? row[i] : expf(src[i] - m) / z; };
+  auto prob = [&](int i) -> float { return IN_SMEM ? row[i] : fexp(src[i]) * inv_z; };
   // probability of sequence token 0: slot 0 when page 0 is a candidate, else it is not in the row
   const bool sink_present = has_cand ? (cand[0] == 0) : true;
   const float x0 = sink_present ? prob(0) : 0.f;
@@ -284,43 +401,49 @@ topp_prune_kernel(const PruneParams p) {
   if (top_p > 1.f) {
     low = 0.f;  // no pruning asked for: keep every candidate with non-zero probability
   } else if (IN_SMEM) {
-    low = topp_search_smem4<THREADS>(row, n / 4, x0, top_p, red, p.status);
+    const int seg_cap = ((p.list_cap / (THREADS / 32)) & ~3);
+    low = topp_search_narrowing<THREADS>(row, n, row + p.row_cap, seg_cap, wsum + 40, x0, top_p, red,
+                                         p.status);
   } else {
     low = topp_search<THREADS, float>(prob, n, x0, top_p, red, p.status);
   }
   __syncthreads();
-  // ordered compaction: 4 consecutive slots per thread per tile
+  // ordered compaction: every warp owns a contiguous slice of the row, counts its kept slots,
+  // the warp counts are prefix-summed once, then each warp writes its tokens in order
+  constexpr int NW = THREADS / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int slice = ((n + NW - 1) / NW + 31) & ~31;
+  const int s_begin = warp * slice, s_end = min(n, s_begin + slice);
+  int my_cnt = 0;
+  for (int i0 = s_begin; i0 < s_end; i0 += 32) {
+    const bool keep = (i0 + lane < s_end) && (prob(i0 + lane) > low);
+    my_cnt += __popc(__ballot_sync(0xffffffffu, keep));
+  }
+  if (lane == 0) wsum[warp] = my_cnt;
+  __syncthreads();
+  int inc = lane < NW ? wsum[lane] : 0;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  const int base = __shfl_sync(0xffffffffu, inc, NW - 1);              // kept tokens of the row
+  int off = __shfl_sync(0xffffffffu, inc, warp) - my_cnt;              // exclusive prefix of this warp
   int32_t* out = p.out_indices + (size_t)r * p.index_stride;
-  int base = 0;
-  for (int t0 = 0; t0 < n; t0 += THREADS * 4) {
-    const int i0 = t0 + threadIdx.x * 4;
-    int keep[4], cnt = 0;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      keep[k] = (i0 + k < n) && (prob(i0 + k) > low);
-      cnt += keep[k];
+  for (int i0 = s_begin; i0 < s_end; i0 += 32) {
+    const int i = i0 + lane;
+    const bool keep = (i < s_end) && (prob(i) > low);
+    const unsigned mk = __ballot_sync(0xffffffffu, keep);
+    const int pos = off + __popc(mk & ((1u << lane) - 1));
+    if (keep && pos < p.index_stride) {
+      const int page = has_cand ? cand[i / kPage] : (i / kPage);
+      out[pos] = page * kPage + (i % kPage);
     }
-    int total;
-    int off = base + block_excl_scan<THREADS>(cnt, &total, wsum);
-    if (cnt) {
-      const int page = has_cand ? cand[i0 / kPage] : (i0 / kPage);  // i0 % 4 == 0: one page
-      const int tok0 = page * kPage + (i0 % kPage);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        if (keep[k]) {
-          if (off < p.index_stride) out[off] = tok0 + k;
-          ++off;
-        }
-      }
-    }
-    base += total;
+    off += __popc(mk);
   }
   if (threadIdx.x == 0) {
-    if (base > p.index_stride) {
-      raise_flag(p.status, TWL_FLAG_BAD_INDEX);
-      base = p.index_stride;
-    }
-    p.out_budget[r] = base;
+    if (base > p.index_stride) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+    p.out_budget[r] = min(base, p.index_stride);
     if (p.out_threshold) {
       p.out_threshold[2 * r] = low;
       p.out_threshold[2 * r + 1] = x0;
@@ -330,14 +453,17 @@ topp_prune_kernel(const PruneParams p) {
 
 template <int THREADS>
 static int launch_prune(const PruneParams& p, int rows, int n_max, cudaStream_t st) {
-  if (n_max <= kRowCap) {
-    const size_t smem = (256 + (size_t)n_max) * sizeof(float);
+  if (n_max <= kPruneRowCap) {
+    PruneParams q = p;
+    q.row_cap = (n_max + 3) & ~3;
+    q.list_cap = std::max(q.row_cap / 4, 32 * (THREADS / 32));
+    const size_t smem = (352 + (size_t)q.row_cap + q.list_cap) * sizeof(float);
     auto kern = topp_prune_kernel<THREADS, true>;
     TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<rows, THREADS, smem, st>>>(p);
+    kern<<<rows, THREADS, smem, st>>>(q);
   } else {
     auto kern = topp_prune_kernel<THREADS, false>;
-    kern<<<rows, THREADS, 256 * sizeof(float), st>>>(p);
+    kern<<<rows, THREADS, 352 * sizeof(float), st>>>(p);
   }
   TWL_CHECK_LAUNCH();
   return TWL_OK;
@@ -394,7 +520,10 @@ extern "C" int twl_topp_prune(const float* scores, int32_t score_stride,
   const int n_max = cand_pages ? (int)std::min<int64_t>((int64_t)max_k * kPage, score_stride)
                                : score_stride;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (n_max <= 8192) return launch_prune<256>(p, rows, n_max, st);
-  if (n_max <= 16384) return launch_prune<512>(p, rows, n_max, st);
+  // one block per row; more threads per row when there are too few rows to fill the machine
+  const bool few_rows = rows <= 4 * kNumSMs;
+  if (n_max <= 2048) return launch_prune<256>(p, rows, n_max, st);
+  if (n_max <= 8192) return few_rows ? launch_prune<512>(p, rows, n_max, st) : launch_prune<256>(p, rows, n_max, st);
+  if (n_max <= 16384) return few_rows ? launch_prune<1024>(p, rows, n_max, st) : launch_prune<512>(p, rows, n_max, st);
   return launch_prune<1024>(p, rows, n_max, st);
 }

@@ -77,7 +77,7 @@ class DecodeWorkspace:
     config: SparseConfig
     device: torch.device
     dtype: torch.dtype
-    attn_chunk: int = 256
+    attn_chunk: int = 512
     page_scores: Optional[torch.Tensor] = None
     cand_pages: Optional[torch.Tensor] = None
     cand_npages: Optional[torch.Tensor] = None
@@ -110,7 +110,7 @@ class DecodeWorkspace:
 
     @classmethod
     def for_cache(cls, cache: PagedKVCache, num_q_heads: int, config: SparseConfig,
-                  attn_chunk: int = 256) -> "DecodeWorkspace":
+                  attn_chunk: int = 512) -> "DecodeWorkspace":
         return cls(cache.batch, num_q_heads, cache.max_pages, config, cache.device, cache.dtype,
                    attn_chunk)
 
