@@ -66,6 +66,7 @@ typedef enum {
 #define TWL_HEAD_DIM 128
 #define TWL_QUANT_GROUP 32
 #define TWL_K4_SLAB_BYTES 1280
+#define TWL_STATIC_ATTN_MAX_ROWS 512  /* row limit (batch*query heads) of twl_sparse_decode_attn_static */
 
 TWL_API int twl_version(void);
 TWL_API const char* twl_status_string(int status);
@@ -155,6 +156,27 @@ TWL_API int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pages
                            int32_t num_kv_heads, int32_t num_pages_total, float sm_scale,
                            void* out, void* workspace, size_t workspace_bytes, int32_t chunk,
                            int32_t* status, void* stream);
+
+/* ---- kernel #3 without a caller workspace -------------------------------------------------
+ * No counterpart in the reference.  Same computation and arguments as twl_sparse_decode_attn,
+ * minus workspace/workspace_bytes: the split-KV scratch is a fixed array inside the library
+ * image (about 8.4 MB per GPU that loads the library, kept until the process exits), so this
+ * call performs no device allocation of any kind.  It exists for hosts that cannot allocate
+ * after start-up: a serving process whose memory pool already owns all free device memory, or
+ * a plugin that may only be called where cudaMalloc is forbidden.
+ * Limit: batch*num_q_heads <= TWL_STATIC_ATTN_MAX_ROWS, else TWL_ERR_TOO_LARGE.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ * that device current); make that first call outside any stream capture.
+ * Every call on a device uses the same array: the arrival counters are cleared on `stream` at
+ * the start of each call, the rest is overwritten as needed; two calls whose kernels can overlap
+ * on the GPU (different streams, no ordering between them) race on it and must not be issued. */
+TWL_API int twl_sparse_decode_attn_static(const void* q, int dtype, const void* k_pages,
+                                          const void* v_pages, const int32_t* kv_indptr,
+                                          const int32_t* kv_indices, const int32_t* indices,
+                                          int32_t index_stride, const int32_t* budget,
+                                          int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                          int32_t num_pages_total, float sm_scale, void* out,
+                                          int32_t chunk, int32_t* status, void* stream);
 
 /* ---- cache-append side ------------------------------------------------------------------
  * twl_quantize_k_pages: min/max asymmetric 4-bit quantiser of quantize.py:4-13 applied per

@@ -326,3 +326,92 @@ extern "C" int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pa
   TWL_CHECK_LAUNCH();
   return TWL_OK;
 }
+
+// ---- the same kernel on library-owned scratch ------------------------------------------------
+// Some hosts of this library must not allocate device memory at all once they are up: a serving
+// process that has handed every free byte to its own pool, or a plugin that is only ever called
+// from inside a loop where cudaMalloc is forbidden by policy.  For them the split-KV scratch of
+// the attention kernel lives in the library image itself, sized for at most
+// TWL_STATIC_ATTN_MAX_ROWS (batch * query heads) rows.
+namespace twl {
+
+constexpr size_t kStaticRows = TWL_STATIC_ATTN_MAX_ROWS;
+constexpr size_t kStaticCounterBytes = (kStaticRows * sizeof(int32_t) + 255) / 256 * 256;
+constexpr size_t kStaticMlBytes = (kStaticRows * kMaxChunksPerRow * 2 * sizeof(float) + 255) / 256 * 256;
+constexpr size_t kStaticScratchBytes =
+    kStaticCounterBytes + kStaticMlBytes + kStaticRows * kMaxChunksPerRow * kD * sizeof(float);
+
+// One copy per GPU that loads the library, held until the process exits.  In host code this name
+// is only a handle for cudaGetSymbolAddress; the device address it returns is what kernels get.
+static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_static_attn_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the current device (looked up once per device).
+static int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  TWL_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return TWL_ERR_UNSUPPORTED;
+  void* ptr = __atomic_load_n(&g_static_attn_ptr[dev], __ATOMIC_ACQUIRE);
+  if (ptr == nullptr) {
+    TWL_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_attn_scratch));
+    if (ptr == nullptr) return TWL_ERR_LAUNCH;
+    __atomic_store_n(&g_static_attn_ptr[dev], ptr, __ATOMIC_RELEASE);  // same value from any thread
+  }
+  *out = ptr;
+  return TWL_OK;
+}
+
+}  // namespace twl
+
+extern "C" int twl_sparse_decode_attn_static(const void* q, int dtype, const void* k_pages,
+                                             const void* v_pages, const int32_t* kv_indptr,
+                                             const int32_t* kv_indices, const int32_t* indices,
+                                             int32_t index_stride, const int32_t* budget,
+                                             int32_t batch, int32_t num_q_heads,
+                                             int32_t num_kv_heads, int32_t num_pages_total,
+                                             float sm_scale, void* out, int32_t chunk,
+                                             int32_t* status, void* stream) {
+  using namespace twl;
+  if (!q || !k_pages || !v_pages || !kv_indptr || !kv_indices || !indices || !budget || !out)
+    return TWL_ERR_BAD_ARG;
+  if (batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || index_stride <= 0 ||
+      num_pages_total <= 0 || num_q_heads % num_kv_heads != 0)
+    return TWL_ERR_BAD_ARG;
+  if (chunk <= 0) chunk = 256;
+  if (chunk % 32 != 0) return TWL_ERR_BAD_ARG;
+  if (!aligned(q, 8) || !aligned(k_pages, 16) || !aligned(v_pages, 16) || !aligned(out, 2))
+    return TWL_ERR_MISALIGNED;
+  const size_t rows = (size_t)batch * num_q_heads;
+  if (rows > kStaticRows) return TWL_ERR_TOO_LARGE;  // the built-in scratch holds no more rows
+  if ((int64_t)num_pages_total * num_kv_heads * kPage >= (int64_t)1 << 31) return TWL_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  const int rc = static_scratch_for_current_device(&scratch);
+  if (rc != TWL_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // the array keeps whatever the previous call left: the arrival counters must start at zero
+  TWL_CUDA_TRY(cudaMemsetAsync(scratch, 0, kStaticCounterBytes, st));
+  AttParams p;
+  p.q = q; p.k = k_pages; p.v = v_pages; p.indptr = kv_indptr; p.indices = kv_indices;
+  p.idx = indices; p.budget = budget; p.out = out; p.status = status;
+  char* ws = static_cast<char*>(scratch);
+  p.counters = reinterpret_cast<int32_t*>(ws);
+  p.part_ml = reinterpret_cast<float*>(ws + kStaticCounterBytes);
+  p.part_o = reinterpret_cast<float*>(ws + kStaticCounterBytes + kStaticMlBytes);
+  p.index_stride = index_stride; p.rows = (int)rows; p.Hq = num_q_heads; p.Hkv = num_kv_heads;
+  p.num_pages_total = num_pages_total; p.chunk = chunk; p.sm_scale = sm_scale;
+  const size_t max_items =
+      rows * std::min<size_t>(kMaxChunksPerRow, ((size_t)index_stride + chunk - 1) / chunk);
+  const unsigned grid = (unsigned)std::min<size_t>(max_items, (size_t)kNumSMs * kAttBlocksPerSM);
+  const size_t smem = (rows + 1) * sizeof(int);
+  if (dtype == TWL_F16) {
+    sparse_decode_attn_kernel<__half><<<grid, kAttThreads, smem, st>>>(p);
+  } else if (dtype == TWL_BF16) {
+    sparse_decode_attn_kernel<__nv_bfloat16><<<grid, kAttThreads, smem, st>>>(p);
+  } else {
+    return TWL_ERR_UNSUPPORTED;
+  }
+  TWL_CHECK_LAUNCH();
+  return TWL_OK;
+}

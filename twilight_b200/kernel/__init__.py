@@ -8,6 +8,7 @@ from .ops import (  # noqa: F401
     topp_prune,
     sparse_decode_attn,
     sparse_attn_workspace_bytes,
+    sparse_decode_attn_static,
     quantize_k_pages,
     build_page_meta,
     append_kv,

@@ -216,6 +216,33 @@ def sparse_decode_attn(q, k_pages, v_pages, kv_indptr, kv_indices, indices, budg
     return out
 
 
+STATIC_ATTN_MAX_ROWS = 512
+
+
+def sparse_decode_attn_static(q, k_pages, v_pages, kv_indptr, kv_indices, indices, budget, *,
+                              out: torch.Tensor, sm_scale: Optional[float] = None, chunk: int = 256,
+                              status=None) -> torch.Tensor:
+    """:func:`sparse_decode_attn` on scratch memory that is part of the library itself, for
+    callers that cannot allocate device memory after start-up (a process whose own pool holds all
+    of it, a plugin called where allocation is forbidden).  ``out`` must be supplied; nothing is
+    allocated here or in the library.  At most ``STATIC_ATTN_MAX_ROWS`` (batch x query heads) rows.
+    All calls on a device share one scratch array, so calls that could overlap on the GPU must
+    not be issued; make the first call on a device outside any stream capture."""
+    lib = _lib.load()
+    q = _q3(q)
+    b, hq, _ = q.shape
+    n_total, hkv = k_pages.shape[0], k_pages.shape[1]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(HEAD_DIM)
+    _lib.check(lib.twl_sparse_decode_attn_static(q.data_ptr(), _dtype_code(q), k_pages.data_ptr(),
+                                                 v_pages.data_ptr(), kv_indptr.data_ptr(),
+                                                 kv_indices.data_ptr(), indices.data_ptr(),
+                                                 indices.shape[-1], budget.data_ptr(), b, hq, hkv,
+                                                 n_total, sm_scale, out.data_ptr(), chunk, _p(status),
+                                                 _stream(q.device)), "sparse_decode_attn_static")
+    return out
+
+
 # ---------------------------------------------------------------------------------------------
 # cache-append side
 # ---------------------------------------------------------------------------------------------
