@@ -222,7 +222,7 @@ def main():
         q, cache = layers[i % R]
         out = select_prune_attend_step(q, cache, ws, variant=args.variant)
         if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
+            dist.all_gather_into_tensor(gathered.view(-1, args.heads, 128), out)
 
     def token_step():
         for i in range(args.layers):
@@ -368,7 +368,7 @@ def main():
                 dq.copy_(host_q[i % R], non_blocking=True)
                 out = select_prune_attend_step(dq, layers[i % R][1], ws, variant=args.variant)
                 if world > 1:
-                    dist.all_gather_into_tensor(gathered, out)
+                    dist.all_gather_into_tensor(gathered.view(-1, args.heads, 128), out)
                 host_out.copy_(out, non_blocking=True)
             torch.cuda.synchronize()
 

@@ -113,7 +113,11 @@ TWL_API int twl_quest_topk_pages(const float* page_scores, int32_t max_pages,
  * not written.  score_stride must be a multiple of 16.
  * cand_pages == NULL: every page of the sequence is a candidate (slot == token position),
  * K pages are read once per KV head for its whole query-head group.
- * variant: 0 = library default; 1 = fp32 FMA; 2 = packed-half FMA; 3 = integer dot product. */
+ * variant: arithmetic 0 = library default (3), 1 = fp32 FMA, 2 = packed-half FMA (about 1e-2
+ * off in the logit), 3 = integer dot product; add 16 for the kernel that uses direct 128-bit
+ * global loads, add 128 for the block-wide bulk-copy (TMA) ring even when a row has a single
+ * query head (by default such rows use warp-private 16-byte async copies).  The non-default
+ * variants exist for measurement. */
 TWL_API int twl_estimate_int4(const void* q, int dtype, const uint8_t* k4_pages,
                       const int32_t* kv_indptr, const int32_t* kv_indices,
                       const int32_t* kv_last_page_len, const int32_t* cand_pages,

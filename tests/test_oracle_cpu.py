@@ -166,3 +166,31 @@ def test_decode_step_budget_counts_mask():
     idx = torch.nonzero(r["mask"][0, 0, 0]).flatten().numpy()
     o = O.sparse_attention_fp32(q[0, 0, 0].numpy(), k[0, 0].numpy(), v[0, 0].numpy(), idx, 1 / math.sqrt(128))
     assert np.allclose(o, r["out"][0, 0, 0].numpy(), atol=1e-5)
+
+
+# ---- top-p search vs the reference's own CUDA kernel (masks recorded on a B200) ---------------
+def test_topp_oracle_matches_recorded_reference_kernel_masks():
+    """tests/golden/topp_k1.npz holds the masks TopPReturnMaskKernel (csrc/include/sampling.cuh,
+    compiled unmodified) produced for seeded rows; tests/golden/make_topp_golden.py made it."""
+    import importlib.util
+    from pathlib import Path
+    gold_dir = Path(__file__).resolve().parent / "golden"
+    spec = importlib.util.spec_from_file_location("make_topp_golden", gold_dir / "make_topp_golden.py")
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    data = np.load(gold_dir / "topp_k1.npz")
+    assert [tuple(c) for c in data["cases"].tolist()] == [tuple(float(x) for x in c) for c in gen.CASES]
+    total_diff = 0
+    for i, (seed, rows, L, std, boost, p) in enumerate(gen.CASES):
+        probs = gen.make_probs(seed, rows, L, std, boost).numpy()
+        k1 = np.unpackbits(data[f"mask_{i}"], axis=1)[:, :L].astype(bool)
+        assert (k1.sum(1) == data[f"budget_{i}"]).all()
+        for r in range(rows):
+            low, _ = O.top_p_search(probs[r], p)
+            mine = probs[r] > low
+            bad = np.nonzero(mine != k1[r])[0]
+            # block-reduce summation order is the only freedom: differences sit at the threshold
+            assert (np.abs(probs[r][bad] - low) <= 1e-4).all()
+            total_diff += bad.size
+            assert k1[r][0]                                  # the sink is always kept
+    assert total_diff <= 8

@@ -34,7 +34,7 @@ struct EstParams {
   const int32_t* cand_npages;
   float* scores;
   int32_t* status;
-  int max_k, B, Hq, Hkv, num_pages_total, stride, pages_per_block, debug;
+  int max_k, B, Hq, Hkv, num_pages_total, stride, pages_per_block, force_ring;
   float sm_scale;
 };
 
@@ -443,11 +443,11 @@ estimate_int4_tma_kernel(const EstParams p) {
         if (!ok) break;
         const int pg0 = st * kStagePages, pg1 = min(n_here, pg0 + kStagePages);
         uint32_t bytes = 0;
-        for (int pg = pg0; pg < pg1; ++pg) bytes += (sm_phys[pg] >= 0 && !(p.debug & 2)) ? kSlab : 0;
+        for (int pg = pg0; pg < pg1; ++pg) bytes += sm_phys[pg] >= 0 ? kSlab : 0;
         mbar_arrive_expect_tx(&sm_full[slot], bytes);
         for (int pg = pg0; pg < pg1; ++pg) {
           const int phys = sm_phys[pg];
-          if (phys >= 0 && !(p.debug & 2))
+          if (phys >= 0)
             bulk_copy_g2s(sm_ring + ((size_t)slot * kStagePages + (pg - pg0)) * kSlab,
                           p.k4 + ((size_t)phys * p.Hkv + kvh) * kSlab, kSlab, &sm_full[slot]);
         }
@@ -479,7 +479,7 @@ estimate_int4_tma_kernel(const EstParams p) {
     const int pg0 = st * kStagePages;
     const int n_steps = (min(n_here, pg0 + kStagePages) - pg0) * 2;
     const uint8_t* stage = sm_ring + (size_t)slot * kStagePages * kSlab;
-    for (int s = warp; s < n_steps && !(p.debug & 1); s += kEstWarps) {
+    for (int s = warp; s < n_steps; s += kEstWarps) {
       const int pgl = s >> 1, half = s & 1;
       const int pg = pg0 + pgl;
       const bool present = sm_phys[pg] >= 0;
@@ -671,7 +671,7 @@ static int launch_one(const EstParams& p, int rows, int max_row_pages, bool ldg,
   if (ldg) {
     dim3 grid((max_row_pages + kPagesPerBlock - 1) / kPagesPerBlock, rows);
     estimate_int4_kernel<T, G, VARIANT><<<grid, kEstThreads, 0, st>>>(p);
-  } else if (G == 1 && !(p.debug & 4)) {
+  } else if (G == 1 && !p.force_ring) {
     constexpr int kBytes = kEstWarps * kRingDepth * kWarpStageBytes;
     auto kern = estimate_int4_warp_kernel<T, VARIANT>;
     TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
@@ -705,8 +705,9 @@ static int launch_variant(const EstParams& p, bool has_cand, int max_row_pages, 
 template <typename T>
 static int launch_dtype(const EstParams& p, bool has_cand, int max_row_pages, int variant,
                         cudaStream_t st) {
-  const_cast<EstParams&>(p).debug = (variant >> 5) & 7;
-  const bool ldg = (variant & 16) != 0;  // +16: direct global loads instead of the staged ring
+  // +16: direct global loads; +128: the block-wide bulk-copy ring even for a single query head
+  const_cast<EstParams&>(p).force_ring = (variant & 128) != 0;
+  const bool ldg = (variant & 16) != 0;
   switch (variant & 15) {
     case VAR_F32: return launch_variant<T, VAR_F32>(p, has_cand, max_row_pages, ldg, st);
     case VAR_H2: return launch_variant<T, VAR_H2>(p, has_cand, max_row_pages, ldg, st);
