@@ -107,43 +107,26 @@ __device__ float topp_search(F load, int n, float x0, float p_in, float* red, in
   return low;
 }
 
-struct Red4 {
-  float s, a, b;
-  int c;
-};
-
-// Block-wide (sum, min, max, count) in one barrier; `buf` = 128 words, alternate two buffers.
-template <int THREADS>
-__device__ __forceinline__ Red4 block_red4(float s, float a, float b, int c, float* buf) {
-  constexpr int NW = THREADS / 32;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  s = warp_sum(s);
-  a = warp_min(a);
-  b = warp_max(b);
-  c = warp_sum_i(c);
-  if (lane == 0) {
-    buf[warp] = s;
-    buf[32 + warp] = a;
-    buf[64 + warp] = b;
-    reinterpret_cast<int*>(buf)[96 + warp] = c;
+// Warp-wide inclusive prefix sum of one int per lane.
+__device__ __forceinline__ int warp_incl_scan(int v) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += t;
   }
-  __syncthreads();
-  Red4 r;
-  r.s = warp_sum(lane < NW ? buf[lane] : 0.f);
-  r.a = warp_min(lane < NW ? buf[32 + lane] : INFINITY);
-  r.b = warp_max(lane < NW ? buf[64 + lane] : -INFINITY);
-  r.c = warp_sum_i(lane < NW ? reinterpret_cast<int*>(buf)[96 + lane] : 0);
-  return r;
+  return v;
 }
 
 // The same search with the row in shared memory and a shrinking working set.
 //
 // Once `low` has risen, elements <= low can no longer change any of the three reductions of a
 // round: S sums x > mid > low, a = min{x > low}, and b = max({x <= high} U {low}) is at least low
-// anyway.  So whenever a round raises low and few elements remain above it, every warp squeezes
-// its share of the current working set (its slice of the row, later its own segment of the list)
-// into a private segment of `list`, and the following rounds walk the list only.  Ordering inside
-// a segment is fixed by lane order, so results do not depend on scheduling.
+// anyway.  So whenever a round raises low, every warp squeezes its share of the current working
+// set (its slice of the row, later its own segment of the list) into a private segment of `list`
+// and the following rounds walk the list only; a squeeze whose survivors do not fit is dropped and
+// the search goes on over the old set.  Ordering inside a segment is fixed by lane order, so
+// results do not depend on scheduling.
 //   x: n floats (n % 4 == 0); list: NW segments of seg_cap floats; red: 256 words.
 template <int THREADS>
 __device__ float topp_search_narrowing(const float* x, int n, float* list, int seg_cap, int* seg_cnt,
@@ -152,8 +135,8 @@ __device__ float topp_search_narrowing(const float* x, int n, float* list, int s
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float4* x4 = reinterpret_cast<const float4*>(x);
   const int n4 = n >> 2;
-  // slice of the row owned by this warp when the row is squeezed for the first time
-  const int slice = ((n + NW - 1) / NW + 31) & ~31;
+  // slice of the row owned by this warp when the row is squeezed (whole float4 groups per lane)
+  const int slice = ((n + NW - 1) / NW + 127) & ~127;
   float* const my_seg = list + warp * seg_cap;
   bool in_list = false;
   int my_cnt = 0;    // elements in this warp's segment (valid when in_list)
@@ -163,16 +146,13 @@ __device__ float topp_search_narrowing(const float* x, int n, float* list, int s
   while (true) {
     const float mid = (low + high) * 0.5f;
     float s = 0.f, a = high, b = low;
-    int c = 0;
     if (!in_list) {
       for (int i = threadIdx.x; i < n4; i += THREADS) {
         const float4 v = x4[i];
         const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const bool gt = e[k] > mid;
-          s += gt ? e[k] : 0.f;
-          c += gt ? 1 : 0;
+          s += (e[k] > mid) ? e[k] : 0.f;
           a = (e[k] > low) ? fminf(a, e[k]) : a;
           b = (e[k] <= high) ? fmaxf(b, e[k]) : b;
         }
@@ -180,14 +160,12 @@ __device__ float topp_search_narrowing(const float* x, int n, float* list, int s
     } else {
       for (int i = lane; i < my_cnt; i += 32) {
         const float e = my_seg[i];
-        const bool gt = e > mid;
-        s += gt ? e : 0.f;
-        c += gt ? 1 : 0;
+        s += (e > mid) ? e : 0.f;
         a = (e > low) ? fminf(a, e) : a;
         b = (e <= high) ? fmaxf(b, e) : b;
       }
     }
-    const Red4 r = block_red4<THREADS>(s, a, b, c, red + (round & 1) * 128);
+    const Red3 r = block_red3<THREADS>(s, a, b, red + (round & 1) * 96);
     bool rose = false;
     if (r.s >= p) {
       low = mid;
@@ -201,19 +179,28 @@ __device__ float topp_search_narrowing(const float* x, int n, float* list, int s
       if (threadIdx.x == 0) raise_flag(status, TWL_FLAG_ITER_CAP);
       break;
     }
-    // r.c elements exceed the new low; squeeze when that at least halves the working set and the
-    // segments have room for twice the average share
-    if (rose && 2 * r.c <= total && r.c * 2 <= seg_cap * NW) {
+    if (rose && total > 32) {
       int cnt = 0;
       if (!in_list) {
         const int begin = warp * slice, end = min(n, begin + slice);
-        for (int i0 = begin; i0 < end; i0 += 32) {
-          const float e = (i0 + lane < end) ? x[i0 + lane] : 0.f;
-          const bool keep = e > low;
-          const unsigned m = __ballot_sync(0xffffffffu, keep);
-          const int pos = cnt + __popc(m & ((1u << lane) - 1));
-          if (keep && pos < seg_cap) my_seg[pos] = e;
-          cnt += __popc(m);
+        for (int i0 = begin; i0 < end; i0 += 128) {
+          const int i = i0 + lane * 4;
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (i < end) v = *reinterpret_cast<const float4*>(x + i);  // n % 4 == 0: whole groups
+          const float e[4] = {v.x, v.y, v.z, v.w};
+          int c = 0;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) c += e[k] > low ? 1 : 0;
+          const int inc = warp_incl_scan(c);
+          int pos = cnt + inc - c;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (e[k] > low) {
+              if (pos < seg_cap) my_seg[pos] = e[k];
+              ++pos;
+            }
+          }
+          cnt += __shfl_sync(0xffffffffu, inc, 31);
         }
       } else {
         for (int i0 = 0; i0 < my_cnt; i0 += 32) {
@@ -229,13 +216,18 @@ __device__ float topp_search_narrowing(const float* x, int n, float* list, int s
       if (lane == 0) seg_cnt[warp] = cnt;
       __syncthreads();
       bool fits = true;
+      int sum = 0;
 #pragma unroll 1
-      for (int w = 0; w < NW; ++w) fits = fits && (seg_cnt[w] <= seg_cap);
+      for (int w = 0; w < NW; ++w) {
+        const int cw = seg_cnt[w];
+        fits = fits && (cw <= seg_cap);
+        sum += cw;
+      }
       __syncthreads();  // seg_cnt is rewritten by the next squeeze
       if (fits) {       // (a list-to-list squeeze always fits)
         in_list = true;
         my_cnt = cnt;
-        total = r.c;
+        total = sum;
       }
     }
   }
@@ -412,34 +404,71 @@ topp_prune_kernel(const PruneParams p) {
   // the warp counts are prefix-summed once, then each warp writes its tokens in order
   constexpr int NW = THREADS / 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int slice = ((n + NW - 1) / NW + 31) & ~31;
+  const int slice = ((n + NW - 1) / NW + 127) & ~127;
   const int s_begin = warp * slice, s_end = min(n, s_begin + slice);
-  int my_cnt = 0;
-  for (int i0 = s_begin; i0 < s_end; i0 += 32) {
-    const bool keep = (i0 + lane < s_end) && (prob(i0 + lane) > low);
-    my_cnt += __popc(__ballot_sync(0xffffffffu, keep));
-  }
-  if (lane == 0) wsum[warp] = my_cnt;
-  __syncthreads();
-  int inc = lane < NW ? wsum[lane] : 0;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int t = __shfl_up_sync(0xffffffffu, inc, o);
-    if (lane >= o) inc += t;
-  }
-  const int base = __shfl_sync(0xffffffffu, inc, NW - 1);              // kept tokens of the row
-  int off = __shfl_sync(0xffffffffu, inc, warp) - my_cnt;              // exclusive prefix of this warp
   int32_t* out = p.out_indices + (size_t)r * p.index_stride;
-  for (int i0 = s_begin; i0 < s_end; i0 += 32) {
-    const int i = i0 + lane;
-    const bool keep = (i < s_end) && (prob(i) > low);
-    const unsigned mk = __ballot_sync(0xffffffffu, keep);
-    const int pos = off + __popc(mk & ((1u << lane) - 1));
-    if (keep && pos < p.index_stride) {
-      const int page = has_cand ? cand[i / kPage] : (i / kPage);
-      out[pos] = page * kPage + (i % kPage);
+  int base;
+  if (IN_SMEM) {
+    // four consecutive slots per lane (n is a multiple of 16, so groups never straddle the end)
+    int my_cnt = 0;
+    for (int i0 = s_begin; i0 < s_end; i0 += 128) {
+      const int i = i0 + lane * 4;
+      if (i < s_end) {
+        const float4 v = *reinterpret_cast<const float4*>(row + i);
+        my_cnt += (v.x > low) + (v.y > low) + (v.z > low) + (v.w > low);
+      }
     }
-    off += __popc(mk);
+    my_cnt = warp_sum_i(my_cnt);
+    if (lane == 0) wsum[warp] = my_cnt;
+    __syncthreads();
+    const int inc_w = warp_incl_scan(lane < NW ? wsum[lane] : 0);
+    base = __shfl_sync(0xffffffffu, inc_w, NW - 1);                // kept tokens of the row
+    int off = __shfl_sync(0xffffffffu, inc_w, warp) - my_cnt;      // exclusive prefix of this warp
+    for (int i0 = s_begin; i0 < s_end; i0 += 128) {
+      const int i = i0 + lane * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < s_end) v = *reinterpret_cast<const float4*>(row + i);
+      const float e[4] = {v.x, v.y, v.z, v.w};
+      int c = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) c += e[k] > low ? 1 : 0;   // absent groups hold 0 and low >= 0
+      const int inc = warp_incl_scan(c);
+      if (c) {
+        const int page = has_cand ? cand[i / kPage] : (i / kPage);  // i % 4 == 0: one page
+        const int tok0 = page * kPage + (i % kPage);
+        int pos = off + inc - c;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (e[k] > low) {
+            if (pos < p.index_stride) out[pos] = tok0 + k;
+            ++pos;
+          }
+        }
+      }
+      off += __shfl_sync(0xffffffffu, inc, 31);
+    }
+  } else {
+    int my_cnt = 0;
+    for (int i0 = s_begin; i0 < s_end; i0 += 32) {
+      const bool keep = (i0 + lane < s_end) && (prob(i0 + lane) > low);
+      my_cnt += __popc(__ballot_sync(0xffffffffu, keep));
+    }
+    if (lane == 0) wsum[warp] = my_cnt;
+    __syncthreads();
+    const int inc_w = warp_incl_scan(lane < NW ? wsum[lane] : 0);
+    base = __shfl_sync(0xffffffffu, inc_w, NW - 1);
+    int off = __shfl_sync(0xffffffffu, inc_w, warp) - my_cnt;
+    for (int i0 = s_begin; i0 < s_end; i0 += 32) {
+      const int i = i0 + lane;
+      const bool keep = (i < s_end) && (prob(i) > low);
+      const unsigned mk = __ballot_sync(0xffffffffu, keep);
+      const int pos = off + __popc(mk & ((1u << lane) - 1));
+      if (keep && pos < p.index_stride) {
+        const int page = has_cand ? cand[i / kPage] : (i / kPage);
+        out[pos] = page * kPage + (i % kPage);
+      }
+      off += __popc(mk);
+    }
   }
   if (threadIdx.x == 0) {
     if (base > p.index_stride) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
@@ -520,10 +549,12 @@ extern "C" int twl_topp_prune(const float* scores, int32_t score_stride,
   const int n_max = cand_pages ? (int)std::min<int64_t>((int64_t)max_k * kPage, score_stride)
                                : score_stride;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  // one block per row; more threads per row when there are too few rows to fill the machine
-  const bool few_rows = rows <= 4 * kNumSMs;
+  // one block per row.  More threads per row shorten a row's latency, but only pay while all rows
+  // still run at the same time (3 blocks of 512 threads per SM, 6 of 256): a second wave costs more
+  const bool one_wave_512 = rows <= 3 * kNumSMs;
+  const bool one_wave_1024 = rows <= kNumSMs;
   if (n_max <= 2048) return launch_prune<256>(p, rows, n_max, st);
-  if (n_max <= 8192) return few_rows ? launch_prune<512>(p, rows, n_max, st) : launch_prune<256>(p, rows, n_max, st);
-  if (n_max <= 16384) return few_rows ? launch_prune<1024>(p, rows, n_max, st) : launch_prune<512>(p, rows, n_max, st);
+  if (n_max <= 8192) return one_wave_512 ? launch_prune<512>(p, rows, n_max, st) : launch_prune<256>(p, rows, n_max, st);
+  if (n_max <= 16384) return one_wave_1024 ? launch_prune<1024>(p, rows, n_max, st) : launch_prune<512>(p, rows, n_max, st);
   return launch_prune<1024>(p, rows, n_max, st);
 }
