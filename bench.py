@@ -394,12 +394,15 @@ def main():
         seqs = min(8, args.batch)
         data = cpu_reference_inputs(args, args.heads, seqs)
         cpu_reference_step(args, data[:1])
-        t = cpu_reference_step(args, data)
+        times = []
+        while sum(times) < 12.0 and len(times) < 20:
+            times.append(cpu_reference_step(args, data))
+        t = statistics.mean(times)
         cpu_baseline = {"value": seqs / (t * args.layers), "unit": "tokens/s", "cores": torch.get_num_threads(),
                         "kind": "port",
-                        "sample": f"1 of {args.layers} layer passes over {seqs} of {args.batch} sequences x "
-                                  f"{args.heads} heads at ctx {args.ctx} ({t:.1f} s of CPU work); tokens/s = "
-                                  f"sequences / (time x layers)"}
+                        "sample": f"{len(times)} x (1 of {args.layers} layer passes over {seqs} of {args.batch} "
+                                  f"sequences x {args.heads} heads at ctx {args.ctx}), {sum(times):.1f} s of CPU "
+                                  f"work; tokens/s = sequences / (mean pass time x layers)"}
 
     if rank == 0:
         line = {

@@ -29,11 +29,13 @@ struct ScoreParams {
 template <typename T, int G>
 __global__ void __launch_bounds__(kSelThreads)
 quest_page_scores_kernel(const ScoreParams p) {
-  const int row = blockIdx.y;  // (b, kv head)
+  // blocks that run side by side take the same pages of different KV heads: their 512-byte slabs
+  // are neighbours inside one 512*H_kv-byte page record, which keeps DRAM rows open
+  const int row = blockIdx.x;  // (b, kv head), kv head fastest
   const int b = row / p.Hkv, kvh = row % p.Hkv;
   const int page_base = p.indptr[b];
   const int n_pages = min(p.indptr[b + 1] - page_base, p.max_pages);
-  const int first = blockIdx.x * kSelPagesPerBlock;
+  const int first = blockIdx.y * kSelPagesPerBlock;
   if (first >= n_pages) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane & 7, pg_in_step = lane >> 3;
@@ -56,53 +58,73 @@ quest_page_scores_kernel(const ScoreParams p) {
     }
   }
 
-  const int last = min(first + kSelPagesPerBlock, n_pages);
-  for (int lp0 = first + warp * 4; lp0 < last; lp0 += (kSelThreads / 32) * 4) {
-    const int lp = lp0 + pg_in_step;
-    const bool live = lp < last;
-    uint4 mn[2], mx[2];
-    bool ok = false;
-    if (live) {
-      const int phys = p.indices[page_base + lp];
-      ok = phys >= 0 && phys < p.num_pages_total;
-      if (ok) {
-        const T* slab = reinterpret_cast<const T*>(p.kmeta) + ((size_t)phys * p.Hkv + kvh) * 2 * kD;
-#pragma unroll
-        for (int part = 0; part < 2; ++part) {
-          mn[part] = ldg_stream_u4(reinterpret_cast<const uint4*>(slab) + sub + 8 * part);
-          mx[part] = ldg_stream_u4(reinterpret_cast<const uint4*>(slab + kD) + sub + 8 * part);
-        }
-      } else {
+  // physical page ids of the block's pages go to shared memory first, so that the streaming loop
+  // has no dependent index loads
+  __shared__ int sm_phys[kSelPagesPerBlock];
+  const int n_here = min(kSelPagesPerBlock, n_pages - first);
+  if (threadIdx.x < kSelPagesPerBlock) {
+    int phys = -1;
+    if ((int)threadIdx.x < n_here) {
+      phys = p.indices[page_base + first + threadIdx.x];
+      if (phys < 0 || phys >= p.num_pages_total) {
+        phys = -1;
         raise_flag(p.status, TWL_FLAG_BAD_INDEX);
       }
     }
-    float acc[G];
+    sm_phys[threadIdx.x] = phys;
+  }
+  __syncthreads();
+
+  constexpr int kU = 1;  // page quads in flight per warp (2 was measured slower)
+  for (int l0 = warp * 4; l0 < n_here; l0 += (kSelThreads / 32) * 4 * kU) {
+    uint4 mn[kU][2], mx[kU][2];
+    bool ok[kU], live[kU];
 #pragma unroll
-    for (int g = 0; g < G; ++g) acc[g] = 0.f;
-    if (ok) {
+    for (int u = 0; u < kU; ++u) {
+      const int l = l0 + u * (kSelThreads / 32) * 4 + pg_in_step;
+      live[u] = l < n_here;
+      const int phys = live[u] ? sm_phys[l] : -1;
+      ok[u] = phys >= 0;
+      if (ok[u]) {
+        const T* slab = reinterpret_cast<const T*>(p.kmeta) + ((size_t)phys * p.Hkv + kvh) * 2 * kD;
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        const uint32_t un[4] = {mn[part].x, mn[part].y, mn[part].z, mn[part].w};
-        const uint32_t ux[4] = {mx[part].x, mx[part].y, mx[part].z, mx[part].w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float2 lo = Elem<T>::to_f2(un[k]), hi = Elem<T>::to_f2(ux[k]);
-#pragma unroll
-          for (int g = 0; g < G; ++g) {
-            const float q0 = qf[g][8 * part + 2 * k], q1 = qf[g][8 * part + 2 * k + 1];
-            acc[g] += fmaxf(q0 * hi.x, q0 * lo.x);
-            acc[g] += fmaxf(q1 * hi.y, q1 * lo.y);
-          }
+        for (int part = 0; part < 2; ++part) {
+          mn[u][part] = ldg_stream_u4(reinterpret_cast<const uint4*>(slab) + sub + 8 * part);
+          mx[u][part] = ldg_stream_u4(reinterpret_cast<const uint4*>(slab + kD) + sub + 8 * part);
         }
       }
     }
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 1);
-      acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 2);
-      acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 4);
-      if (live && (g & 7) == sub)
-        p.page_scores[(size_t)(b * p.Hq + h0 + g) * p.max_pages + lp] = ok ? acc[g] : -INFINITY;
+    for (int u = 0; u < kU; ++u) {
+      const int lp = first + l0 + u * (kSelThreads / 32) * 4 + pg_in_step;
+      float acc[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) acc[g] = 0.f;
+      if (ok[u]) {
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          const uint32_t un[4] = {mn[u][part].x, mn[u][part].y, mn[u][part].z, mn[u][part].w};
+          const uint32_t ux[4] = {mx[u][part].x, mx[u][part].y, mx[u][part].z, mx[u][part].w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 lo = Elem<T>::to_f2(un[k]), hi = Elem<T>::to_f2(ux[k]);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              const float q0 = qf[g][8 * part + 2 * k], q1 = qf[g][8 * part + 2 * k + 1];
+              acc[g] += fmaxf(q0 * hi.x, q0 * lo.x);
+              acc[g] += fmaxf(q1 * hi.y, q1 * lo.y);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 1);
+        acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 2);
+        acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 4);
+        if (live[u] && (g & 7) == sub)
+          p.page_scores[(size_t)(b * p.Hq + h0 + g) * p.max_pages + lp] = ok[u] ? acc[g] : -INFINITY;
+      }
     }
   }
 }
@@ -222,8 +244,9 @@ quest_topk_pages_kernel(const float* __restrict__ page_scores, int max_pages,
 template <typename T, int G>
 static int launch_scores(const ScoreParams& p, cudaStream_t st) {
   const int rows = p.B * p.Hkv;
-  if (rows > 65535) return TWL_ERR_TOO_LARGE;
-  dim3 grid((p.max_pages + kSelPagesPerBlock - 1) / kSelPagesPerBlock, rows);
+  const int chunks = (p.max_pages + kSelPagesPerBlock - 1) / kSelPagesPerBlock;
+  if (chunks > 65535) return TWL_ERR_TOO_LARGE;
+  dim3 grid(rows, chunks);
   quest_page_scores_kernel<T, G><<<grid, kSelThreads, 0, st>>>(p);
   TWL_CHECK_LAUNCH();
   return TWL_OK;
