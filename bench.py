@@ -36,7 +36,7 @@ METRIC = "sparse decode attn tokens/s/GPU @32k ctx; % HBM roofline; avg pruned b
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=16)
@@ -74,7 +74,7 @@ class ClockSampler:
             f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
             self.path = f.name
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=f, stderr=subprocess.DEVNULL)
+                                          "-i", str(self.index), "-lms", "20"], stdout=f, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
@@ -346,10 +346,17 @@ def main():
     peak = float(peaks.get("hbm_gbs", 6650.0))
     peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
     dom_bytes = kbytes.get(dominant, 0.0)
+    # DRAM traffic per (sequence, KV head) row from the ncu capture summarised in
+    # profiles/kernels_config1_small_case_ncu_full.md (256 rows; traffic is proportional to rows);
+    # only valid for the configuration that capture was taken on
+    ncu_bytes_per_row = {"quest_page_scores": 276.33e6 / 256, "estimate_int4": 176.96e6 / 256}
+    traffic = None
+    if (args.ctx, args.token_budget, args.heads, args.kv_heads) == (32768, 8192, 32, 32) and dominant in ncu_bytes_per_row:
+        traffic = ncu_bytes_per_row[dominant] * args.batch * args.kv_heads
     achieved = dom_bytes / (kavg[dominant] * 1e-3) / 1e9 if dom_bytes else 0.0
     step_gbs = bytes_["total"] * args.layers / (ms_per_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
+                "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": traffic,
                 "algorithmic_bytes_per_launch": dom_bytes,
                 "kernels_ms": {k: round(v, 5) for k, v in kavg.items()},
                 "kernels_gbs": {k: round(kbytes[k] / (kavg[k] * 1e-3) / 1e9, 1) for k in kbytes},
