@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--recipe", default="literal", choices=["literal", "mid", "calibrated"])
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--gather-per-layer", action="store_true",
+                    help="all-gather the outputs after every layer pass instead of once per decoded token")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--kernel-reps", type=int, default=5)
@@ -173,12 +175,23 @@ def workload_config(args, n):
                         f"{args.layers} layers/token",
             "global_batch": args.batch * n, "seq_len": args.ctx, "parallelism": f"(batch,kv-head) shards x{n}",
             "recipe": args.recipe, "resident_layers": args.resident_layers,
+            "output_gather": "none (1 GPU)" if n == 1 else ("NCCL all-gather per layer pass" if args.gather_per_layer
+                                                             else "one NCCL all-gather per decoded token"),
             "l2": "inputs larger than L2: each layer pass streams >0.8 GB and layers alternate"}
 
 
 # ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
+_T0 = time.time()
+
+
+def log(msg):
+    """Progress lines on stderr (every rank), so that a stalled multi-rank run shows where it is."""
+    sys.stderr.write(f"[bench r{os.environ.get('RANK', '0')} +{time.time() - _T0:6.1f}s] {msg}\n")
+    sys.stderr.flush()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -203,6 +216,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+        log("process group up")
 
     cfg = SparseConfig(selector="quest", token_budget=args.token_budget, weight_pruner="top_p",
                        threshold=args.top_p)
@@ -213,20 +227,28 @@ def main():
                                       dtype=torch.bfloat16, device=dev, seed=1000 * rank + l,
                                       recipe=args.recipe, shuffle_pages=True)
         layers.append((q, cache))
+    log(f"{R} resident layers generated")
     ws = DecodeWorkspace.for_cache(layers[0][1], args.heads, cfg)
-    gathered = None
+    # Outputs of all layer passes of one token.  A rank's heads feed its own slice of the output
+    # projection, so nothing has to cross GPUs between layers; the per-token result is gathered
+    # once (NCCL all-gather), or after every layer pass with --gather-per-layer.
+    outs = torch.empty(args.layers, args.batch, args.heads, 128, dtype=torch.bfloat16, device=dev)
+    gathered = gathered_all = None
     if world > 1:
         gathered = torch.empty(world, args.batch, args.heads, 128, dtype=torch.bfloat16, device=dev)
+        gathered_all = torch.empty(world, args.layers, args.batch, args.heads, 128, dtype=torch.bfloat16, device=dev)
 
     def layer_pass(i):
         q, cache = layers[i % R]
-        out = select_prune_attend_step(q, cache, ws, variant=args.variant)
-        if world > 1:
+        out = select_prune_attend_step(q, cache, ws, variant=args.variant, out=outs[i % args.layers])
+        if world > 1 and args.gather_per_layer:
             dist.all_gather_into_tensor(gathered.view(-1, args.heads, 128), out)
 
     def token_step():
         for i in range(args.layers):
             layer_pass(i)
+        if world > 1 and not args.gather_per_layer:
+            dist.all_gather_into_tensor(gathered_all.view(-1, args.batch, args.heads, 128), outs)
 
     # one eager step (also sets function attributes before any capture)
     token_step()
@@ -239,6 +261,7 @@ def main():
         budgets.append(ws.budget.clone())
     avg_budget = float(torch.stack(budgets).float().mean().item())
 
+    log(f"eager step done, avg budget {avg_budget:.1f}")
     graph = None
     if not args.no_graph:
         try:
@@ -254,6 +277,7 @@ def main():
             sys.stderr.write(f"[bench] CUDA graph capture failed ({e}); timing eager launches\n")
             graph = None
     run_step = graph.replay if graph is not None else token_step
+    log(f"graph captured: {graph is not None}")
 
     def barrier():
         if world > 1:
@@ -279,6 +303,7 @@ def main():
         t = torch.tensor([elapsed_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed_ms = float(t.item())
+    log("timed region done")
     ms_per_step = elapsed_ms / args.steps
     value = args.batch * world / (ms_per_step * 1e-3)
 
@@ -363,6 +388,7 @@ def main():
                 "step": {"algorithmic_bytes_per_layer_pass": bytes_["total"], "achieved": step_gbs,
                          "frac": step_gbs / peak, "frac_of_8000_nominal": step_gbs / 8000.0}}
 
+    log("per-kernel timing done")
     # ---- end to end: q from pinned host memory in, output to pinned host memory out ------------
     e2e = None
     if not args.no_e2e:
@@ -373,10 +399,12 @@ def main():
         def e2e_step():
             for i in range(args.layers):
                 dq.copy_(host_q[i % R], non_blocking=True)
-                out = select_prune_attend_step(dq, layers[i % R][1], ws, variant=args.variant)
-                if world > 1:
+                out = select_prune_attend_step(dq, layers[i % R][1], ws, variant=args.variant, out=outs[i])
+                if world > 1 and args.gather_per_layer:
                     dist.all_gather_into_tensor(gathered.view(-1, args.heads, 128), out)
                 host_out.copy_(out, non_blocking=True)
+            if world > 1 and not args.gather_per_layer:
+                dist.all_gather_into_tensor(gathered_all.view(-1, args.batch, args.heads, 128), outs)
             torch.cuda.synchronize()
 
         for _ in range(3):
@@ -423,7 +451,15 @@ def main():
         }
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # A captured graph that holds NCCL kernels made communicator teardown stall at exit; the
+        # result is out, so synchronise, release the graph and leave without the teardown.
+        sys.stdout.flush()
+        torch.cuda.synchronize()
+        dist.barrier()
+        if graph is not None:
+            graph.reset()
+        log("done")
+        os._exit(0)
 
 
 if __name__ == "__main__":

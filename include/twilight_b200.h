@@ -104,6 +104,16 @@ TWL_API int twl_quest_topk_pages(const float* page_scores, int32_t max_pages,
                          int32_t token_budget, int32_t* cand_pages, int32_t* cand_npages,
                          int32_t max_k, void* stream);
 
+/* Both steps in one launch: the block that finishes the scores of a (batch, kv-head) row last
+ * (an atomic ticket, nobody waits) picks that row's pages.  counters: int32[batch*num_kv_heads],
+ * zero on entry, left zero.  Same results as the two calls above. */
+TWL_API int twl_quest_select(const void* q, int dtype, const void* kmeta, const int32_t* kv_indptr,
+                             const int32_t* kv_indices, int32_t batch, int32_t num_q_heads,
+                             int32_t num_kv_heads, int32_t num_pages_total, int32_t token_budget,
+                             float* page_scores, int32_t max_pages, int32_t* cand_pages,
+                             int32_t* cand_npages, int32_t max_k, int32_t* counters,
+                             int32_t* status, void* stream);
+
 /* ---- kernel #1: INT4 K-cache q.k estimator --------------------------------------------
  * Replaces the estimator of twilight/pyimpl/attention.py:247-255 (with quantize.py:4-13
  * applied once at cache-append time) and the absent ftka op batched_sparse_gemv_int4_k
@@ -140,6 +150,17 @@ TWL_API int twl_topp_prune(const float* scores, int32_t score_stride, const int3
                    int32_t num_q_heads, const float* top_p_arr, float top_p_val,
                    int32_t* out_indices, int32_t index_stride, int32_t* out_budget,
                    float* out_threshold, int32_t* status, void* stream);
+
+/* Element-wise threshold pruner on the same scores, replacing elementwise_threshold of
+ * twilight/pyimpl/elementwise_threshold.py:9-18: a candidate is kept when its score exceeds
+ * (score of sequence token 0) - threshold; when token 0 is not a candidate every candidate is
+ * kept.  Outputs as for twl_topp_prune; out_threshold = {cut, score of token 0}. */
+TWL_API int twl_threshold_prune(const float* scores, int32_t score_stride, const int32_t* kv_indptr,
+                                const int32_t* kv_last_page_len, const int32_t* cand_pages,
+                                const int32_t* cand_npages, int32_t max_k, int32_t batch,
+                                int32_t num_q_heads, float threshold, int32_t* out_indices,
+                                int32_t index_stride, int32_t* out_budget, float* out_threshold,
+                                int32_t* status, void* stream);
 
 /* ---- kernel #3: sparse paged decode attention ------------------------------------------
  * Replaces attention.py:188-190 restricted to the kept tokens and :298-306 (masked fp32

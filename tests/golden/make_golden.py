@@ -55,6 +55,12 @@ def main():
         for budget in (32, 40, 1000):
             m = quest.quest_selector(model, q.to(dt), k.to(dt), 16, token_budget=budget)
             out[f"quest_mask_{name}_{budget}"] = m.numpy()
+    # element-wise threshold pruner (twilight/pyimpl/elementwise_threshold.py:9-18)
+    thr = load("ref_threshold", "twilight/pyimpl/elementwise_threshold.py")
+    w = torch.randn(2, 3, 1, 40, generator=g) * 3
+    out["thr_w"] = w.numpy()
+    for t in (0.5, 4.0):
+        out[f"thr_mask_{t}"] = thr.elementwise_threshold(w, t).numpy()
     np.savez_compressed(OUT, **out)
     print("wrote", OUT, OUT.stat().st_size, "bytes")
 

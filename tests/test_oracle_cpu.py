@@ -48,6 +48,12 @@ def test_quest_matches_reference(golden, name, dt, budget):
     assert np.array_equal(m.numpy(), golden[f"quest_mask_{name}_{budget}"])
 
 
+def test_elementwise_threshold_matches_reference(golden):
+    w = torch.from_numpy(golden["thr_w"])
+    for t in (0.5, 4.0):
+        assert np.array_equal(O.elementwise_threshold(w, t).numpy(), golden[f"thr_mask_{t}"])
+
+
 def test_quest_meta_form_equals_dense_form():
     g = torch.Generator().manual_seed(1)
     q = torch.randn(1, 2, 1, 128, generator=g)

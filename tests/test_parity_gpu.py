@@ -128,6 +128,29 @@ def test_quest_select_vs_oracle(hq, hkv):
                 assert abs(want[pg] - othr) <= 1e-3 * max(1.0, abs(othr))
 
 
+@pytest.mark.parametrize("hq,hkv", [(4, 4), (8, 2)])
+def test_fused_quest_select_equals_two_step_form(hq, hkv):
+    lens = [100, 1000, 257, 16, 4096]
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=torch.bfloat16, device=DEV,
+                                  seed=41, recipe="mid", shuffle_pages=True)
+    counters = torch.zeros(len(lens) * hkv, dtype=torch.int32, device=DEV)
+    for budget in (160, 17, 100000):
+        a_pages, a_n, a_scores = ops.quest_select(q, cache.kmeta, cache.kv_indptr, cache.kv_indices, budget,
+                                                  max_pages=cache.max_pages)
+        for _ in range(2):  # twice: the counters must come back to zero
+            b_pages, b_n, b_scores = ops.quest_select(q, cache.kmeta, cache.kv_indptr, cache.kv_indices, budget,
+                                                      max_pages=cache.max_pages, counters=counters)
+            torch.cuda.synchronize()
+            assert int(counters.abs().sum()) == 0
+            assert torch.equal(a_n, b_n)
+            for b in range(len(lens)):
+                npg = (lens[b] + PAGE - 1) // PAGE
+                assert torch.equal(a_scores[b, :, :npg], b_scores[b, :, :npg])
+                for h in range(hq):
+                    k = int(a_n[b, h])
+                    assert torch.equal(a_pages[b, h, :k], b_pages[b, h, :k])
+
+
 def test_quest_selector_mask_interface_matches_reference_fixture(golden):
     from twilight_b200.pyimpl import quest_selector
     q = torch.from_numpy(golden["quest_q"]).to(torch.bfloat16).to(DEV)
@@ -290,6 +313,38 @@ def test_prune_is_deterministic_and_per_row_threshold():
         probs, keep, low = U.oracle_prune_row(row, np.arange(128), float(p_arr[r]))
         U.check_index_parity(i1.reshape(12, -1)[r, : int(b1.flatten()[r])].cpu().numpy(), probs, keep, low,
                              np.arange(128), P_TOL)
+
+
+@pytest.mark.parametrize("with_cand", [False, True])
+def test_threshold_prune_is_exact(with_cand):
+    """Element-wise threshold pruner: integer work on identical fp32 scores, so bit-exact."""
+    lens = [17, 700, 3000]
+    hq, hkv = 4, 2
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=torch.bfloat16, device=DEV,
+                                  seed=31, recipe="calibrated", shuffle_pages=True)
+    cand_pages = cand_npages = None
+    if with_cand:
+        cand_pages, cand_npages, _ = ops.quest_select(q, cache.kmeta, cache.kv_indptr, cache.kv_indices, 512,
+                                                      max_pages=cache.max_pages)
+        cand_pages[1, 0, 0] = cand_pages[1, 0, 1]   # one row without token 0 among its candidates
+    scores = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
+                               max_pages=cache.max_pages, cand_pages=cand_pages, cand_npages=cand_npages)
+    for t in (0.5, 3.0, 100.0):
+        cut = torch.zeros(len(lens), hq, 2, device=DEV)
+        indices, budget = ops.threshold_prune(scores, cache.kv_indptr, cache.kv_last_page_len, t,
+                                              cand_pages=cand_pages, cand_npages=cand_npages, cut=cut)
+        for b, n in enumerate(lens):
+            npg = (n + PAGE - 1) // PAGE
+            for h in range(hq):
+                pages = (np.arange(npg) if cand_pages is None
+                         else cand_pages[b, h, : int(cand_npages[b, h])].cpu().numpy())
+                row = scores[b, h, : len(pages) * PAGE].cpu().numpy()
+                # the reference's dense row: token 0's weight is row[0] iff page 0 leads the list
+                w0 = row[0] if pages[0] == 0 else -np.inf
+                keep = row > np.float32(w0 - np.float32(t))
+                want = U.slots_to_tokens(pages, np.nonzero(keep)[0])
+                got = indices[b, h, : int(budget[b, h])].cpu().numpy()
+                assert np.array_equal(got, want), (t, b, h)
 
 
 # ---- reference-compatible mask operators -----------------------------------------------------------------

@@ -23,10 +23,14 @@ SIGNATURES = {
     "twl_quest_page_scores": (C.c_int, [ptr, C.c_int, ptr, ptr, ptr, i32, i32, i32, i32, ptr, i32,
                                         ptr, ptr]),
     "twl_quest_topk_pages": (C.c_int, [ptr, i32, ptr, i32, i32, i32, ptr, ptr, i32, ptr]),
+    "twl_quest_select": (C.c_int, [ptr, C.c_int, ptr, ptr, ptr, i32, i32, i32, i32, i32, ptr, i32, ptr, ptr,
+                                   i32, ptr, ptr, ptr]),
     "twl_estimate_int4": (C.c_int, [ptr, C.c_int, ptr, ptr, ptr, ptr, ptr, ptr, i32, i32, i32, i32,
                                     i32, f32, ptr, i32, i32, ptr, ptr]),
     "twl_topp_prune": (C.c_int, [ptr, i32, ptr, ptr, ptr, ptr, i32, i32, i32, ptr, f32, ptr, i32,
                                  ptr, ptr, ptr, ptr]),
+    "twl_threshold_prune": (C.c_int, [ptr, i32, ptr, ptr, ptr, ptr, i32, i32, i32, f32, ptr, i32, ptr, ptr,
+                                      ptr, ptr]),
     "twl_sparse_attn_workspace_bytes": (sz, [i32, i32, i32, i32]),
     "twl_sparse_decode_attn": (C.c_int, [ptr, C.c_int, ptr, ptr, ptr, ptr, ptr, i32, ptr, i32, i32,
                                          i32, i32, f32, ptr, ptr, sz, i32, ptr, ptr]),

@@ -152,6 +152,52 @@ sparse_decode_attn_kernel(const AttParams p) {
         // K and V rows of 16 tokens are all requested before any is used
         int rr[16];
         uint2 kk[16], vv[16];
+        if (n_here <= 4) {
+          // short tail (budgets of a few tokens are the common case after pruning): four rows,
+          // plain warp sums, no transpose
+          uint2 k4[4], v4[4];
+          int r4[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            r4[u] = __shfl_sync(0xffffffffu, ro, half * 16 + u);
+            const int rc = max(r4[u], 0);
+            k4[u] = ldg_stream_u2(kbase + (size_t)rc * kD + lane * 4);
+            v4[u] = ldg_stream_u2(vbase + (size_t)rc * kD + lane * 4);
+          }
+          float sc[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float2 k0 = Elem<T>::to_f2(k4[u].x), k1 = Elem<T>::to_f2(k4[u].y);
+            sc[u] = qf[0] * k0.x + qf[1] * k0.y + qf[2] * k1.x + qf[3] * k1.y;
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+          }
+          float m_new = m;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            sc[u] = (u < n_here && r4[u] >= 0) ? sc[u] : -INFINITY;
+            m_new = fmaxf(m_new, sc[u]);
+          }
+          const float scale = __expf(m - m_new);
+          l *= scale;
+#pragma unroll
+          for (int d = 0; d < 4; ++d) acc[d] *= scale;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float pu = __expf(sc[u] - m_new);
+            l += pu;
+            const float2 v0 = Elem<T>::to_f2(v4[u].x), v1 = Elem<T>::to_f2(v4[u].y);
+            acc[0] = fmaf(pu, v0.x, acc[0]);
+            acc[1] = fmaf(pu, v0.y, acc[1]);
+            acc[2] = fmaf(pu, v1.x, acc[2]);
+            acc[3] = fmaf(pu, v1.y, acc[3]);
+          }
+          m = m_new;
+          break;  // a tail of at most four tokens is the last work of this warp in the chunk
+        }
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
           // tokens that are absent or invalid read row 0 (always mapped) and get weight 0 below,

@@ -21,7 +21,21 @@ struct ScoreParams {
   float* page_scores;
   int32_t* status;
   int B, Hq, Hkv, num_pages_total, max_pages;
+  // fused selection (counters != nullptr): the block that finishes a row's scores last also
+  // picks the row's best pages
+  int32_t* counters;     // [B*Hkv], zero on entry, left zero
+  int32_t* cand_pages;   // [B][Hq][max_k]
+  int32_t* cand_npages;  // [B][Hq]
+  int token_budget, max_k;
 };
+
+struct TopkScratch {
+  int hist[256];
+  int wsum[33];
+  uint32_t prefix;
+  int krem;
+};
+__device__ void topk_row(const float* src, int n, int k, int32_t* out, uint32_t* keys, TopkScratch& sc);
 
 // Eight lanes share a page: lane `sub` reads 16-byte pieces sub and sub+8 of the 256-byte min
 // row and of the max row (channels 8*sub..8*sub+7 and 64+8*sub..), so a warp step covers four
@@ -36,7 +50,11 @@ quest_page_scores_kernel(const ScoreParams p) {
   const int page_base = p.indptr[b];
   const int n_pages = min(p.indptr[b + 1] - page_base, p.max_pages);
   const int first = blockIdx.y * kSelPagesPerBlock;
-  if (first >= n_pages) return;
+  if (first >= n_pages) {
+    if (p.counters != nullptr && n_pages <= 0 && blockIdx.y == 0 && threadIdx.x < G)
+      p.cand_npages[b * p.Hq + kvh * G + threadIdx.x] = 0;
+    return;
+  }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane & 7, pg_in_step = lane >> 3;
   const int h0 = kvh * G;
@@ -127,6 +145,34 @@ quest_page_scores_kernel(const ScoreParams p) {
       }
     }
   }
+  if (p.counters == nullptr) return;
+  // ---- fused selection: last block of the row to arrive (ticket; nobody waits) ----
+  extern __shared__ __align__(16) uint32_t dyn_keys[];  // max_pages keys
+  __shared__ TopkScratch sc;
+  __shared__ int sm_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int n_blocks = (n_pages + kSelPagesPerBlock - 1) / kSelPagesPerBlock;
+    const int ticket = atomicAdd(&p.counters[row], 1);
+    sm_last = (ticket == n_blocks - 1);
+    if (sm_last) p.counters[row] = 0;  // ready for the next call
+  }
+  __syncthreads();
+  if (!sm_last) return;
+  __threadfence();
+  int k = max(1, p.token_budget / kPage) + ((p.token_budget % kPage) != 0 ? 1 : 0);  // quest.py:93-95
+  k = min(min(k, n_pages), p.max_k);                                                 // quest.py:98
+  for (int g = 0; g < G; ++g) {
+    const int qrow = b * p.Hq + h0 + g;
+    int32_t* out = p.cand_pages + (size_t)qrow * p.max_k;
+    if (threadIdx.x == 0) p.cand_npages[qrow] = k;
+    if (k == n_pages) {
+      for (int i = threadIdx.x; i < n_pages; i += kSelThreads) out[i] = i;
+    } else if (k > 0) {
+      topk_row(p.page_scores + (size_t)qrow * p.max_pages, n_pages, k, out, dyn_keys, sc);
+    }
+  }
 }
 
 // ---- top-k pages of one (batch, query head) row ---------------------------------------------
@@ -136,31 +182,17 @@ __device__ __forceinline__ uint32_t order_key(float f) {
 }
 
 constexpr int kTopkThreads = 256;
+static_assert(kTopkThreads == kSelThreads, "the fused tail runs the selection with the scoring block");
 
-__global__ void __launch_bounds__(kTopkThreads)
-quest_topk_pages_kernel(const float* __restrict__ page_scores, int max_pages,
-                        const int32_t* __restrict__ indptr, int Hq, int token_budget,
-                        int32_t* __restrict__ cand_pages, int32_t* __restrict__ cand_npages,
-                        int max_k) {
-  extern __shared__ __align__(16) uint32_t keys[];  // max_pages keys
-  __shared__ int hist[256];
-  __shared__ int wsum[33];
-  __shared__ uint32_t sh_prefix;
-  __shared__ int sh_krem;
-
-  const int row = blockIdx.x, b = row / Hq;
-  const int n = min(indptr[b + 1] - indptr[b], max_pages);
-  int k = max(1, token_budget / kPage) + ((token_budget % kPage) != 0 ? 1 : 0);  // quest.py:93-95
-  k = min(min(k, n), max_k);                                                     // quest.py:98
-  int32_t* out = cand_pages + (size_t)row * max_k;
-  if (threadIdx.x == 0) cand_npages[row] = k;
-  if (k <= 0) return;
-  if (k == n) {  // every page is kept
-    for (int i = threadIdx.x; i < n; i += kTopkThreads) out[i] = i;
-    return;
-  }
-  const float* src = page_scores + (size_t)row * max_pages;
-  for (int i = threadIdx.x; i < n; i += kTopkThreads) keys[i] = order_key(src[i]);
+// Keeps the k best of src[0..n) (k < n) and writes their positions, ascending, to out[0..k).
+// Called by a whole block of kTopkThreads threads; keys: n words of shared memory.  Scores are
+// read through L2 because other blocks may have written them.
+__device__ void topk_row(const float* src, int n, int k, int32_t* out, uint32_t* keys, TopkScratch& sc) {
+  int (&hist)[256] = sc.hist;
+  int (&wsum)[33] = sc.wsum;
+  uint32_t& sh_prefix = sc.prefix;
+  int& sh_krem = sc.krem;
+  for (int i = threadIdx.x; i < n; i += kTopkThreads) keys[i] = order_key(__ldcg(src + i));
   if (threadIdx.x == 0) {
     sh_prefix = 0;
     sh_krem = k;
@@ -241,13 +273,38 @@ quest_topk_pages_kernel(const float* __restrict__ page_scores, int max_pages,
   }
 }
 
+__global__ void __launch_bounds__(kTopkThreads)
+quest_topk_pages_kernel(const float* __restrict__ page_scores, int max_pages,
+                        const int32_t* __restrict__ indptr, int Hq, int token_budget,
+                        int32_t* __restrict__ cand_pages, int32_t* __restrict__ cand_npages,
+                        int max_k) {
+  extern __shared__ __align__(16) uint32_t keys[];  // max_pages keys
+  __shared__ TopkScratch sc;
+  const int row = blockIdx.x, b = row / Hq;
+  const int n = min(indptr[b + 1] - indptr[b], max_pages);
+  int k = max(1, token_budget / kPage) + ((token_budget % kPage) != 0 ? 1 : 0);  // quest.py:93-95
+  k = min(min(k, n), max_k);                                                     // quest.py:98
+  int32_t* out = cand_pages + (size_t)row * max_k;
+  if (threadIdx.x == 0) cand_npages[row] = k;
+  if (k <= 0) return;
+  if (k == n) {  // every page is kept
+    for (int i = threadIdx.x; i < n; i += kTopkThreads) out[i] = i;
+    return;
+  }
+  topk_row(page_scores + (size_t)row * max_pages, n, k, out, keys, sc);
+}
+
 template <typename T, int G>
 static int launch_scores(const ScoreParams& p, cudaStream_t st) {
   const int rows = p.B * p.Hkv;
   const int chunks = (p.max_pages + kSelPagesPerBlock - 1) / kSelPagesPerBlock;
   if (chunks > 65535) return TWL_ERR_TOO_LARGE;
   dim3 grid(rows, chunks);
-  quest_page_scores_kernel<T, G><<<grid, kSelThreads, 0, st>>>(p);
+  const size_t smem = p.counters ? (size_t)p.max_pages * sizeof(uint32_t) : 0;
+  if (smem > 48 * 1024)
+    TWL_CUDA_TRY(cudaFuncSetAttribute(quest_page_scores_kernel<T, G>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024 * 4));
+  quest_page_scores_kernel<T, G><<<grid, kSelThreads, smem, st>>>(p);
   TWL_CHECK_LAUNCH();
   return TWL_OK;
 }
@@ -280,6 +337,34 @@ extern "C" int twl_quest_page_scores(const void* q, int dtype, const void* kmeta
   p.q = q; p.kmeta = kmeta; p.indptr = kv_indptr; p.indices = kv_indices;
   p.page_scores = page_scores; p.status = status; p.B = batch; p.Hq = num_q_heads;
   p.Hkv = num_kv_heads; p.num_pages_total = num_pages_total; p.max_pages = max_pages;
+  p.counters = nullptr; p.cand_pages = nullptr; p.cand_npages = nullptr; p.token_budget = 0; p.max_k = 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == TWL_F16) return launch_scores_g<__half>(p, st);
+  if (dtype == TWL_BF16) return launch_scores_g<__nv_bfloat16>(p, st);
+  return TWL_ERR_UNSUPPORTED;
+}
+
+extern "C" int twl_quest_select(const void* q, int dtype, const void* kmeta,
+                                const int32_t* kv_indptr, const int32_t* kv_indices, int32_t batch,
+                                int32_t num_q_heads, int32_t num_kv_heads, int32_t num_pages_total,
+                                int32_t token_budget, float* page_scores, int32_t max_pages,
+                                int32_t* cand_pages, int32_t* cand_npages, int32_t max_k,
+                                int32_t* counters, int32_t* status, void* stream) {
+  using namespace twl;
+  if (!q || !kmeta || !kv_indptr || !kv_indices || !page_scores || !cand_pages || !cand_npages ||
+      !counters)
+    return TWL_ERR_BAD_ARG;
+  if (batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_pages_total <= 0 ||
+      max_pages <= 0 || max_k <= 0 || token_budget < 0 || num_q_heads % num_kv_heads != 0)
+    return TWL_ERR_BAD_ARG;
+  if (max_pages > 48 * 1024) return TWL_ERR_TOO_LARGE;  // keys of a row live in shared memory
+  if (!aligned(q, 16) || !aligned(kmeta, 16)) return TWL_ERR_MISALIGNED;
+  ScoreParams p;
+  p.q = q; p.kmeta = kmeta; p.indptr = kv_indptr; p.indices = kv_indices;
+  p.page_scores = page_scores; p.status = status; p.B = batch; p.Hq = num_q_heads;
+  p.Hkv = num_kv_heads; p.num_pages_total = num_pages_total; p.max_pages = max_pages;
+  p.counters = counters; p.cand_pages = cand_pages; p.cand_npages = cand_npages;
+  p.token_budget = token_budget; p.max_k = max_k;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == TWL_F16) return launch_scores_g<__half>(p, st);
   if (dtype == TWL_BF16) return launch_scores_g<__nv_bfloat16>(p, st);

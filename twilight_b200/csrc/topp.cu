@@ -307,6 +307,7 @@ struct PruneParams {
   float* out_threshold;
   int32_t* status;
   int stride, max_k, B, Hq, index_stride, row_cap, list_cap;
+  int mode;  // 0: softmax + top-p search; 1: keep scores above (score of token 0) - top_p_val
   float top_p_val;
 };
 
@@ -350,54 +351,69 @@ topp_prune_kernel(const PruneParams p) {
   Red3 r1 = block_red3<THREADS>(0.f, 0.f, m, red);
   m = r1.b;
   __syncthreads();
-  // pass 2: exponentials and their sum.  exp(s-m) = 2^(s*log2e - m*log2e), one FMA and one
-  // ex2.approx (2 ulp, subnormal results kept so that "probability > 0" means what it says).
   const float kLog2e = 1.4426950408889634f;
   const float m2 = m * kLog2e;
+  // exp(s-m) = 2^(s*log2e - m*log2e): one FMA and one ex2.approx (2 ulp, subnormal results kept
+  // so that "probability > 0" means what it says)
   auto fexp = [&](float sc) -> float {
     float y;
     asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(fmaf(sc, kLog2e, -m2)));
     return y;
   };
-  float z = 0.f;
-  if (IN_SMEM) {
-    float4* r4 = reinterpret_cast<float4*>(row);
-    for (int i = threadIdx.x; i < n / 4; i += THREADS) {
-      float4 v = r4[i];
-      v.x = fexp(v.x); v.y = fexp(v.y); v.z = fexp(v.z); v.w = fexp(v.w);
-      r4[i] = v;
-      z += (v.x + v.y) + (v.z + v.w);
+  const bool thresh_mode = p.mode == 1;
+  float inv_z = 1.f;
+  if (!thresh_mode) {
+    // pass 2: exponentials and their sum
+    float z = 0.f;
+    if (IN_SMEM) {
+      float4* r4 = reinterpret_cast<float4*>(row);
+      for (int i = threadIdx.x; i < n / 4; i += THREADS) {
+        float4 v = r4[i];
+        v.x = fexp(v.x); v.y = fexp(v.y); v.z = fexp(v.z); v.w = fexp(v.w);
+        r4[i] = v;
+        z += (v.x + v.y) + (v.z + v.w);
+      }
+    } else {
+      for (int i = threadIdx.x; i < n; i += THREADS) z += fexp(src[i]);
     }
-  } else {
-    for (int i = threadIdx.x; i < n; i += THREADS) z += fexp(src[i]);
-  }
-  Red3 r2 = block_red3<THREADS>(z, 0.f, 0.f, red + 96);
-  z = r2.s;
-  const float inv_z = 1.f / z;
-  __syncthreads();
-  if (IN_SMEM) {
-    float4* r4 = reinterpret_cast<float4*>(row);
-    for (int i = threadIdx.x; i < n / 4; i += THREADS) {
-      float4 v = r4[i];
-      v.x *= inv_z; v.y *= inv_z; v.z *= inv_z; v.w *= inv_z;
-      r4[i] = v;
-    }
+    Red3 r2 = block_red3<THREADS>(z, 0.f, 0.f, red + 96);
+    z = r2.s;
+    inv_z = 1.f / z;
     __syncthreads();
+    if (IN_SMEM) {
+      float4* r4 = reinterpret_cast<float4*>(row);
+      for (int i = threadIdx.x; i < n / 4; i += THREADS) {
+        float4 v = r4[i];
+        v.x *= inv_z; v.y *= inv_z; v.z *= inv_z; v.w *= inv_z;
+        r4[i] = v;
+      }
+      __syncthreads();
+    }
   }
-  auto prob = [&](int i) -> float { return IN_SMEM ? row[i] : fexp(src[i]) * inv_z; };
-  // probability of sequence token 0: slot 0 when page 0 is a candidate, else it is not in the row
+  // value that is compared with the cut: the probability, or the raw score in threshold mode
+  auto prob = [&](int i) -> float {
+    return IN_SMEM ? row[i] : (thresh_mode ? src[i] : fexp(src[i]) * inv_z);
+  };
+  // token 0 of the sequence: slot 0 when page 0 is a candidate, else it is not in the row
   const bool sink_present = has_cand ? (cand[0] == 0) : true;
-  const float x0 = sink_present ? prob(0) : 0.f;
   const float top_p = p.top_p_arr ? p.top_p_arr[r] : p.top_p_val;
-  float low;
-  if (top_p > 1.f) {
-    low = 0.f;  // no pruning asked for: keep every candidate with non-zero probability
-  } else if (IN_SMEM) {
-    const int seg_cap = ((p.list_cap / (THREADS / 32)) & ~3);
-    low = topp_search_narrowing<THREADS>(row, n, row + p.row_cap, seg_cap, wsum + 40, x0, top_p, red,
-                                         p.status);
+  float x0, low;
+  if (thresh_mode) {
+    // twilight/pyimpl/elementwise_threshold.py:15-17: weights > weight[0] - threshold; a token 0
+    // outside the candidates holds the dtype's minimum there, so every candidate passes
+    x0 = sink_present ? prob(0) : -INFINITY;
+    low = sink_present ? x0 - top_p : -INFINITY;
   } else {
-    low = topp_search<THREADS, float>(prob, n, x0, top_p, red, p.status);
+    x0 = sink_present ? prob(0) : 0.f;
+    if (top_p > 1.f) {
+      low = 0.f;  // no pruning asked for: keep every candidate with non-zero probability
+    } else if (IN_SMEM) {
+      const int seg_cap = ((p.list_cap / (THREADS / 32)) & ~3);
+      low = topp_search_narrowing<THREADS>(row, n, row + p.row_cap, seg_cap, wsum + 40, x0, top_p, red,
+                                           p.status);
+    } else {
+      low = topp_search<THREADS, float>(prob, n, x0, top_p, red, p.status);
+    }
   }
   __syncthreads();
   // ordered compaction: every warp owns a contiguous slice of the row, counts its kept slots,
@@ -426,12 +442,12 @@ topp_prune_kernel(const PruneParams p) {
     int off = __shfl_sync(0xffffffffu, inc_w, warp) - my_cnt;      // exclusive prefix of this warp
     for (int i0 = s_begin; i0 < s_end; i0 += 128) {
       const int i = i0 + lane * 4;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);  // never above any cut
       if (i < s_end) v = *reinterpret_cast<const float4*>(row + i);
       const float e[4] = {v.x, v.y, v.z, v.w};
       int c = 0;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) c += e[k] > low ? 1 : 0;   // absent groups hold 0 and low >= 0
+      for (int k = 0; k < 4; ++k) c += e[k] > low ? 1 : 0;
       const int inc = warp_incl_scan(c);
       if (c) {
         const int page = has_cand ? cand[i / kPage] : (i / kPage);  // i % 4 == 0: one page
@@ -524,31 +540,12 @@ extern "C" int twl_top_p_return_mask_f16(const void* probs, int dtype, uint8_t* 
   return TWL_ERR_UNSUPPORTED;
 }
 
-extern "C" int twl_topp_prune(const float* scores, int32_t score_stride,
-                              const int32_t* kv_indptr, const int32_t* kv_last_page_len,
-                              const int32_t* cand_pages, const int32_t* cand_npages,
-                              int32_t max_k, int32_t batch, int32_t num_q_heads,
-                              const float* top_p_arr, float top_p_val, int32_t* out_indices,
-                              int32_t index_stride, int32_t* out_budget, float* out_threshold,
-                              int32_t* status, void* stream) {
-  using namespace twl;
-  if (!scores || !kv_indptr || !out_indices || !out_budget) return TWL_ERR_BAD_ARG;
-  if (batch <= 0 || num_q_heads <= 0 || score_stride <= 0 || index_stride <= 0)
-    return TWL_ERR_BAD_ARG;
-  if (score_stride % kPage != 0) return TWL_ERR_BAD_ARG;
-  if (cand_pages && (!cand_npages || max_k <= 0)) return TWL_ERR_BAD_ARG;
-  if (!aligned(scores, 16)) return TWL_ERR_MISALIGNED;
-  (void)kv_last_page_len;
-  PruneParams p;
-  p.scores = scores; p.indptr = kv_indptr; p.last_len = kv_last_page_len;
-  p.cand_pages = cand_pages; p.cand_npages = cand_npages; p.top_p_arr = top_p_arr;
-  p.out_indices = out_indices; p.out_budget = out_budget; p.out_threshold = out_threshold;
-  p.status = status; p.stride = score_stride; p.max_k = max_k; p.B = batch; p.Hq = num_q_heads;
-  p.index_stride = index_stride; p.top_p_val = top_p_val;
+namespace twl {
+static int run_prune(PruneParams& p, int batch, int num_q_heads, int score_stride, const int32_t* cand_pages,
+                     int max_k, cudaStream_t st) {
   const int rows = batch * num_q_heads;
   const int n_max = cand_pages ? (int)std::min<int64_t>((int64_t)max_k * kPage, score_stride)
                                : score_stride;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   // one block per row.  More threads per row shorten a row's latency, but only pay while all rows
   // still run at the same time (3 blocks of 512 threads per SM, 6 of 256): a second wave costs more
   const bool one_wave_512 = rows <= 3 * kNumSMs;
@@ -557,4 +554,49 @@ extern "C" int twl_topp_prune(const float* scores, int32_t score_stride,
   if (n_max <= 8192) return one_wave_512 ? launch_prune<512>(p, rows, n_max, st) : launch_prune<256>(p, rows, n_max, st);
   if (n_max <= 16384) return one_wave_1024 ? launch_prune<1024>(p, rows, n_max, st) : launch_prune<512>(p, rows, n_max, st);
   return launch_prune<1024>(p, rows, n_max, st);
+}
+
+static int prune_entry(int mode, const float* scores, int32_t score_stride, const int32_t* kv_indptr,
+                       const int32_t* kv_last_page_len, const int32_t* cand_pages,
+                       const int32_t* cand_npages, int32_t max_k, int32_t batch, int32_t num_q_heads,
+                       const float* arr, float val, int32_t* out_indices, int32_t index_stride,
+                       int32_t* out_budget, float* out_threshold, int32_t* status, void* stream) {
+  if (!scores || !kv_indptr || !out_indices || !out_budget) return TWL_ERR_BAD_ARG;
+  if (batch <= 0 || num_q_heads <= 0 || score_stride <= 0 || index_stride <= 0)
+    return TWL_ERR_BAD_ARG;
+  if (score_stride % kPage != 0) return TWL_ERR_BAD_ARG;
+  if (cand_pages && (!cand_npages || max_k <= 0)) return TWL_ERR_BAD_ARG;
+  if (!aligned(scores, 16)) return TWL_ERR_MISALIGNED;
+  PruneParams p;
+  p.scores = scores; p.indptr = kv_indptr; p.last_len = kv_last_page_len;
+  p.cand_pages = cand_pages; p.cand_npages = cand_npages; p.top_p_arr = arr;
+  p.out_indices = out_indices; p.out_budget = out_budget; p.out_threshold = out_threshold;
+  p.status = status; p.stride = score_stride; p.max_k = max_k; p.B = batch; p.Hq = num_q_heads;
+  p.index_stride = index_stride; p.top_p_val = val; p.mode = mode;
+  return run_prune(p, batch, num_q_heads, score_stride, cand_pages, max_k,
+                   reinterpret_cast<cudaStream_t>(stream));
+}
+}  // namespace twl
+
+extern "C" int twl_topp_prune(const float* scores, int32_t score_stride,
+                              const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                              const int32_t* cand_pages, const int32_t* cand_npages,
+                              int32_t max_k, int32_t batch, int32_t num_q_heads,
+                              const float* top_p_arr, float top_p_val, int32_t* out_indices,
+                              int32_t index_stride, int32_t* out_budget, float* out_threshold,
+                              int32_t* status, void* stream) {
+  return twl::prune_entry(0, scores, score_stride, kv_indptr, kv_last_page_len, cand_pages, cand_npages,
+                          max_k, batch, num_q_heads, top_p_arr, top_p_val, out_indices, index_stride,
+                          out_budget, out_threshold, status, stream);
+}
+
+extern "C" int twl_threshold_prune(const float* scores, int32_t score_stride,
+                                   const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                                   const int32_t* cand_pages, const int32_t* cand_npages,
+                                   int32_t max_k, int32_t batch, int32_t num_q_heads, float threshold,
+                                   int32_t* out_indices, int32_t index_stride, int32_t* out_budget,
+                                   float* out_threshold, int32_t* status, void* stream) {
+  return twl::prune_entry(1, scores, score_stride, kv_indptr, kv_last_page_len, cand_pages, cand_npages,
+                          max_k, batch, num_q_heads, nullptr, threshold, out_indices, index_stride,
+                          out_budget, out_threshold, status, stream);
 }

@@ -6,6 +6,7 @@ from .ops import (  # noqa: F401
     quest_select,
     estimate_int4,
     topp_prune,
+    threshold_prune,
     sparse_decode_attn,
     sparse_attn_workspace_bytes,
     sparse_decode_attn_static,

@@ -102,11 +102,12 @@ def top_p_fp16_return_mask(probs: torch.Tensor, top_p: Union[torch.Tensor, float
 # index-list operators
 # ---------------------------------------------------------------------------------------------
 def quest_select(q, kmeta, kv_indptr, kv_indices, token_budget: int, *, max_pages: int,
-                 page_scores=None, cand_pages=None, cand_npages=None, status=None
+                 page_scores=None, cand_pages=None, cand_npages=None, status=None, counters=None
                  ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Quest selector on stored page metadata (twilight/pyimpl/quest.py:17-122).
 
-    Returns ``(cand_pages[B,H,max_k] int32 ascending, cand_npages[B,H] int32, page_scores)``."""
+    Returns ``(cand_pages[B,H,max_k] int32 ascending, cand_npages[B,H] int32, page_scores)``.
+    With ``counters`` (zeroed int32 ``[B*H_kv]``) scoring and selection run as one kernel."""
     lib = _lib.load()
     q = _q3(q)
     b, hq, _ = q.shape
@@ -121,6 +122,13 @@ def quest_select(q, kmeta, kv_indptr, kv_indices, token_budget: int, *, max_page
     if cand_npages is None:
         cand_npages = torch.empty(b, hq, dtype=torch.int32, device=dev)
     s = _stream(dev)
+    if counters is not None:
+        _lib.check(lib.twl_quest_select(q.data_ptr(), _dtype_code(q), kmeta.data_ptr(), kv_indptr.data_ptr(),
+                                        kv_indices.data_ptr(), b, hq, hkv, n_total, token_budget,
+                                        page_scores.data_ptr(), max_pages, cand_pages.data_ptr(),
+                                        cand_npages.data_ptr(), cand_pages.shape[-1], counters.data_ptr(),
+                                        _p(status), s), "quest_select")
+        return cand_pages, cand_npages, page_scores
     _lib.check(lib.twl_quest_page_scores(q.data_ptr(), _dtype_code(q), kmeta.data_ptr(),
                                          kv_indptr.data_ptr(), kv_indices.data_ptr(), b, hq, hkv,
                                          n_total, page_scores.data_ptr(), max_pages, _p(status), s),
@@ -180,6 +188,28 @@ def topp_prune(scores, kv_indptr, kv_last_page_len, top_p: Union[torch.Tensor, f
                                   max_k, b, hq, _p(arr), val, indices.data_ptr(),
                                   indices.shape[-1], budget.data_ptr(), _p(threshold), _p(status),
                                   _stream(dev)), "topp_prune")
+    return indices, budget
+
+
+def threshold_prune(scores, kv_indptr, kv_last_page_len, threshold: float, *, cand_pages=None,
+                    cand_npages=None, indices=None, budget=None, cut=None, status=None
+                    ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Element-wise threshold pruner (twilight/pyimpl/elementwise_threshold.py:9-18) in index-list
+    form: keeps candidates whose score exceeds ``score(token 0) - threshold``."""
+    lib = _lib.load()
+    _cuda_contig(scores, "scores")
+    b, hq, stride = scores.shape
+    dev = scores.device
+    if indices is None:
+        indices = torch.empty(b, hq, stride, dtype=torch.int32, device=dev)
+    if budget is None:
+        budget = torch.empty(b, hq, dtype=torch.int32, device=dev)
+    max_k = 0 if cand_pages is None else cand_pages.shape[-1]
+    _lib.check(lib.twl_threshold_prune(scores.data_ptr(), stride, kv_indptr.data_ptr(),
+                                       kv_last_page_len.data_ptr(), _p(cand_pages), _p(cand_npages),
+                                       max_k, b, hq, float(threshold), indices.data_ptr(),
+                                       indices.shape[-1], budget.data_ptr(), _p(cut), _p(status),
+                                       _stream(dev)), "threshold_prune")
     return indices, budget
 
 

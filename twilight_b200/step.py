@@ -25,7 +25,7 @@ class SparseConfig:
     chunk_size: int = PAGE            # quest: must equal the page size, 16
     weight_estimator: str = "min_max_quant"   # only the INT4 estimator has a kernel
     quant_bit: int = 4
-    weight_pruner: str = "top_p"      # "top_p" | "none"                  (WeightPrunerType)
+    weight_pruner: str = "top_p"      # "top_p" | "threshold" | "none"    (WeightPrunerType)
     threshold: float = 0.95
     use_estimated_weights_in_attn: bool = False
     skip_first_two_layers: bool = True
@@ -50,7 +50,7 @@ class SparseConfig:
             out.chunk_size = int(sel_args.get("chunk_size", PAGE))
         if est == "min_max_quant":
             out.quant_bit = int(est_args.get("quant_bit", 4))
-        if prn == "top_p":
+        if prn in ("top_p", "threshold"):
             out.threshold = float(prn_args["threshold"])
         out.validate()
         return out
@@ -62,7 +62,7 @@ class SparseConfig:
             raise _lib.TwilightError("quest needs chunk_size == 16 (the page size) and a positive token_budget")
         if self.weight_estimator != "min_max_quant" or self.quant_bit != 4:
             raise _lib.TwilightError("the estimator kernel reads the 4-bit min/max cache only")
-        if self.weight_pruner not in ("top_p", "none"):
+        if self.weight_pruner not in ("top_p", "threshold", "none"):
             raise _lib.TwilightError(f"pruner '{self.weight_pruner}' has no kernel on this path")
         if self.use_estimated_weights_in_attn:
             raise _lib.TwilightError("attention over estimated weights is not implemented")
@@ -120,9 +120,9 @@ class DecodeWorkspace:
 
 
 def select_prune_attend_step(q: torch.Tensor, cache: PagedKVCache, ws: DecodeWorkspace,
-                             variant: int = 0) -> torch.Tensor:
+                             variant: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One decode step of one attention layer.  q ``[B,H_q,128]`` (or ``[B,H_q,1,128]``);
-    returns ``ws.out [B,H_q,128]``.  ``ws.budget`` holds the per-head pruned budgets and
+    returns ``ws.out [B,H_q,128]`` (or ``out`` when given).  ``ws.budget`` holds the per-head pruned budgets and
     ``ws.indices`` the kept tokens afterwards.  Launches 3 kernels (5 with the Quest selector)
     on the current stream and nothing else."""
     cfg = ws.config
@@ -136,14 +136,19 @@ def select_prune_attend_step(q: torch.Tensor, cache: PagedKVCache, ws: DecodeWor
                       max_pages=ws.max_pages, cand_pages=cand_pages, cand_npages=cand_npages,
                       scores=ws.scores, variant=variant, status=ws.status)
     # pruner "none" keeps every candidate with non-zero probability: top-p of 1 does not prune
-    top_p = cfg.threshold if cfg.weight_pruner == "top_p" else 2.0
-    ops.topp_prune(ws.scores, cache.kv_indptr, cache.kv_last_page_len, top_p,
-                   cand_pages=cand_pages, cand_npages=cand_npages, indices=ws.indices,
-                   budget=ws.budget, threshold=ws.threshold, status=ws.status)
+    if cfg.weight_pruner == "threshold":
+        ops.threshold_prune(ws.scores, cache.kv_indptr, cache.kv_last_page_len, cfg.threshold,
+                            cand_pages=cand_pages, cand_npages=cand_npages, indices=ws.indices,
+                            budget=ws.budget, cut=ws.threshold, status=ws.status)
+    else:
+        top_p = cfg.threshold if cfg.weight_pruner == "top_p" else 2.0
+        ops.topp_prune(ws.scores, cache.kv_indptr, cache.kv_last_page_len, top_p,
+                       cand_pages=cand_pages, cand_npages=cand_npages, indices=ws.indices,
+                       budget=ws.budget, threshold=ws.threshold, status=ws.status)
     ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices,
-                           ws.indices, ws.budget, out=ws.out, workspace=ws.attn_ws,
-                           chunk=ws.attn_chunk, status=ws.status)
-    return ws.out
+                           ws.indices, ws.budget, out=ws.out if out is None else out,
+                           workspace=ws.attn_ws, chunk=ws.attn_chunk, status=ws.status)
+    return ws.out if out is None else out
 
 
 def step_algorithmic_bytes(cache: PagedKVCache, num_q_heads: int, config: SparseConfig,
