@@ -565,12 +565,13 @@ estimate_int4_warp_kernel(const EstParams p) {
   const int n_here = min(kWarpPagesPerBlock, n_pages - first);
 
   const int tid = threadIdx.x;
-  if (tid >= kEstThreads - 4) {
-    const int grp_j = tid - (kEstThreads - 4);
-    float qf[32];
-    load_q_group<T>(reinterpret_cast<const T*>(p.q) + ((size_t)(b * p.Hq + h)) * kD + grp_j * kGroup, qf);
-    sm_q[grp_j].init(qf);
-  } else if (tid < kWarpPagesPerBlock) {
+  // four threads fetch q now and convert it later, after the first copies are on their way
+  const bool q_thread = tid >= kEstThreads - 4;
+  float qf[32];
+  if (q_thread)
+    load_q_group<T>(reinterpret_cast<const T*>(p.q) + ((size_t)(b * p.Hq + h)) * kD +
+                        (tid - (kEstThreads - 4)) * kGroup, qf);
+  if (tid < kWarpPagesPerBlock) {
     int phys = -1, ntok = 0;
     if (tid < n_here) {
       const int seq_page = has_cand ? p.cand_pages[(size_t)(b * p.Hq + h) * p.max_k + first + tid] : first + tid;
@@ -587,10 +588,6 @@ estimate_int4_warp_kernel(const EstParams p) {
   __syncthreads();
 
   const int lane = tid & 31, warp = tid >> 5;
-  QRegs<VARIANT> qr[4];
-#pragma unroll
-  for (int g = 0; g < 4; ++g) qr[g] = sm_q[g];
-
   uint8_t* const ring = sm_ring + (size_t)warp * kRingDepth * kWarpStageBytes;
   const uint32_t ring_u32 = smem_u32(ring);
   const int n_pairs = (n_here + 1) >> 1;
@@ -617,11 +614,11 @@ estimate_int4_warp_kernel(const EstParams p) {
   const uint4* const k4_head16 = reinterpret_cast<const uint4*>(p.k4 + (size_t)kvh * kSlab);
   const uint32_t page_stride16 = (uint32_t)(p.Hkv * (kSlab / 16));
 
-  // issue the copies of this warp's i-th pair into ring slot i % kRingDepth
-  auto issue = [&](int i) {
+  // issue the copies of this warp's i-th pair into the given ring slot
+  auto issue = [&](int i, int slot) {
     if (i < my_pairs) {
       const int pg0 = (warp + i * kEstWarps) * 2;
-      const uint32_t dst0 = ring_u32 + (i % kRingDepth) * kWarpStageBytes;
+      const uint32_t dst0 = ring_u32 + slot * kWarpStageBytes;
       const int phys0 = sm_phys[pg0], phys1 = sm_phys[pg0 + 1];  // missing pages hold -1
 #pragma unroll
       for (int c5 = 0; c5 < 5; ++c5) {
@@ -634,17 +631,24 @@ estimate_int4_warp_kernel(const EstParams p) {
   };
 
 #pragma unroll
-  for (int i = 0; i < kRingDepth - 1; ++i) issue(i);
+  for (int i = 0; i < kRingDepth - 1; ++i) issue(i, i);
+
+  if (q_thread) sm_q[tid - (kEstThreads - 4)].init(qf);
+  __syncthreads();
+  QRegs<VARIANT> qr[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) qr[g] = sm_q[g];
 
   uint32_t rd_off[4];
 #pragma unroll
   for (int g = 0; g < 4; ++g) rd_off[g] = lane * 64 + (((g + (lane >> 1)) & 3) << 4);
   float* const out_row = p.scores + (size_t)(b * p.Hq + h) * p.stride + (size_t)first * kPage;
+  int use_slot = 0, fill_slot = kRingDepth - 1;
   for (int i = 0; i < my_pairs; ++i) {
     cp_async_wait<kRingDepth - 2>();  // pair i has landed (this thread's copies)
     __syncwarp();                     // ... and every other lane's
     const int pg0 = (warp + i * kEstWarps) * 2;
-    const uint8_t* stage = ring + (i % kRingDepth) * kWarpStageBytes;
+    const uint8_t* stage = ring + use_slot * kWarpStageBytes;
     const int pgl = lane >> 4, tl = lane & 15;
     const int ntok = sm_ntok[pg0 + pgl];
     const bool present = sm_phys[pg0 + pgl] >= 0;
@@ -659,8 +663,170 @@ estimate_int4_warp_kernel(const EstParams p) {
       acc = fmaf(szf.y, qr[g].qsum, acc);
     }
     __syncwarp();      // all lanes are done reading the slot that the next issue overwrites
-    issue(i + kRingDepth - 1);
+    issue(i + kRingDepth - 1, fill_slot);
+    use_slot = (use_slot + 1 == kRingDepth) ? 0 : use_slot + 1;
+    fill_slot = (fill_slot + 1 == kRingDepth) ? 0 : fill_slot + 1;
     if (present) out_row[(pg0 + pgl) * kPage + tl] = (tl < ntok) ? acc * p.sm_scale : -INFINITY;
+  }
+  cp_async_wait<0>();
+}
+
+// The same streaming scheme for a KV head shared by G query heads (every page is a candidate).
+// The codes of a token are unpacked once and used for all G heads; q does not fit in registers G
+// times, so each head's converted q sits in shared memory and is read with broadcast loads.
+template <typename T, int G>
+__global__ void __launch_bounds__(kEstThreads)
+estimate_int4_warp_group_kernel(const EstParams p) {
+  constexpr int VARIANT = VAR_DP4A;
+  extern __shared__ __align__(128) uint8_t sm_ring[];  // kEstWarps * kRingDepth * kWarpStageBytes
+  __shared__ int sm_phys[kWarpPagesPerBlock];
+  __shared__ int sm_ntok[kWarpPagesPerBlock];
+  __shared__ __align__(16) QRegs<VARIANT> sm_q[G][4];
+
+  const int row = blockIdx.y;
+  constexpr bool has_cand = false;
+  const int b = row / p.Hkv, kvh = row % p.Hkv;
+  const int h = kvh * G;  // first query head of the group
+  const int page_base = p.indptr[b];
+  const int n_seq_pages = p.indptr[b + 1] - page_base;
+  int n_pages = has_cand ? min(p.cand_npages[b * p.Hq + h], p.max_k) : n_seq_pages;
+  if (n_pages > p.stride / kPage) {
+    n_pages = p.stride / kPage;
+    if (threadIdx.x == 0 && blockIdx.x == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+  }
+  const int first = blockIdx.x * kWarpPagesPerBlock;
+  if (first >= n_pages) return;
+  const int n_here = min(kWarpPagesPerBlock, n_pages - first);
+
+  const int tid = threadIdx.x;
+  // four threads fetch q now and convert it later, after the first copies are on their way
+  const bool q_thread = tid >= kEstThreads - 4 * G;
+  const int qj = tid - (kEstThreads - 4 * G);  // head qj/4 of the group, channel group qj%4
+  float qf[32];
+  if (q_thread)
+    load_q_group<T>(reinterpret_cast<const T*>(p.q) + ((size_t)(b * p.Hq + h + (qj >> 2))) * kD +
+                        (qj & 3) * kGroup, qf);
+  if (tid < kWarpPagesPerBlock) {
+    int phys = -1, ntok = 0;
+    if (tid < n_here) {
+      const int seq_page = has_cand ? p.cand_pages[(size_t)(b * p.Hq + h) * p.max_k + first + tid] : first + tid;
+      if (seq_page >= 0 && seq_page < n_seq_pages) {
+        phys = p.indices[page_base + seq_page];
+        if (phys < 0 || phys >= p.num_pages_total) phys = -1;
+      }
+      if (phys < 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+      ntok = (seq_page == n_seq_pages - 1) ? p.last_len[b] : kPage;
+    }
+    sm_phys[tid] = phys;
+    sm_ntok[tid] = phys < 0 ? 0 : ntok;
+  }
+  __syncthreads();
+
+  const int lane = tid & 31, warp = tid >> 5;
+  uint8_t* const ring = sm_ring + (size_t)warp * kRingDepth * kWarpStageBytes;
+  const uint32_t ring_u32 = smem_u32(ring);
+  const int n_pairs = (n_here + 1) >> 1;
+  const int my_pairs = (n_pairs > warp) ? (n_pairs - warp + kEstWarps - 1) / kEstWarps : 0;
+
+  // Per-lane constants of the five 16-byte copies of a stage: chunk c = c5*32+lane of the pair,
+  // i.e. page c/80 and chunk r = c%80 of its slab (0..63 codes, 64..79 scale/min).
+  uint32_t src16[5], dst_off[5];
+  bool second[5];
+#pragma unroll
+  for (int c5 = 0; c5 < 5; ++c5) {
+    const int c = c5 * 32 + lane;
+    const int pgl = c >= 80 ? 1 : 0;
+    const int r = c - pgl * 80;
+    second[c5] = pgl != 0;
+    src16[c5] = r;
+    if (r < 64) {
+      const int t = pgl * 16 + (r >> 2), g = r & 3;
+      dst_off[c5] = t * 64 + (((g + (t >> 1)) & 3) << 4);
+    } else {
+      dst_off[c5] = 2048 + (pgl * 16 + (r - 64)) * 16;
+    }
+  }
+  const uint4* const k4_head16 = reinterpret_cast<const uint4*>(p.k4 + (size_t)kvh * kSlab);
+  const uint32_t page_stride16 = (uint32_t)(p.Hkv * (kSlab / 16));
+
+  // issue the copies of this warp's i-th pair into the given ring slot
+  auto issue = [&](int i, int slot) {
+    if (i < my_pairs) {
+      const int pg0 = (warp + i * kEstWarps) * 2;
+      const uint32_t dst0 = ring_u32 + slot * kWarpStageBytes;
+      const int phys0 = sm_phys[pg0], phys1 = sm_phys[pg0 + 1];  // missing pages hold -1
+#pragma unroll
+      for (int c5 = 0; c5 < 5; ++c5) {
+        const int phys = second[c5] ? phys1 : phys0;
+        if (phys >= 0)
+          cp_async16(dst0 + dst_off[c5], k4_head16 + ((size_t)phys * page_stride16 + src16[c5]));
+      }
+    }
+    cp_async_commit();  // always commit so that group counting stays uniform
+  };
+
+#pragma unroll
+  for (int i = 0; i < kRingDepth - 1; ++i) issue(i, i);
+
+  if (q_thread) sm_q[qj >> 2][qj & 3].init(qf);
+  __syncthreads();
+
+  uint32_t rd_off[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) rd_off[g] = lane * 64 + (((g + (lane >> 1)) & 3) << 4);
+  float* const out_row = p.scores + (size_t)(b * p.Hq + h) * p.stride + (size_t)first * kPage;
+  int use_slot = 0, fill_slot = kRingDepth - 1;
+  for (int i = 0; i < my_pairs; ++i) {
+    cp_async_wait<kRingDepth - 2>();  // pair i has landed (this thread's copies)
+    __syncwarp();                     // ... and every other lane's
+    const int pg0 = (warp + i * kEstWarps) * 2;
+    const uint8_t* stage = ring + use_slot * kWarpStageBytes;
+    const int pgl = lane >> 4, tl = lane & 15;
+    const int ntok = sm_ntok[pg0 + pgl];
+    const bool present = sm_phys[pg0 + pgl] >= 0;
+    const uint4 sz = *reinterpret_cast<const uint4*>(stage + 2048 + lane * 16);
+    const uint32_t szw[4] = {sz.x, sz.y, sz.z, sz.w};
+    float acc[G];
+#pragma unroll
+    for (int hh = 0; hh < G; ++hh) acc[hh] = 0.f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const uint4 w = *reinterpret_cast<const uint4*>(stage + rd_off[g]);
+      const float2 szf = __half22float2(*reinterpret_cast<const __half2*>(&szw[g]));
+      const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+      uint32_t even[4], odd16[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        even[j] = ws[j] & 0x0F0F0F0Fu;
+        odd16[j] = ws[j] & 0xF0F0F0F0u;
+      }
+#pragma unroll
+      for (int hh = 0; hh < G; ++hh) {
+        const QRegs<VARIANT>& qs = sm_q[hh][g];  // same address in every lane: broadcast reads
+        int he = 0, ho = 0;
+        uint32_t le = 0, lo = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          he = dp4a_u8_s8(even[j], qs.qh_even[j], he);
+          ho = dp4a_u8_s8(odd16[j], qs.qh_odd[j], ho);
+          le = dp4a_u8_u8(even[j], qs.ql_even[j], le);
+          lo = dp4a_u8_u8(odd16[j], qs.ql_odd[j], lo);
+        }
+        const int tot = (he + (ho >> 4)) * 256 + (int)(le + (lo >> 4));
+        const float dot = (__int_as_float(0x4B400000 + tot) - 12582912.f) * qs.inv;
+        acc[hh] = fmaf(szf.x, dot, acc[hh]);
+        acc[hh] = fmaf(szf.y, qs.qsum, acc[hh]);
+      }
+    }
+    __syncwarp();      // all lanes are done reading the slot that the next issue overwrites
+    issue(i + kRingDepth - 1, fill_slot);
+    use_slot = (use_slot + 1 == kRingDepth) ? 0 : use_slot + 1;
+    fill_slot = (fill_slot + 1 == kRingDepth) ? 0 : fill_slot + 1;
+    if (present) {
+#pragma unroll
+      for (int hh = 0; hh < G; ++hh)
+        out_row[(size_t)hh * p.stride + (pg0 + pgl) * kPage + tl] = (tl < ntok) ? acc[hh] * p.sm_scale : -INFINITY;
+    }
   }
   cp_async_wait<0>();
 }
@@ -671,6 +837,12 @@ static int launch_one(const EstParams& p, int rows, int max_row_pages, bool ldg,
   if (ldg) {
     dim3 grid((max_row_pages + kPagesPerBlock - 1) / kPagesPerBlock, rows);
     estimate_int4_kernel<T, G, VARIANT><<<grid, kEstThreads, 0, st>>>(p);
+  } else if (G > 1 && VARIANT == VAR_DP4A && !p.force_ring) {
+    constexpr int kBytes = kEstWarps * kRingDepth * kWarpStageBytes;
+    auto kern = estimate_int4_warp_group_kernel<T, G>;
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+    dim3 grid((max_row_pages + kWarpPagesPerBlock - 1) / kWarpPagesPerBlock, rows);
+    kern<<<grid, kEstThreads, kBytes, st>>>(p);
   } else if (G == 1 && !p.force_ring) {
     constexpr int kBytes = kEstWarps * kRingDepth * kWarpStageBytes;
     auto kern = estimate_int4_warp_kernel<T, VARIANT>;

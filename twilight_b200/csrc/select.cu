@@ -59,19 +59,31 @@ quest_page_scores_kernel(const ScoreParams p) {
   const int sub = lane & 7, pg_in_step = lane >> 3;
   const int h0 = kvh * G;
 
-  float qf[G][16];
+  // Query heads of the group: in registers for small groups; for 4 or more heads the registers
+  // would cost too much occupancy, so q (as fp32) sits in shared memory and each head's 16 values
+  // are fetched per page with four 128-bit loads (the 8 lanes of a page read 8 distinct pieces).
+  // (Splitting q into positive and negative parts to use two FMAs per channel was measured
+  // slower: it doubles the shared-memory reads.)
+  constexpr bool kQInSmem = G > 2;
+  __shared__ __align__(16) float sm_qf[kQInSmem ? G : 1][kD];
+  float qf[kQInSmem ? 1 : G][16];
+  if (kQInSmem) {
+    for (int i = threadIdx.x; i < G * kD; i += kSelThreads)
+      sm_qf[i / kD][i % kD] = Elem<T>::to_f(reinterpret_cast<const T*>(p.q)[(size_t)(b * p.Hq + h0) * kD + i]);
+  } else {
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const T* qrow = reinterpret_cast<const T*>(p.q) + (size_t)(b * p.Hq + h0 + g) * kD;
+    for (int g = 0; g < G; ++g) {
+      const T* qrow = reinterpret_cast<const T*>(p.q) + (size_t)(b * p.Hq + h0 + g) * kD;
 #pragma unroll
-    for (int part = 0; part < 2; ++part) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(qrow) + sub + 8 * part);
-      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+      for (int part = 0; part < 2; ++part) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(qrow) + sub + 8 * part);
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f = Elem<T>::to_f2(u[k]);
-        qf[g][8 * part + 2 * k] = f.x;
-        qf[g][8 * part + 2 * k + 1] = f.y;
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = Elem<T>::to_f2(u[k]);
+          qf[g][8 * part + 2 * k] = f.x;
+          qf[g][8 * part + 2 * k + 1] = f.y;
+        }
       }
     }
   }
@@ -119,6 +131,7 @@ quest_page_scores_kernel(const ScoreParams p) {
 #pragma unroll
       for (int g = 0; g < G; ++g) acc[g] = 0.f;
       if (ok[u]) {
+        float lo16[16], hi16[16];
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
           const uint32_t un[4] = {mn[u][part].x, mn[u][part].y, mn[u][part].z, mn[u][part].w};
@@ -126,13 +139,28 @@ quest_page_scores_kernel(const ScoreParams p) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const float2 lo = Elem<T>::to_f2(un[k]), hi = Elem<T>::to_f2(ux[k]);
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-              const float q0 = qf[g][8 * part + 2 * k], q1 = qf[g][8 * part + 2 * k + 1];
-              acc[g] += fmaxf(q0 * hi.x, q0 * lo.x);
-              acc[g] += fmaxf(q1 * hi.y, q1 * lo.y);
-            }
+            lo16[8 * part + 2 * k] = lo.x; lo16[8 * part + 2 * k + 1] = lo.y;
+            hi16[8 * part + 2 * k] = hi.x; hi16[8 * part + 2 * k + 1] = hi.y;
           }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float qv[16];
+          if (kQInSmem) {
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+              const float4 a = *reinterpret_cast<const float4*>(&sm_qf[g][64 * part + 8 * sub]);
+              const float4 c = *reinterpret_cast<const float4*>(&sm_qf[g][64 * part + 8 * sub + 4]);
+              qv[8 * part + 0] = a.x; qv[8 * part + 1] = a.y; qv[8 * part + 2] = a.z; qv[8 * part + 3] = a.w;
+              qv[8 * part + 4] = c.x; qv[8 * part + 5] = c.y; qv[8 * part + 6] = c.z; qv[8 * part + 7] = c.w;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) qv[i] = qf[g][i];
+          }
+          // same order of additions in both forms
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[g] += fmaxf(qv[i] * hi16[i], qv[i] * lo16[i]);
         }
       }
 #pragma unroll
