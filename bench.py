@@ -147,6 +147,8 @@ def run_reference_arm(args):
     if rank != 0:
         return
     seqs = min(4, args.batch)
+    # torchrun pins OMP_NUM_THREADS to 1 per rank; this arm runs alone on rank 0 and may use the host
+    torch.set_num_threads(max(torch.get_num_threads(), os.cpu_count() or 1))
     threads = torch.get_num_threads()
     data = cpu_reference_inputs(args, args.heads, seqs)
     for _ in range(args.warmup):
@@ -393,19 +395,45 @@ def main():
     e2e = None
     if not args.no_e2e:
         host_q = [layers[i][0].cpu().pin_memory() for i in range(R)]
-        host_out = torch.empty(args.batch, args.heads, 128, dtype=torch.bfloat16).pin_memory()
+        host_out = torch.empty(args.layers, args.batch, args.heads, 128, dtype=torch.bfloat16).pin_memory()
         dq = torch.empty_like(layers[0][0])
 
-        def e2e_step():
+        def e2e_body():
+            # per layer pass: q from pinned host memory, the kernels, the output back to pinned memory
             for i in range(args.layers):
                 dq.copy_(host_q[i % R], non_blocking=True)
                 out = select_prune_attend_step(dq, layers[i % R][1], ws, variant=args.variant, out=outs[i])
                 if world > 1 and args.gather_per_layer:
                     dist.all_gather_into_tensor(gathered.view(-1, args.heads, 128), out)
-                host_out.copy_(out, non_blocking=True)
+                host_out[i].copy_(out, non_blocking=True)
             if world > 1 and not args.gather_per_layer:
                 dist.all_gather_into_tensor(gathered_all.view(-1, args.batch, args.heads, 128), outs)
-            torch.cuda.synchronize()
+
+        # the copies use fixed pinned buffers, so the whole token step (copies included) is one graph;
+        # a caller refills the pinned q buffers before each replay
+        e2e_graph = None
+        e2e_body()
+        torch.cuda.synchronize()
+        if not args.no_graph:
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    e2e_body()
+                torch.cuda.current_stream().wait_stream(side)
+                e2e_graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(e2e_graph):
+                    e2e_body()
+            except Exception as e:
+                sys.stderr.write(f"[bench] e2e graph capture failed ({e}); timing eager launches\n")
+                e2e_graph = None
+
+        def e2e_step():
+            if e2e_graph is not None:
+                e2e_graph.replay()
+            else:
+                e2e_body()
+            torch.cuda.synchronize()   # the host holds the token's outputs from here on
 
         for _ in range(3):
             e2e_step()
@@ -422,7 +450,7 @@ def main():
             dt = float(t.item())
         nbytes = args.batch * args.heads * 128 * 2 * args.layers
         e2e = {"value": args.batch * world * args.steps / dt, "unit": "tokens/s",
-               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "cuda_graph": e2e_graph is not None}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -458,6 +486,8 @@ def main():
         dist.barrier()
         if graph is not None:
             graph.reset()
+        if not args.no_e2e and e2e_graph is not None:
+            e2e_graph.reset()
         log("done")
         os._exit(0)
 

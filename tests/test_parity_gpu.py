@@ -573,3 +573,34 @@ def test_step_repeatable_and_graph_capturable():
         assert torch.equal(ws.indices.reshape(16, -1)[r, :n], i1.reshape(16, -1)[r, :n])
     assert (ws.out.float() - o1.float()).abs().max() <= 1e-2
     _status_ok(ws)
+
+
+def test_decode_attention_object_follows_the_reference_layer_rules():
+    """Layers 0 and 1 run full attention and record nothing; later layers are sparsified and their
+    budgets enter the average exactly as HistoryBudgetInfo does in the reference."""
+    from twilight_b200.pyimpl import enable_sparse_attention
+    lens = [300, 1000]
+    hq, hkv = 4, 2
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=torch.bfloat16, device=DEV, seed=51,
+                                  recipe="mid", shuffle_pages=True)
+    cfg = {"compressor": {"type": "none"}, "selector": {"type": "quest", "token_budget": 256, "chunk_size": 16},
+           "weight_estimator": {"type": "min_max_quant", "quant_bit": 4},
+           "weight_pruner": {"type": "top_p", "threshold": 0.9}, "skip_first_two_layers": True}
+    attn, info = enable_sparse_attention(cfg, hq, enable_budget_info=True)
+    outs, budgets = [], []
+    for layer in range(4):
+        outs.append(attn(layer, q[:, :, None, :], cache).clone())
+        budgets.append(attn._workspace(cache).budget.clone())
+    torch.cuda.synchronize()
+    # dense layers against fp64 attention over all tokens
+    for b, n in enumerate(lens):
+        for h in range(hq):
+            k, v = cache.dense_kv(b, h // (hq // hkv))
+            want = O.sparse_attention_fp32(q[b, h].float().cpu().numpy(), k.float().cpu().numpy(),
+                                           v.float().cpu().numpy(), np.arange(n), U.SM_SCALE)
+            assert np.abs(outs[0][b, h].float().cpu().numpy() - want).max() <= ATOL_MAX
+    assert torch.equal(outs[0], outs[1]) or (outs[0].float() - outs[1].float()).abs().max() <= 1e-2
+    assert (outs[2].float() - outs[0].float()).abs().max() > 0          # the sparse layers differ
+    want_avg = float(torch.stack([budgets[2].float().mean(), budgets[3].float().mean()]).mean())
+    assert abs(info.get_total_avg_budget() - want_avg) < 1e-4
+    assert len(info._budget_num) == 1 and sorted(info._budget_num[0]) == [2, 3]
