@@ -396,18 +396,42 @@ def main():
     if not args.no_e2e:
         host_q = [layers[i][0].cpu().pin_memory() for i in range(R)]
         host_out = torch.empty(args.layers, args.batch, args.heads, 128, dtype=torch.bfloat16).pin_memory()
-        dq = torch.empty_like(layers[0][0])
+        dq = [torch.empty_like(layers[0][0]) for _ in range(2)]
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
 
         def e2e_body():
-            # per layer pass: q from pinned host memory, the kernels, the output back to pinned memory
+            # per layer pass: q from pinned host memory, the kernels, the output back to pinned
+            # memory.  The copies run on two side streams (the two copy engines) so that the next
+            # layer's q arrives and the previous layer's output leaves while a layer computes.
+            main = torch.cuda.current_stream()
+            fork = torch.cuda.Event()
+            fork.record(main)
+            s_in.wait_event(fork)
+            s_out.wait_event(fork)
+            done = [None] * args.layers
             for i in range(args.layers):
-                dq.copy_(host_q[i % R], non_blocking=True)
-                out = select_prune_attend_step(dq, layers[i % R][1], ws, variant=args.variant, out=outs[i])
+                with torch.cuda.stream(s_in):
+                    if i >= 2:
+                        s_in.wait_event(done[i - 2])          # dq[i % 2] is free again
+                    dq[i % 2].copy_(host_q[i % R], non_blocking=True)
+                    arrived = torch.cuda.Event()
+                    arrived.record(s_in)
+                main.wait_event(arrived)
+                out = select_prune_attend_step(dq[i % 2], layers[i % R][1], ws, variant=args.variant, out=outs[i])
                 if world > 1 and args.gather_per_layer:
                     dist.all_gather_into_tensor(gathered.view(-1, args.heads, 128), out)
-                host_out[i].copy_(out, non_blocking=True)
+                done[i] = torch.cuda.Event()
+                done[i].record(main)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(done[i])
+                    host_out[i].copy_(out, non_blocking=True)
             if world > 1 and not args.gather_per_layer:
                 dist.all_gather_into_tensor(gathered_all.view(-1, args.batch, args.heads, 128), outs)
+            join_in, join_out = torch.cuda.Event(), torch.cuda.Event()
+            join_in.record(s_in)
+            join_out.record(s_out)
+            main.wait_event(join_in)
+            main.wait_event(join_out)
 
         # the copies use fixed pinned buffers, so the whole token step (copies included) is one graph;
         # a caller refills the pinned q buffers before each replay
