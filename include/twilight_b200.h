@@ -182,6 +182,29 @@ TWL_API int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pages
                            void* out, void* workspace, size_t workspace_bytes, int32_t chunk,
                            int32_t* status, void* stream);
 
+/* ---- attention over the estimated weights (use_estimated_weights_in_attn, -------------------
+ * twilight/pyimpl/attention.py:295-296).  twl_prune_with_weights is twl_topp_prune (mode 0, value =
+ * top-p) or twl_threshold_prune (mode 1, value = threshold) that also writes, next to every kept
+ * token, its un-normalised softmax weight exp(estimated logit - row maximum) into
+ * out_weights[rows][index_stride].  twl_sparse_decode_attn_weighted normalises those weights over
+ * the kept tokens and applies them to V; K pages are not read. */
+TWL_API int twl_prune_with_weights(int32_t mode, const float* scores, int32_t score_stride,
+                                   const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                                   const int32_t* cand_pages, const int32_t* cand_npages,
+                                   int32_t max_k, int32_t batch, int32_t num_q_heads,
+                                   const float* top_p_arr, float value, int32_t* out_indices,
+                                   int32_t index_stride, int32_t* out_budget, float* out_threshold,
+                                   float* out_weights, int32_t* status, void* stream);
+TWL_API int twl_sparse_decode_attn_weighted(const void* q, int dtype, const void* k_pages,
+                                            const void* v_pages, const int32_t* kv_indptr,
+                                            const int32_t* kv_indices, const int32_t* indices,
+                                            int32_t index_stride, const int32_t* budget,
+                                            const float* weights, int32_t batch, int32_t num_q_heads,
+                                            int32_t num_kv_heads, int32_t num_pages_total,
+                                            float sm_scale, void* out, void* workspace,
+                                            size_t workspace_bytes, int32_t chunk, int32_t* status,
+                                            void* stream);
+
 /* ---- kernel #3 without a caller workspace -------------------------------------------------
  * No counterpart in the reference.  Same computation and arguments as twl_sparse_decode_attn,
  * minus workspace/workspace_bytes: the split-KV scratch is a fixed array inside the library

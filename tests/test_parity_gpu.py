@@ -604,3 +604,36 @@ def test_decode_attention_object_follows_the_reference_layer_rules():
     want_avg = float(torch.stack([budgets[2].float().mean(), budgets[3].float().mean()]).mean())
     assert abs(info.get_total_avg_budget() - want_avg) < 1e-4
     assert len(info._budget_num) == 1 and sorted(info._budget_num[0]) == [2, 3]
+
+
+@pytest.mark.parametrize("pruner,value", [("top_p", 0.9), ("threshold", 4.0)])
+def test_attention_over_estimated_weights(pruner, value):
+    """use_estimated_weights_in_attn (attention.py:295-296): the final softmax runs over the
+    estimator's logits of the kept tokens instead of exact q.k."""
+    lens = [700, 2500, 17]
+    hq, hkv = 4, 2
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=torch.bfloat16, device=DEV, seed=61,
+                                  recipe="calibrated", shuffle_pages=True)
+    cfg = SparseConfig(selector="none", weight_pruner=pruner, threshold=value, use_estimated_weights_in_attn=True)
+    ws = DecodeWorkspace.for_cache(cache, hq, cfg)
+    out = select_prune_attend_step(q, cache, ws).clone()
+    cfg2 = SparseConfig(selector="none", weight_pruner=pruner, threshold=value)
+    ws2 = DecodeWorkspace.for_cache(cache, hq, cfg2)
+    out_exact = select_prune_attend_step(q, cache, ws2).clone()
+    torch.cuda.synchronize()
+    _status_ok(ws)
+    assert torch.equal(ws.budget, ws2.budget)            # pruning itself does not change
+    errs = []
+    for b, n in enumerate(lens):
+        for h in range(hq):
+            bud = int(ws.budget[b, h])
+            idx = ws.indices[b, h, :bud].cpu().numpy().astype(np.int64)
+            s = ws.scores[b, h].cpu().numpy().astype(np.float64)[idx]     # no selector: slot == token
+            w = np.exp(s - s.max())
+            w /= w.sum()
+            _, v = cache.dense_kv(b, h // (hq // hkv))
+            want = w @ v.float().cpu().numpy().astype(np.float64)[idx]
+            errs.append(np.abs(out[b, h].float().cpu().numpy() - want))
+    errs = np.stack(errs)
+    assert errs.max() <= ATOL_MAX and errs.mean() <= ATOL_MEAN
+    assert (out.float() - out_exact.float()).abs().max() > 1e-4   # it really is a different attention

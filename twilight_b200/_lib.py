@@ -34,6 +34,10 @@ SIGNATURES = {
     "twl_sparse_attn_workspace_bytes": (sz, [i32, i32, i32, i32]),
     "twl_sparse_decode_attn": (C.c_int, [ptr, C.c_int, ptr, ptr, ptr, ptr, ptr, i32, ptr, i32, i32,
                                          i32, i32, f32, ptr, ptr, sz, i32, ptr, ptr]),
+    "twl_prune_with_weights": (C.c_int, [i32, ptr, i32, ptr, ptr, ptr, ptr, i32, i32, i32, ptr, f32, ptr, i32,
+                                         ptr, ptr, ptr, ptr, ptr]),
+    "twl_sparse_decode_attn_weighted": (C.c_int, [ptr, C.c_int, ptr, ptr, ptr, ptr, ptr, i32, ptr, ptr, i32,
+                                                  i32, i32, i32, f32, ptr, ptr, sz, i32, ptr, ptr]),
     "twl_sparse_decode_attn_static": (C.c_int, [ptr, C.c_int, ptr, ptr, ptr, ptr, ptr, i32, ptr, i32, i32,
                                                 i32, i32, f32, ptr, i32, ptr, ptr]),
     "twl_quantize_k_pages": (C.c_int, [ptr, C.c_int, ptr, i64, ptr]),

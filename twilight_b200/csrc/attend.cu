@@ -40,6 +40,7 @@ struct AttParams {
   float* part_ml;     // [rows][kMaxChunksPerRow][2]
   float* part_o;      // [rows][kMaxChunksPerRow][128]
   int32_t* status;
+  const float* weights;  // [rows][index_stride] softmax weights of the kept tokens, or nullptr
   int index_stride, rows, Hq, Hkv, num_pages_total, chunk;
   float sm_scale;
 };
@@ -52,7 +53,9 @@ __device__ __forceinline__ int row_chunk_len(int budget, int chunk) {
   return len;
 }
 
-template <typename T>
+// USE_W: the caller supplies un-normalised softmax weights of the kept tokens (attention over
+// estimated weights, twilight/pyimpl/attention.py:295-296); K is then not read at all.
+template <typename T, bool USE_W = false>
 __global__ void __launch_bounds__(kAttThreads)
 sparse_decode_attn_kernel(const AttParams p) {
   extern __shared__ int sm_prefix[];  // rows + 1 exclusive prefix sums of chunk counts
@@ -137,7 +140,7 @@ sparse_decode_attn_kernel(const AttParams p) {
       return ro;
     };
 
-    float m = kNegBig, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float m = USE_W ? 0.f : kNegBig, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
     const int t_first = begin + warp * 32, t_step = kAttWarps * 32;
     int ro_next = lookup(load_tok(t_first + lane), t_first + lane);
     int tok_next = load_tok(t_first + t_step + lane);
@@ -149,10 +152,33 @@ sparse_decode_attn_kernel(const AttParams p) {
       for (int half = 0; half < 2; ++half) {
         const int n_here = min(16, end - t0 - half * 16);
         if (n_here <= 0) break;  // warp-uniform
+        if (USE_W) {
+          const int t = t0 + half * 16 + (lane & 15);
+          const int my_ro = __shfl_sync(0xffffffffu, ro, half * 16 + (lane & 15));
+          const float pw = (lane < 16 && t < end && my_ro >= 0)
+                               ? p.weights[(size_t)row * p.index_stride + t] : 0.f;
+          uint2 vw[16];
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const int rv = max(__shfl_sync(0xffffffffu, ro, half * 16 + u), 0);
+            vw[u] = ldg_stream_u2(vbase + (size_t)rv * kD + lane * 4);
+          }
+          l += warp_sum(pw);
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const float pu = __shfl_sync(0xffffffffu, pw, u);
+            const float2 v0 = Elem<T>::to_f2(vw[u].x), v1 = Elem<T>::to_f2(vw[u].y);
+            acc[0] = fmaf(pu, v0.x, acc[0]);
+            acc[1] = fmaf(pu, v0.y, acc[1]);
+            acc[2] = fmaf(pu, v1.x, acc[2]);
+            acc[3] = fmaf(pu, v1.y, acc[3]);
+          }
+          continue;
+        }
         // K and V rows of 16 tokens are all requested before any is used
         int rr[16];
         uint2 kk[16], vv[16];
-        if (n_here <= 4) {
+        if (!USE_W && n_here <= 4) {
           // short tail (budgets of a few tokens are the common case after pruning): four rows,
           // plain warp sums, no transpose
           uint2 k4[4], v4[4];
@@ -315,14 +341,12 @@ extern "C" size_t twl_sparse_attn_workspace_bytes(int32_t batch, int32_t num_q_h
   return bytes;
 }
 
-extern "C" int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pages,
-                                      const void* v_pages, const int32_t* kv_indptr,
-                                      const int32_t* kv_indices, const int32_t* indices,
-                                      int32_t index_stride, const int32_t* budget, int32_t batch,
-                                      int32_t num_q_heads, int32_t num_kv_heads,
-                                      int32_t num_pages_total, float sm_scale, void* out,
-                                      void* workspace, size_t workspace_bytes, int32_t chunk,
-                                      int32_t* status, void* stream) {
+static int attn_entry(const void* q, int dtype, const void* k_pages, const void* v_pages,
+                      const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* indices,
+                      int32_t index_stride, const int32_t* budget, const float* weights, int32_t batch,
+                      int32_t num_q_heads, int32_t num_kv_heads, int32_t num_pages_total,
+                      float sm_scale, void* out, void* workspace, size_t workspace_bytes,
+                      int32_t chunk, int32_t* status, void* stream) {
   using namespace twl;
   if (!q || !k_pages || !v_pages || !kv_indptr || !kv_indices || !indices || !budget || !out)
     return TWL_ERR_BAD_ARG;
@@ -342,7 +366,7 @@ extern "C" int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pa
   if ((int64_t)num_pages_total * num_kv_heads * kPage >= (int64_t)1 << 31) return TWL_ERR_TOO_LARGE;
   AttParams p;
   p.q = q; p.k = k_pages; p.v = v_pages; p.indptr = kv_indptr; p.indices = kv_indices;
-  p.idx = indices; p.budget = budget; p.out = out; p.status = status;
+  p.idx = indices; p.budget = budget; p.out = out; p.status = status; p.weights = weights;
   char* ws = static_cast<char*>(workspace);
   p.counters = reinterpret_cast<int32_t*>(ws);
   ws += align_up(rows * sizeof(int32_t), 256);
@@ -358,19 +382,50 @@ extern "C" int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pa
   const unsigned grid = (unsigned)std::min<size_t>(max_items, (size_t)kNumSMs * kAttBlocksPerSM);
   const size_t smem = (rows + 1) * sizeof(int);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define TWL_LAUNCH_ATT(TYPE, W)                                                                    \
+  do {                                                                                             \
+    auto kern = sparse_decode_attn_kernel<TYPE, W>;                                                \
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
+    kern<<<grid, kAttThreads, smem, st>>>(p);                                                      \
+  } while (0)
   if (dtype == TWL_F16) {
-    auto kern = sparse_decode_attn_kernel<__half>;
-    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    kern<<<grid, kAttThreads, smem, st>>>(p);
+    if (weights) TWL_LAUNCH_ATT(__half, true); else TWL_LAUNCH_ATT(__half, false);
   } else if (dtype == TWL_BF16) {
-    auto kern = sparse_decode_attn_kernel<__nv_bfloat16>;
-    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    kern<<<grid, kAttThreads, smem, st>>>(p);
+    if (weights) TWL_LAUNCH_ATT(__nv_bfloat16, true); else TWL_LAUNCH_ATT(__nv_bfloat16, false);
   } else {
     return TWL_ERR_UNSUPPORTED;
   }
+#undef TWL_LAUNCH_ATT
   TWL_CHECK_LAUNCH();
   return TWL_OK;
+}
+
+extern "C" int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pages,
+                                      const void* v_pages, const int32_t* kv_indptr,
+                                      const int32_t* kv_indices, const int32_t* indices,
+                                      int32_t index_stride, const int32_t* budget, int32_t batch,
+                                      int32_t num_q_heads, int32_t num_kv_heads,
+                                      int32_t num_pages_total, float sm_scale, void* out,
+                                      void* workspace, size_t workspace_bytes, int32_t chunk,
+                                      int32_t* status, void* stream) {
+  return attn_entry(q, dtype, k_pages, v_pages, kv_indptr, kv_indices, indices, index_stride, budget,
+                    nullptr, batch, num_q_heads, num_kv_heads, num_pages_total, sm_scale, out,
+                    workspace, workspace_bytes, chunk, status, stream);
+}
+
+extern "C" int twl_sparse_decode_attn_weighted(const void* q, int dtype, const void* k_pages,
+                                               const void* v_pages, const int32_t* kv_indptr,
+                                               const int32_t* kv_indices, const int32_t* indices,
+                                               int32_t index_stride, const int32_t* budget,
+                                               const float* weights, int32_t batch,
+                                               int32_t num_q_heads, int32_t num_kv_heads,
+                                               int32_t num_pages_total, float sm_scale, void* out,
+                                               void* workspace, size_t workspace_bytes,
+                                               int32_t chunk, int32_t* status, void* stream) {
+  if (!weights) return TWL_ERR_BAD_ARG;
+  return attn_entry(q, dtype, k_pages, v_pages, kv_indptr, kv_indices, indices, index_stride, budget,
+                    weights, batch, num_q_heads, num_kv_heads, num_pages_total, sm_scale, out,
+                    workspace, workspace_bytes, chunk, status, stream);
 }
 
 // ---- the same kernel on library-owned scratch ------------------------------------------------
@@ -440,7 +495,7 @@ extern "C" int twl_sparse_decode_attn_static(const void* q, int dtype, const voi
   TWL_CUDA_TRY(cudaMemsetAsync(scratch, 0, kStaticCounterBytes, st));
   AttParams p;
   p.q = q; p.k = k_pages; p.v = v_pages; p.indptr = kv_indptr; p.indices = kv_indices;
-  p.idx = indices; p.budget = budget; p.out = out; p.status = status;
+  p.idx = indices; p.budget = budget; p.out = out; p.status = status; p.weights = nullptr;
   char* ws = static_cast<char*>(scratch);
   p.counters = reinterpret_cast<int32_t*>(ws);
   p.part_ml = reinterpret_cast<float*>(ws + kStaticCounterBytes);

@@ -305,6 +305,7 @@ struct PruneParams {
   int32_t* out_indices;
   int32_t* out_budget;
   float* out_threshold;
+  float* out_weights;  // [rows][index_stride] un-normalised softmax weight of each kept token, or nullptr
   int32_t* status;
   int stride, max_k, B, Hq, index_stride, row_cap, list_cap;
   int mode;  // 0: softmax + top-p search; 1: keep scores above (score of token 0) - top_p_val
@@ -456,7 +457,10 @@ topp_prune_kernel(const PruneParams p) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           if (e[k] > low) {
-            if (pos < p.index_stride) out[pos] = tok0 + k;
+            if (pos < p.index_stride) {
+              out[pos] = tok0 + k;
+              if (p.out_weights) p.out_weights[(size_t)r * p.index_stride + pos] = thresh_mode ? fexp(e[k]) : e[k];
+            }
             ++pos;
           }
         }
@@ -482,6 +486,7 @@ topp_prune_kernel(const PruneParams p) {
       if (keep && pos < p.index_stride) {
         const int page = has_cand ? cand[i / kPage] : (i / kPage);
         out[pos] = page * kPage + (i % kPage);
+        if (p.out_weights) p.out_weights[(size_t)r * p.index_stride + pos] = thresh_mode ? fexp(prob(i)) : prob(i);
       }
       off += __popc(mk);
     }
@@ -560,7 +565,8 @@ static int prune_entry(int mode, const float* scores, int32_t score_stride, cons
                        const int32_t* kv_last_page_len, const int32_t* cand_pages,
                        const int32_t* cand_npages, int32_t max_k, int32_t batch, int32_t num_q_heads,
                        const float* arr, float val, int32_t* out_indices, int32_t index_stride,
-                       int32_t* out_budget, float* out_threshold, int32_t* status, void* stream) {
+                       int32_t* out_budget, float* out_threshold, float* out_weights, int32_t* status,
+                       void* stream) {
   if (!scores || !kv_indptr || !out_indices || !out_budget) return TWL_ERR_BAD_ARG;
   if (batch <= 0 || num_q_heads <= 0 || score_stride <= 0 || index_stride <= 0)
     return TWL_ERR_BAD_ARG;
@@ -571,6 +577,7 @@ static int prune_entry(int mode, const float* scores, int32_t score_stride, cons
   p.scores = scores; p.indptr = kv_indptr; p.last_len = kv_last_page_len;
   p.cand_pages = cand_pages; p.cand_npages = cand_npages; p.top_p_arr = arr;
   p.out_indices = out_indices; p.out_budget = out_budget; p.out_threshold = out_threshold;
+  p.out_weights = out_weights;
   p.status = status; p.stride = score_stride; p.max_k = max_k; p.B = batch; p.Hq = num_q_heads;
   p.index_stride = index_stride; p.top_p_val = val; p.mode = mode;
   return run_prune(p, batch, num_q_heads, score_stride, cand_pages, max_k,
@@ -587,7 +594,22 @@ extern "C" int twl_topp_prune(const float* scores, int32_t score_stride,
                               int32_t* status, void* stream) {
   return twl::prune_entry(0, scores, score_stride, kv_indptr, kv_last_page_len, cand_pages, cand_npages,
                           max_k, batch, num_q_heads, top_p_arr, top_p_val, out_indices, index_stride,
-                          out_budget, out_threshold, status, stream);
+                          out_budget, out_threshold, nullptr, status, stream);
+}
+
+extern "C" int twl_prune_with_weights(int32_t mode, const float* scores, int32_t score_stride,
+                                      const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                                      const int32_t* cand_pages, const int32_t* cand_npages,
+                                      int32_t max_k, int32_t batch, int32_t num_q_heads,
+                                      const float* top_p_arr, float value, int32_t* out_indices,
+                                      int32_t index_stride, int32_t* out_budget, float* out_threshold,
+                                      float* out_weights, int32_t* status, void* stream) {
+  if (mode != 0 && mode != 1) return TWL_ERR_BAD_ARG;
+  if (!out_weights) return TWL_ERR_BAD_ARG;
+  return twl::prune_entry(mode, scores, score_stride, kv_indptr, kv_last_page_len, cand_pages,
+                          cand_npages, max_k, batch, num_q_heads, mode == 0 ? top_p_arr : nullptr, value,
+                          out_indices, index_stride, out_budget, out_threshold, out_weights, status,
+                          stream);
 }
 
 extern "C" int twl_threshold_prune(const float* scores, int32_t score_stride,
@@ -598,5 +620,5 @@ extern "C" int twl_threshold_prune(const float* scores, int32_t score_stride,
                                    float* out_threshold, int32_t* status, void* stream) {
   return twl::prune_entry(1, scores, score_stride, kv_indptr, kv_last_page_len, cand_pages, cand_npages,
                           max_k, batch, num_q_heads, nullptr, threshold, out_indices, index_stride,
-                          out_budget, out_threshold, status, stream);
+                          out_budget, out_threshold, nullptr, status, stream);
 }

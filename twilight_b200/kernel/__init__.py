@@ -7,6 +7,7 @@ from .ops import (  # noqa: F401
     estimate_int4,
     topp_prune,
     threshold_prune,
+    prune_with_weights,
     sparse_decode_attn,
     sparse_attn_workspace_bytes,
     sparse_decode_attn_static,

@@ -213,6 +213,36 @@ def threshold_prune(scores, kv_indptr, kv_last_page_len, threshold: float, *, ca
     return indices, budget
 
 
+def prune_with_weights(scores, kv_indptr, kv_last_page_len, value, *, mode: str = "top_p",
+                       cand_pages=None, cand_npages=None, indices=None, budget=None, weights=None,
+                       threshold=None, status=None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Top-p (``mode="top_p"``) or element-wise threshold (``mode="threshold"``) pruner that also
+    returns, for every kept token, its un-normalised softmax weight over the estimated logits
+    (for attention with ``use_estimated_weights_in_attn``, twilight/pyimpl/attention.py:295-296).
+    Returns ``(indices, budget, weights[B,H,stride] fp32)``."""
+    lib = _lib.load()
+    _cuda_contig(scores, "scores")
+    b, hq, stride = scores.shape
+    dev = scores.device
+    if indices is None:
+        indices = torch.empty(b, hq, stride, dtype=torch.int32, device=dev)
+    if budget is None:
+        budget = torch.empty(b, hq, dtype=torch.int32, device=dev)
+    if weights is None:
+        weights = torch.empty(b, hq, indices.shape[-1], dtype=torch.float32, device=dev)
+    arr, val = (value, 0.0) if isinstance(value, torch.Tensor) else (None, float(value))
+    if arr is not None:
+        arr = arr.to(device=dev, dtype=torch.float32).contiguous()
+    max_k = 0 if cand_pages is None else cand_pages.shape[-1]
+    _lib.check(lib.twl_prune_with_weights({"top_p": 0, "threshold": 1}[mode], scores.data_ptr(), stride,
+                                          kv_indptr.data_ptr(), kv_last_page_len.data_ptr(),
+                                          _p(cand_pages), _p(cand_npages), max_k, b, hq, _p(arr), val,
+                                          indices.data_ptr(), indices.shape[-1], budget.data_ptr(),
+                                          _p(threshold), weights.data_ptr(), _p(status), _stream(dev)),
+               "prune_with_weights")
+    return indices, budget, weights
+
+
 def sparse_attn_workspace_bytes(batch: int, num_q_heads: int, index_stride: int, chunk: int = 256
                                 ) -> int:
     return int(_lib.load().twl_sparse_attn_workspace_bytes(batch, num_q_heads, index_stride, chunk))
@@ -220,10 +250,12 @@ def sparse_attn_workspace_bytes(batch: int, num_q_heads: int, index_stride: int,
 
 def sparse_decode_attn(q, k_pages, v_pages, kv_indptr, kv_indices, indices, budget, *,
                        sm_scale: Optional[float] = None, out=None, workspace=None,
-                       chunk: int = 256, status=None) -> torch.Tensor:
+                       chunk: int = 256, status=None, weights=None) -> torch.Tensor:
     """Attention of each (batch, query head) over its kept tokens
     (twilight/pyimpl/attention.py:188-190, :298-306).  Returns ``[B,H,D]`` in q's dtype.
-    ``workspace``: zero-initialised uint8 tensor of ``sparse_attn_workspace_bytes`` bytes."""
+    ``workspace``: zero-initialised uint8 tensor of ``sparse_attn_workspace_bytes`` bytes.
+    ``weights`` (from :func:`prune_with_weights`): attend with these weights instead of exact
+    q.k logits (attention.py:295-296); K is then not read."""
     lib = _lib.load()
     q = _q3(q)
     b, hq, _ = q.shape
@@ -236,6 +268,13 @@ def sparse_decode_attn(q, k_pages, v_pages, kv_indptr, kv_indices, indices, budg
                                 device=q.device)
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(HEAD_DIM)
+    if weights is not None:
+        _lib.check(lib.twl_sparse_decode_attn_weighted(
+            q.data_ptr(), _dtype_code(q), k_pages.data_ptr(), v_pages.data_ptr(), kv_indptr.data_ptr(),
+            kv_indices.data_ptr(), indices.data_ptr(), stride, budget.data_ptr(), weights.data_ptr(), b, hq,
+            hkv, n_total, sm_scale, out.data_ptr(), workspace.data_ptr(), workspace.numel(), chunk,
+            _p(status), _stream(q.device)), "sparse_decode_attn_weighted")
+        return out
     _lib.check(lib.twl_sparse_decode_attn(q.data_ptr(), _dtype_code(q), k_pages.data_ptr(),
                                           v_pages.data_ptr(), kv_indptr.data_ptr(),
                                           kv_indices.data_ptr(), indices.data_ptr(), stride,

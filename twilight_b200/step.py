@@ -64,8 +64,6 @@ class SparseConfig:
             raise _lib.TwilightError("the estimator kernel reads the 4-bit min/max cache only")
         if self.weight_pruner not in ("top_p", "threshold", "none"):
             raise _lib.TwilightError(f"pruner '{self.weight_pruner}' has no kernel on this path")
-        if self.use_estimated_weights_in_attn:
-            raise _lib.TwilightError("attention over estimated weights is not implemented")
 
 
 @dataclass
@@ -87,6 +85,7 @@ class DecodeWorkspace:
     threshold: torch.Tensor = field(init=False)
     out: torch.Tensor = field(init=False)
     attn_ws: torch.Tensor = field(init=False)
+    weights: Optional[torch.Tensor] = None   # softmax weights of kept tokens (estimated-weights mode)
     status: torch.Tensor = field(init=False)
 
     def __post_init__(self) -> None:
@@ -107,6 +106,8 @@ class DecodeWorkspace:
         self.attn_ws = torch.zeros(ops.sparse_attn_workspace_bytes(b, h, stride, self.attn_chunk),
                                    dtype=torch.uint8, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        if self.config.use_estimated_weights_in_attn:
+            self.weights = torch.empty(b, h, stride, dtype=torch.float32, device=dev)
 
     @classmethod
     def for_cache(cls, cache: PagedKVCache, num_q_heads: int, config: SparseConfig,
@@ -135,19 +136,26 @@ def select_prune_attend_step(q: torch.Tensor, cache: PagedKVCache, ws: DecodeWor
     ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
                       max_pages=ws.max_pages, cand_pages=cand_pages, cand_npages=cand_npages,
                       scores=ws.scores, variant=variant, status=ws.status)
-    # pruner "none" keeps every candidate with non-zero probability: top-p of 1 does not prune
-    if cfg.weight_pruner == "threshold":
-        ops.threshold_prune(ws.scores, cache.kv_indptr, cache.kv_last_page_len, cfg.threshold,
+    # pruner "none" keeps every candidate with non-zero probability: a top-p above 1 does that
+    mode = "threshold" if cfg.weight_pruner == "threshold" else "top_p"
+    value = cfg.threshold if cfg.weight_pruner in ("top_p", "threshold") else 2.0
+    if cfg.use_estimated_weights_in_attn:  # attention.py:295-296
+        ops.prune_with_weights(ws.scores, cache.kv_indptr, cache.kv_last_page_len, value, mode=mode,
+                               cand_pages=cand_pages, cand_npages=cand_npages, indices=ws.indices,
+                               budget=ws.budget, weights=ws.weights, threshold=ws.threshold,
+                               status=ws.status)
+    elif mode == "threshold":
+        ops.threshold_prune(ws.scores, cache.kv_indptr, cache.kv_last_page_len, value,
                             cand_pages=cand_pages, cand_npages=cand_npages, indices=ws.indices,
                             budget=ws.budget, cut=ws.threshold, status=ws.status)
     else:
-        top_p = cfg.threshold if cfg.weight_pruner == "top_p" else 2.0
-        ops.topp_prune(ws.scores, cache.kv_indptr, cache.kv_last_page_len, top_p,
+        ops.topp_prune(ws.scores, cache.kv_indptr, cache.kv_last_page_len, value,
                        cand_pages=cand_pages, cand_npages=cand_npages, indices=ws.indices,
                        budget=ws.budget, threshold=ws.threshold, status=ws.status)
     ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices,
                            ws.indices, ws.budget, out=ws.out if out is None else out,
-                           workspace=ws.attn_ws, chunk=ws.attn_chunk, status=ws.status)
+                           workspace=ws.attn_ws, chunk=ws.attn_chunk, status=ws.status,
+                           weights=ws.weights)
     return ws.out if out is None else out
 
 
