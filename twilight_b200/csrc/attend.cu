@@ -65,6 +65,7 @@ sparse_decode_attn_kernel(const AttParams p) {
   __shared__ int sm_ticket;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();  // budgets and index lists come from the pruner launched before
   // ---- schedule: chunk counts of all rows, prefix-summed (identical in every block) ----
   {
     int carry = 0;
@@ -386,7 +387,7 @@ static int attn_entry(const void* q, int dtype, const void* k_pages, const void*
   do {                                                                                             \
     auto kern = sparse_decode_attn_kernel<TYPE, W>;                                                \
     TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
-    kern<<<grid, kAttThreads, smem, st>>>(p);                                                      \
+    TWL_CUDA_TRY(launch_chain(kern, dim3(grid), dim3(kAttThreads), smem, st, p));                  \
   } while (0)
   if (dtype == TWL_F16) {
     if (weights) TWL_LAUNCH_ATT(__half, true); else TWL_LAUNCH_ATT(__half, false);

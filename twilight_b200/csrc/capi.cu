@@ -1,9 +1,18 @@
 // Library-level entry points: version, status strings, last CUDA error.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace twl {
 static thread_local cudaError_t g_last_error = cudaSuccess;
 void set_last_cuda_error(cudaError_t e) { g_last_error = e; }
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("TWL_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 }  // namespace twl
 
 extern "C" int twl_version(void) { return 100; }

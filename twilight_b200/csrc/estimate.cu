@@ -555,6 +555,7 @@ estimate_int4_warp_kernel(const EstParams p) {
   }
   const int page_base = p.indptr[b];
   const int n_seq_pages = p.indptr[b + 1] - page_base;
+  pdl_wait();  // candidate lists come from the kernel before; scores may still be read by an older one
   int n_pages = has_cand ? min(p.cand_npages[b * p.Hq + h], p.max_k) : n_seq_pages;
   if (n_pages > p.stride / kPage) {
     n_pages = p.stride / kPage;
@@ -689,6 +690,7 @@ estimate_int4_warp_group_kernel(const EstParams p) {
   const int h = kvh * G;  // first query head of the group
   const int page_base = p.indptr[b];
   const int n_seq_pages = p.indptr[b + 1] - page_base;
+  pdl_wait();  // candidate lists come from the kernel before; scores may still be read by an older one
   int n_pages = has_cand ? min(p.cand_npages[b * p.Hq + h], p.max_k) : n_seq_pages;
   if (n_pages > p.stride / kPage) {
     n_pages = p.stride / kPage;
@@ -842,13 +844,13 @@ static int launch_one(const EstParams& p, int rows, int max_row_pages, bool ldg,
     auto kern = estimate_int4_warp_group_kernel<T, G>;
     TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
     dim3 grid((max_row_pages + kWarpPagesPerBlock - 1) / kWarpPagesPerBlock, rows);
-    kern<<<grid, kEstThreads, kBytes, st>>>(p);
+    TWL_CUDA_TRY(launch_chain(kern, grid, dim3(kEstThreads), kBytes, st, p));
   } else if (G == 1 && !p.force_ring) {
     constexpr int kBytes = kEstWarps * kRingDepth * kWarpStageBytes;
     auto kern = estimate_int4_warp_kernel<T, VARIANT>;
     TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
     dim3 grid((max_row_pages + kWarpPagesPerBlock - 1) / kWarpPagesPerBlock, rows);
-    kern<<<grid, kEstThreads, kBytes, st>>>(p);
+    TWL_CUDA_TRY(launch_chain(kern, grid, dim3(kEstThreads), kBytes, st, p));
   } else {
     constexpr int kRingBytes = kStages * kStagePages * kSlab;
     auto kern = estimate_int4_tma_kernel<T, G, VARIANT>;

@@ -51,6 +51,7 @@ quest_page_scores_kernel(const ScoreParams p) {
   const int n_pages = min(p.indptr[b + 1] - page_base, p.max_pages);
   const int first = blockIdx.y * kSelPagesPerBlock;
   if (first >= n_pages) {
+    pdl_wait();  // every block waits, so that this grid never completes before the one before it
     if (p.counters != nullptr && n_pages <= 0 && blockIdx.y == 0 && threadIdx.x < G)
       p.cand_npages[b * p.Hq + kvh * G + threadIdx.x] = 0;
     return;
@@ -104,6 +105,7 @@ quest_page_scores_kernel(const ScoreParams p) {
     sm_phys[threadIdx.x] = phys;
   }
   __syncthreads();
+  pdl_wait();     // page_scores may still be read by an earlier launch
 
   constexpr int kU = 1;  // page quads in flight per warp (2 was measured slower)
   for (int l0 = warp * 4; l0 < n_here; l0 += (kSelThreads / 32) * 4 * kU) {
@@ -301,24 +303,32 @@ __device__ void topk_row(const float* src, int n, int k, int32_t* out, uint32_t*
   }
 }
 
+struct TopkParams {
+  const float* page_scores;
+  const int32_t* indptr;
+  int32_t* cand_pages;
+  int32_t* cand_npages;
+  int max_pages, Hq, token_budget, max_k;
+};
+
 __global__ void __launch_bounds__(kTopkThreads)
-quest_topk_pages_kernel(const float* __restrict__ page_scores, int max_pages,
-                        const int32_t* __restrict__ indptr, int Hq, int token_budget,
-                        int32_t* __restrict__ cand_pages, int32_t* __restrict__ cand_npages,
-                        int max_k) {
+quest_topk_pages_kernel(const TopkParams p) {
   extern __shared__ __align__(16) uint32_t keys[];  // max_pages keys
   __shared__ TopkScratch sc;
-  const int row = blockIdx.x, b = row / Hq;
-  const int n = min(indptr[b + 1] - indptr[b], max_pages);
-  int k = max(1, token_budget / kPage) + ((token_budget % kPage) != 0 ? 1 : 0);  // quest.py:93-95
-  k = min(min(k, n), max_k);                                                     // quest.py:98
-  int32_t* out = cand_pages + (size_t)row * max_k;
-  if (threadIdx.x == 0) cand_npages[row] = k;
+  const int row = blockIdx.x, b = row / p.Hq;
+  const int n = min(p.indptr[b + 1] - p.indptr[b], p.max_pages);
+  int k = max(1, p.token_budget / kPage) + ((p.token_budget % kPage) != 0 ? 1 : 0);  // quest.py:93-95
+  k = min(min(k, n), p.max_k);                                                       // quest.py:98
+  int32_t* out = p.cand_pages + (size_t)row * p.max_k;
+  pdl_wait();  // the page scores come from the kernel launched just before
+  if (threadIdx.x == 0) p.cand_npages[row] = k;
   if (k <= 0) return;
   if (k == n) {  // every page is kept
     for (int i = threadIdx.x; i < n; i += kTopkThreads) out[i] = i;
     return;
   }
+  const float* page_scores = p.page_scores;
+  const int max_pages = p.max_pages;
   topk_row(page_scores + (size_t)row * max_pages, n, k, out, keys, sc);
 }
 
@@ -332,7 +342,7 @@ static int launch_scores(const ScoreParams& p, cudaStream_t st) {
   if (smem > 48 * 1024)
     TWL_CUDA_TRY(cudaFuncSetAttribute(quest_page_scores_kernel<T, G>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024 * 4));
-  quest_page_scores_kernel<T, G><<<grid, kSelThreads, smem, st>>>(p);
+  TWL_CUDA_TRY(launch_chain(quest_page_scores_kernel<T, G>, grid, dim3(kSelThreads), smem, st, p));
   TWL_CHECK_LAUNCH();
   return TWL_OK;
 }
@@ -411,10 +421,12 @@ extern "C" int twl_quest_topk_pages(const float* page_scores, int32_t max_pages,
   const size_t smem = (size_t)max_pages * sizeof(uint32_t);
   TWL_CUDA_TRY(cudaFuncSetAttribute(quest_topk_pages_kernel,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024 * 4));
-  quest_topk_pages_kernel<<<batch * num_q_heads, kTopkThreads, smem,
-                            reinterpret_cast<cudaStream_t>(stream)>>>(
-      page_scores, max_pages, kv_indptr, num_q_heads, token_budget, cand_pages, cand_npages,
-      max_k);
+  TopkParams tp;
+  tp.page_scores = page_scores; tp.indptr = kv_indptr; tp.cand_pages = cand_pages;
+  tp.cand_npages = cand_npages; tp.max_pages = max_pages; tp.Hq = num_q_heads;
+  tp.token_budget = token_budget; tp.max_k = max_k;
+  TWL_CUDA_TRY(launch_chain(quest_topk_pages_kernel, dim3(batch * num_q_heads), dim3(kTopkThreads), smem,
+                            reinterpret_cast<cudaStream_t>(stream), tp));
   TWL_CHECK_LAUNCH();
   return TWL_OK;
 }

@@ -323,6 +323,7 @@ topp_prune_kernel(const PruneParams p) {
   const int b = r / p.Hq;
   const bool has_cand = p.cand_pages != nullptr;
   const int n_seq_pages = p.indptr[b + 1] - p.indptr[b];
+  pdl_wait();  // scores and candidate lists come from the kernels launched before
   int n_pages = has_cand ? min(p.cand_npages[r], p.max_k) : n_seq_pages;
   n_pages = min(n_pages, p.stride / kPage);
   const int n = n_pages * kPage;  // candidate slots; slots past the sequence end hold -inf
@@ -510,10 +511,10 @@ static int launch_prune(const PruneParams& p, int rows, int n_max, cudaStream_t 
     const size_t smem = (352 + (size_t)q.row_cap + q.list_cap) * sizeof(float);
     auto kern = topp_prune_kernel<THREADS, true>;
     TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<rows, THREADS, smem, st>>>(q);
+    TWL_CUDA_TRY(launch_chain(kern, dim3(rows), dim3(THREADS), smem, st, static_cast<const PruneParams&>(q)));
   } else {
     auto kern = topp_prune_kernel<THREADS, false>;
-    kern<<<rows, THREADS, 352 * sizeof(float), st>>>(p);
+    TWL_CUDA_TRY(launch_chain(kern, dim3(rows), dim3(THREADS), 352 * sizeof(float), st, p));
   }
   TWL_CHECK_LAUNCH();
   return TWL_OK;
