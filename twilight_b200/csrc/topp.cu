@@ -24,8 +24,8 @@ constexpr int kSearchRoundCap = 128;
 constexpr float kSearchEps = 1e-5f;
 // floats of a row that fit in shared memory next to the reduction scratch
 constexpr int kRowCap = 56 * 1024;
-// rows of the fused pruner also need a working list of a quarter of the row
-constexpr int kPruneRowCap = 44 * 1024;
+// rows of the fused pruner also need a working list of a quarter of the row (6 bytes an entry)
+constexpr int kPruneRowCap = 40 * 1024;
 
 template <typename T>
 struct Prec;  // rounding of the search scalars to the probability type, as the reference does
@@ -118,26 +118,75 @@ __device__ __forceinline__ int warp_incl_scan(int v) {
   return v;
 }
 
+// Block-wide (sum, sum, min, max) in one barrier; buf holds 4*32 floats.
+struct Red4 {
+  float z, s, a, b;
+};
+template <int THREADS>
+__device__ __forceinline__ Red4 block_red4(float z, float s, float a, float b, float* buf) {
+  constexpr int NW = THREADS / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  z = warp_sum(z);
+  s = warp_sum(s);
+  a = warp_min(a);
+  b = warp_max(b);
+  if (lane == 0) {
+    buf[warp] = z;
+    buf[32 + warp] = s;
+    buf[64 + warp] = a;
+    buf[96 + warp] = b;
+  }
+  __syncthreads();
+  Red4 r;
+  r.z = warp_sum(lane < NW ? buf[lane] : 0.f);
+  r.s = warp_sum(lane < NW ? buf[32 + lane] : 0.f);
+  r.a = warp_min(lane < NW ? buf[64 + lane] : INFINITY);
+  r.b = warp_max(lane < NW ? buf[96 + lane] : -INFINITY);
+  return r;
+}
+
+// Working list of the narrowing search: one private segment per warp, holding values and their
+// offsets inside the owning warp's slice of the row (so that the kept tokens can be written
+// from the list, in row order, without another pass over the row).
+struct SearchList {
+  float* vals;
+  uint16_t* rel;
+  int seg_cap;
+};
+
+struct SearchResult {
+  float low;
+  bool in_list;  // every element above `low` is in the list
+  int my_cnt;    // entries in this warp's segment (valid when in_list)
+};
+
 // The same search with the row in shared memory and a shrinking working set.
 //
 // Once `low` has risen, elements <= low can no longer change any of the three reductions of a
 // round: S sums x > mid > low, a = min{x > low}, and b = max({x <= high} U {low}) is at least low
 // anyway.  So whenever a round raises low, every warp squeezes its share of the current working
-// set (its slice of the row, later its own segment of the list) into a private segment of `list`
+// set (its slice of the row, later its own segment of the list) into its segment of the list
 // and the following rounds walk the list only; a squeeze whose survivors do not fit is dropped and
 // the search goes on over the old set.  Ordering inside a segment is fixed by lane order, so
 // results do not depend on scheduling.
-//   x: n floats (n % 4 == 0); list: NW segments of seg_cap floats; red: 256 words.
+//
+// The caller has already made the first round's pass (mid = x0/2) while it produced the row:
+// `first` holds its three reductions and `first_cnt` the number of elements above x0/2 that
+// this warp wrote (or would have written, had they fitted) to its segment.
+//   x: n floats (n % 4 == 0); red: 256 words; p, eps in the units of x.
 template <int THREADS>
-__device__ float topp_search_narrowing(const float* x, int n, float* list, int seg_cap, int* seg_cnt,
-                                       float x0, float p, float* red, int32_t* status) {
+__device__ SearchResult topp_search_narrowing(const float* x, int n, SearchList L, int* seg_cnt, float x0,
+                                              float p, float eps, Red3 first, int first_cnt, float* red,
+                                              int32_t* status) {
   constexpr int NW = THREADS / 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float4* x4 = reinterpret_cast<const float4*>(x);
   const int n4 = n >> 2;
   // slice of the row owned by this warp when the row is squeezed (whole float4 groups per lane)
   const int slice = ((n + NW - 1) / NW + 127) & ~127;
-  float* const my_seg = list + warp * seg_cap;
+  const int seg_cap = L.seg_cap;
+  float* const my_val = L.vals + warp * seg_cap;
+  uint16_t* const my_rel = L.rel + warp * seg_cap;
   bool in_list = false;
   int my_cnt = 0;    // elements in this warp's segment (valid when in_list)
   int total = n;     // size of the working set
@@ -145,27 +194,33 @@ __device__ float topp_search_narrowing(const float* x, int n, float* list, int s
   int round = 0;
   while (true) {
     const float mid = (low + high) * 0.5f;
-    float s = 0.f, a = high, b = low;
-    if (!in_list) {
-      for (int i = threadIdx.x; i < n4; i += THREADS) {
-        const float4 v = x4[i];
-        const float e[4] = {v.x, v.y, v.z, v.w};
+    Red3 r;
+    if (round == 0) {
+      r = first;
+    } else {
+      float s = 0.f, a = high, b = low;
+      if (!in_list) {
+        for (int i = threadIdx.x; i < n4; i += THREADS) {
+          const float4 v = x4[i];
+          const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          s += (e[k] > mid) ? e[k] : 0.f;
-          a = (e[k] > low) ? fminf(a, e[k]) : a;
-          b = (e[k] <= high) ? fmaxf(b, e[k]) : b;
+          for (int k = 0; k < 4; ++k) {
+            s += (e[k] > mid) ? e[k] : 0.f;
+            a = (e[k] > low) ? fminf(a, e[k]) : a;
+            b = (e[k] <= high) ? fmaxf(b, e[k]) : b;
+          }
+        }
+      } else {
+        for (int i = lane; i < my_cnt; i += 32) {
+          const float e = my_val[i];
+          s += (e > mid) ? e : 0.f;
+          a = (e > low) ? fminf(a, e) : a;
+          b = (e <= high) ? fmaxf(b, e) : b;
         }
       }
-    } else {
-      for (int i = lane; i < my_cnt; i += 32) {
-        const float e = my_seg[i];
-        s += (e > mid) ? e : 0.f;
-        a = (e > low) ? fminf(a, e) : a;
-        b = (e <= high) ? fmaxf(b, e) : b;
-      }
+      // never the buffer of the reduction before: the caller's last one used red + 96
+      r = block_red3<THREADS>(s, a, b, red + ((round + 1) & 1) * 96);
     }
-    const Red3 r = block_red3<THREADS>(s, a, b, red + (round & 1) * 96);
     bool rose = false;
     if (r.s >= p) {
       low = mid;
@@ -174,14 +229,16 @@ __device__ float topp_search_narrowing(const float* x, int n, float* list, int s
       high = fminf(mid, r.b);
     }
     ++round;
-    if (!(r.b - r.a > kSearchEps)) break;
+    if (!(r.b - r.a > eps)) break;
     if (round >= kSearchRoundCap) {
       if (threadIdx.x == 0) raise_flag(status, TWL_FLAG_ITER_CAP);
       break;
     }
     if (rose && total > 32) {
       int cnt = 0;
-      if (!in_list) {
+      if (round == 1) {
+        cnt = first_cnt;  // collected by the caller against the same mid
+      } else if (!in_list) {
         const int begin = warp * slice, end = min(n, begin + slice);
         for (int i0 = begin; i0 < end; i0 += 128) {
           const int i = i0 + lane * 4;
@@ -191,12 +248,16 @@ __device__ float topp_search_narrowing(const float* x, int n, float* list, int s
           int c = 0;
 #pragma unroll
           for (int k = 0; k < 4; ++k) c += e[k] > low ? 1 : 0;
+          if (__ballot_sync(0xffffffffu, c > 0) == 0) continue;
           const int inc = warp_incl_scan(c);
           int pos = cnt + inc - c;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             if (e[k] > low) {
-              if (pos < seg_cap) my_seg[pos] = e[k];
+              if (pos < seg_cap) {
+                my_val[pos] = e[k];
+                my_rel[pos] = (uint16_t)(i - begin + k);
+              }
               ++pos;
             }
           }
@@ -204,12 +265,17 @@ __device__ float topp_search_narrowing(const float* x, int n, float* list, int s
         }
       } else {
         for (int i0 = 0; i0 < my_cnt; i0 += 32) {
-          const float e = (i0 + lane < my_cnt) ? my_seg[i0 + lane] : 0.f;
+          const bool in = i0 + lane < my_cnt;
+          const float e = in ? my_val[i0 + lane] : 0.f;
+          const uint16_t rl = in ? my_rel[i0 + lane] : (uint16_t)0;
           const bool keep = e > low;
           const unsigned m = __ballot_sync(0xffffffffu, keep);
           const int pos = cnt + __popc(m & ((1u << lane) - 1));
           __syncwarp();  // every lane has read its element before the front is overwritten
-          if (keep) my_seg[pos] = e;
+          if (keep) {
+            my_val[pos] = e;
+            my_rel[pos] = rl;
+          }
           cnt += __popc(m);
         }
       }
@@ -231,7 +297,11 @@ __device__ float topp_search_narrowing(const float* x, int n, float* list, int s
       }
     }
   }
-  return low;
+  SearchResult res;
+  res.low = low;
+  res.in_list = in_list;
+  res.my_cnt = my_cnt;
+  return res;
 }
 
 // ---- dense mask form ------------------------------------------------------------------------
@@ -316,9 +386,11 @@ template <int THREADS, bool IN_SMEM>
 __global__ void __launch_bounds__(THREADS)
 topp_prune_kernel(const PruneParams p) {
   extern __shared__ __align__(16) float smem[];
+  constexpr int NW = THREADS / 32;
   float* red = smem;                                  // 256 words
   int* wsum = reinterpret_cast<int*>(smem + 256);     // 96 ints: 33 of scan scratch, 32 segment counts
-  float* row = smem + 352;                            // probabilities when IN_SMEM, then the list
+  float* row = smem + 352;                            // the row when IN_SMEM, then the working list
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int r = blockIdx.x;
   const int b = r / p.Hq;
   const bool has_cand = p.cand_pages != nullptr;
@@ -339,11 +411,15 @@ topp_prune_kernel(const PruneParams p) {
     }
     return;
   }
+  // every warp owns a contiguous slice of the row (whole groups of four slots per lane)
+  const int slice = ((n + NW - 1) / NW + 127) & ~127;
+  const int s_begin = warp * slice, s_end = min(n, s_begin + slice);
   // pass 1: row maximum (and stage the scores)
   float m = -INFINITY;
   {
     const float4* s4 = reinterpret_cast<const float4*>(src);  // stride and n are multiples of 16
     float4* r4 = reinterpret_cast<float4*>(row);
+#pragma unroll 4
     for (int i = threadIdx.x; i < n / 4; i += THREADS) {
       const float4 v = s4[i];
       if (IN_SMEM) r4[i] = v;
@@ -363,70 +439,129 @@ topp_prune_kernel(const PruneParams p) {
     return y;
   };
   const bool thresh_mode = p.mode == 1;
-  float inv_z = 1.f;
-  if (!thresh_mode) {
-    // pass 2: exponentials and their sum
-    float z = 0.f;
-    if (IN_SMEM) {
-      float4* r4 = reinterpret_cast<float4*>(row);
-      for (int i = threadIdx.x; i < n / 4; i += THREADS) {
-        float4 v = r4[i];
-        v.x = fexp(v.x); v.y = fexp(v.y); v.z = fexp(v.z); v.w = fexp(v.w);
-        r4[i] = v;
-        z += (v.x + v.y) + (v.z + v.w);
-      }
-    } else {
-      for (int i = threadIdx.x; i < n; i += THREADS) z += fexp(src[i]);
-    }
-    Red3 r2 = block_red3<THREADS>(z, 0.f, 0.f, red + 96);
-    z = r2.s;
-    inv_z = 1.f / z;
-    __syncthreads();
-    if (IN_SMEM) {
-      float4* r4 = reinterpret_cast<float4*>(row);
-      for (int i = threadIdx.x; i < n / 4; i += THREADS) {
-        float4 v = r4[i];
-        v.x *= inv_z; v.y *= inv_z; v.z *= inv_z; v.w *= inv_z;
-        r4[i] = v;
-      }
-      __syncthreads();
-    }
-  }
-  // value that is compared with the cut: the probability, or the raw score in threshold mode
-  auto prob = [&](int i) -> float {
-    return IN_SMEM ? row[i] : (thresh_mode ? src[i] : fexp(src[i]) * inv_z);
-  };
   // token 0 of the sequence: slot 0 when page 0 is a candidate, else it is not in the row
   const bool sink_present = has_cand ? (cand[0] == 0) : true;
   const float top_p = p.top_p_arr ? p.top_p_arr[r] : p.top_p_val;
-  float x0, low;
+  // x0 and low are in the units of what the row holds at emission time: raw scores in threshold
+  // mode, un-normalised exponentials for a row in shared memory (unit = 1/inv_z), probabilities
+  // for a row read from global memory
+  float x0, low, inv_z = 1.f;
+  bool from_list = false;
+  int list_cnt = 0;
+  SearchList L;
+  L.seg_cap = (p.list_cap / NW) & ~3;
+  L.vals = row + p.row_cap;
+  L.rel = reinterpret_cast<uint16_t*>(L.vals + p.list_cap);
+  auto prob = [&](int i) -> float {  // rows in global memory only
+    return thresh_mode ? src[i] : fexp(src[i]) * inv_z;
+  };
   if (thresh_mode) {
     // twilight/pyimpl/elementwise_threshold.py:15-17: weights > weight[0] - threshold; a token 0
     // outside the candidates holds the dtype's minimum there, so every candidate passes
-    x0 = sink_present ? prob(0) : -INFINITY;
+    x0 = sink_present ? (IN_SMEM ? row[0] : src[0]) : -INFINITY;
     low = sink_present ? x0 - top_p : -INFINITY;
-  } else {
-    x0 = sink_present ? prob(0) : 0.f;
+  } else if (IN_SMEM) {
+    // pass 2: exponentials in place and their sum.  The search runs on the un-normalised values
+    // (p and the stop width scaled by the sum instead of every element divided by it), so this
+    // pass already is the search's first round: low = 0, high = x0, mid = x0/2 need only the
+    // maximum.  Elements above x0/2 - the working set if that round raises low - go to the list.
+    x0 = sink_present ? fexp(row[0]) : 0.f;
+    __syncthreads();  // row[0] is read by everyone before its owner overwrites it
+    const float mid1 = x0 * 0.5f;
+    float z = 0.f, s1 = 0.f, a1 = x0, b1 = 0.f;
+    int first_cnt = 0;
+    float* const my_val = L.vals + warp * L.seg_cap;
+    uint16_t* const my_rel = L.rel + warp * L.seg_cap;
+    for (int i0 = s_begin; i0 < s_end; i0 += 128) {
+      const int i = i0 + lane * 4;
+      float4 v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);  // exp gives 0
+      if (i < s_end) v = *reinterpret_cast<const float4*>(row + i);
+      v.x = fexp(v.x); v.y = fexp(v.y); v.z = fexp(v.z); v.w = fexp(v.w);
+      if (i < s_end) *reinterpret_cast<float4*>(row + i) = v;
+      const float e[4] = {v.x, v.y, v.z, v.w};
+      z += (v.x + v.y) + (v.z + v.w);
+      int c = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        s1 += (e[k] > mid1) ? e[k] : 0.f;
+        a1 = (e[k] > 0.f) ? fminf(a1, e[k]) : a1;
+        b1 = (e[k] <= x0) ? fmaxf(b1, e[k]) : b1;
+        c += e[k] > mid1 ? 1 : 0;
+      }
+      if (__ballot_sync(0xffffffffu, c > 0) == 0) continue;
+      const int inc = warp_incl_scan(c);
+      int pos = first_cnt + inc - c;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (e[k] > mid1) {
+          if (pos < L.seg_cap) {
+            my_val[pos] = e[k];
+            my_rel[pos] = (uint16_t)(i - s_begin + k);
+          }
+          ++pos;
+        }
+      }
+      first_cnt += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    const Red4 r2 = block_red4<THREADS>(z, s1, a1, b1, red + 96);
+    inv_z = 1.f / r2.z;
     if (top_p > 1.f) {
       low = 0.f;  // no pruning asked for: keep every candidate with non-zero probability
-    } else if (IN_SMEM) {
-      const int seg_cap = ((p.list_cap / (THREADS / 32)) & ~3);
-      low = topp_search_narrowing<THREADS>(row, n, row + p.row_cap, seg_cap, wsum + 40, x0, top_p, red,
-                                           p.status);
     } else {
-      low = topp_search<THREADS, float>(prob, n, x0, top_p, red, p.status);
+      Red3 first;
+      first.s = r2.s; first.a = r2.a; first.b = r2.b;
+      const SearchResult res = topp_search_narrowing<THREADS>(row, n, L, wsum + 40, x0, top_p * r2.z,
+                                                              kSearchEps * r2.z, first, first_cnt, red,
+                                                              p.status);
+      low = res.low;
+      from_list = res.in_list;
+      list_cnt = res.my_cnt;
     }
+  } else {
+    float z = 0.f;
+    for (int i = threadIdx.x; i < n; i += THREADS) z += fexp(src[i]);
+    Red3 r2 = block_red3<THREADS>(z, 0.f, 0.f, red + 96);
+    inv_z = 1.f / r2.s;
+    __syncthreads();
+    x0 = sink_present ? prob(0) : 0.f;
+    low = top_p > 1.f ? 0.f : topp_search<THREADS, float>(prob, n, x0, top_p, red, p.status);
   }
   __syncthreads();
-  // ordered compaction: every warp owns a contiguous slice of the row, counts its kept slots,
-  // the warp counts are prefix-summed once, then each warp writes its tokens in order
-  constexpr int NW = THREADS / 32;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int slice = ((n + NW - 1) / NW + 127) & ~127;
-  const int s_begin = warp * slice, s_end = min(n, s_begin + slice);
+  // ordered compaction: the warps count the kept slots of their slices, the counts are
+  // prefix-summed once, then each warp writes its tokens in order
+  const float out_scale = (IN_SMEM && !thresh_mode) ? inv_z : 1.f;
   int32_t* out = p.out_indices + (size_t)r * p.index_stride;
+  float* out_w = p.out_weights ? p.out_weights + (size_t)r * p.index_stride : nullptr;
   int base;
-  if (IN_SMEM) {
+  if (IN_SMEM && from_list) {
+    // everything above `low` is in the list, each warp's segment in row order
+    const float* my_val = L.vals + warp * L.seg_cap;
+    const uint16_t* my_rel = L.rel + warp * L.seg_cap;
+    int my_cnt = 0;
+    for (int i0 = 0; i0 < list_cnt; i0 += 32) {
+      const bool keep = (i0 + lane < list_cnt) && (my_val[i0 + lane] > low);
+      my_cnt += __popc(__ballot_sync(0xffffffffu, keep));
+    }
+    if (lane == 0) wsum[warp] = my_cnt;
+    __syncthreads();
+    const int inc_w = warp_incl_scan(lane < NW ? wsum[lane] : 0);
+    base = __shfl_sync(0xffffffffu, inc_w, NW - 1);
+    int off = __shfl_sync(0xffffffffu, inc_w, warp) - my_cnt;
+    for (int i0 = 0; i0 < list_cnt; i0 += 32) {
+      const bool in = i0 + lane < list_cnt;
+      const float e = in ? my_val[i0 + lane] : 0.f;
+      const bool keep = in && e > low;
+      const unsigned mk = __ballot_sync(0xffffffffu, keep);
+      const int pos = off + __popc(mk & ((1u << lane) - 1));
+      if (keep && pos < p.index_stride) {
+        const int i = s_begin + my_rel[i0 + lane];
+        const int page = has_cand ? cand[i / kPage] : (i / kPage);
+        out[pos] = page * kPage + (i % kPage);
+        if (out_w) out_w[pos] = e * out_scale;
+      }
+      off += __popc(mk);
+    }
+  } else if (IN_SMEM) {
     // four consecutive slots per lane (n is a multiple of 16, so groups never straddle the end)
     int my_cnt = 0;
     for (int i0 = s_begin; i0 < s_end; i0 += 128) {
@@ -450,6 +585,7 @@ topp_prune_kernel(const PruneParams p) {
       int c = 0;
 #pragma unroll
       for (int k = 0; k < 4; ++k) c += e[k] > low ? 1 : 0;
+      if (__ballot_sync(0xffffffffu, c > 0) == 0) continue;
       const int inc = warp_incl_scan(c);
       if (c) {
         const int page = has_cand ? cand[i / kPage] : (i / kPage);  // i % 4 == 0: one page
@@ -460,7 +596,7 @@ topp_prune_kernel(const PruneParams p) {
           if (e[k] > low) {
             if (pos < p.index_stride) {
               out[pos] = tok0 + k;
-              if (p.out_weights) p.out_weights[(size_t)r * p.index_stride + pos] = thresh_mode ? fexp(e[k]) : e[k];
+              if (out_w) out_w[pos] = thresh_mode ? fexp(e[k]) : e[k] * out_scale;
             }
             ++pos;
           }
@@ -487,7 +623,7 @@ topp_prune_kernel(const PruneParams p) {
       if (keep && pos < p.index_stride) {
         const int page = has_cand ? cand[i / kPage] : (i / kPage);
         out[pos] = page * kPage + (i % kPage);
-        if (p.out_weights) p.out_weights[(size_t)r * p.index_stride + pos] = thresh_mode ? fexp(prob(i)) : prob(i);
+        if (out_w) out_w[pos] = thresh_mode ? fexp(prob(i)) : prob(i);
       }
       off += __popc(mk);
     }
@@ -496,8 +632,8 @@ topp_prune_kernel(const PruneParams p) {
     if (base > p.index_stride) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
     p.out_budget[r] = min(base, p.index_stride);
     if (p.out_threshold) {
-      p.out_threshold[2 * r] = low;
-      p.out_threshold[2 * r + 1] = x0;
+      p.out_threshold[2 * r] = low * out_scale;
+      p.out_threshold[2 * r + 1] = x0 * out_scale;
     }
   }
 }
@@ -507,8 +643,8 @@ static int launch_prune(const PruneParams& p, int rows, int n_max, cudaStream_t 
   if (n_max <= kPruneRowCap) {
     PruneParams q = p;
     q.row_cap = (n_max + 3) & ~3;
-    q.list_cap = std::max(q.row_cap / 4, 32 * (THREADS / 32));
-    const size_t smem = (352 + (size_t)q.row_cap + q.list_cap) * sizeof(float);
+    q.list_cap = std::max(q.row_cap / 4, 32 * (THREADS / 32));  // entries: a float and a uint16 each
+    const size_t smem = (((352 + (size_t)q.row_cap + q.list_cap) * sizeof(float) + (size_t)q.list_cap * 2) + 15) & ~(size_t)15;
     auto kern = topp_prune_kernel<THREADS, true>;
     TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     TWL_CUDA_TRY(launch_chain(kern, dim3(rows), dim3(THREADS), smem, st, static_cast<const PruneParams&>(q)));
