@@ -394,39 +394,46 @@ def main():
     # ---- end to end: q from pinned host memory in, output to pinned host memory out ------------
     e2e = None
     if not args.no_e2e:
-        host_q = [layers[i][0].cpu().pin_memory() for i in range(R)]
+        host_q = torch.stack([layers[i % R][0].cpu() for i in range(args.layers)]).pin_memory()
         host_out = torch.empty(args.layers, args.batch, args.heads, 128, dtype=torch.bfloat16).pin_memory()
-        dq = [torch.empty_like(layers[0][0]) for _ in range(2)]
+        dq = torch.empty(args.layers, *layers[0][0].shape, dtype=layers[0][0].dtype, device=dev)
         s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        last = args.layers - 1
 
         def e2e_body():
-            # per layer pass: q from pinned host memory, the kernels, the output back to pinned
-            # memory.  The copies run on two side streams (the two copy engines) so that the next
-            # layer's q arrives and the previous layer's output leaves while a layer computes.
+            # per token: every layer's q from pinned host memory, the kernels, every layer's output
+            # back to pinned memory.  Two copies each way on two side streams (the two copy engines):
+            # the first layer's q alone, so that it can start at once, the other layers' q while it
+            # runs; the outputs of all layers but the last while the last one runs, then the last.
+            # The kernel chain on the main stream stays free of copy nodes.
             main = torch.cuda.current_stream()
             fork = torch.cuda.Event()
             fork.record(main)
             s_in.wait_event(fork)
             s_out.wait_event(fork)
-            done = [None] * args.layers
+            first_in, rest_in = torch.cuda.Event(), torch.cuda.Event()
+            with torch.cuda.stream(s_in):
+                dq[:1].copy_(host_q[:1], non_blocking=True)
+                first_in.record(s_in)
+                if last > 0:
+                    dq[1:].copy_(host_q[1:], non_blocking=True)
+                rest_in.record(s_in)
+            main.wait_event(first_in)
             for i in range(args.layers):
-                with torch.cuda.stream(s_in):
-                    if i >= 2:
-                        s_in.wait_event(done[i - 2])          # dq[i % 2] is free again
-                    dq[i % 2].copy_(host_q[i % R], non_blocking=True)
-                    arrived = torch.cuda.Event()
-                    arrived.record(s_in)
-                main.wait_event(arrived)
-                out = select_prune_attend_step(dq[i % 2], layers[i % R][1], ws, variant=args.variant, out=outs[i])
+                if i == 1:
+                    main.wait_event(rest_in)
+                out = select_prune_attend_step(dq[i], layers[i % R][1], ws, variant=args.variant, out=outs[i])
                 if world > 1 and args.gather_per_layer:
                     dist.all_gather_into_tensor(gathered.view(-1, args.heads, 128), out)
-                done[i] = torch.cuda.Event()
-                done[i].record(main)
-                with torch.cuda.stream(s_out):
-                    s_out.wait_event(done[i])
-                    host_out[i].copy_(out, non_blocking=True)
+                if i == last - 1:
+                    most_done = torch.cuda.Event()
+                    most_done.record(main)
+                    with torch.cuda.stream(s_out):
+                        s_out.wait_event(most_done)
+                        host_out[:last].copy_(outs[:last], non_blocking=True)
             if world > 1 and not args.gather_per_layer:
                 dist.all_gather_into_tensor(gathered_all.view(-1, args.batch, args.heads, 128), outs)
+            host_out[last:].copy_(outs[last:], non_blocking=True)
             join_in, join_out = torch.cuda.Event(), torch.cuda.Event()
             join_in.record(s_in)
             join_out.record(s_out)
