@@ -293,6 +293,49 @@ def test_prune_with_candidates_and_missing_sink():
     assert torch.equal(budget[first_is_zero].long(), nz[first_is_zero])
 
 
+@pytest.mark.parametrize("n", [16, 2048, 8192, 40960, 40976, 65536])
+def test_prune_synthetic_rows_all_paths(n):
+    """Rows written directly (no estimator): up to 40960 slots a row is searched in shared memory
+    with the shrinking working list, longer rows from global memory.  Shapes: one heavy sink,
+    a flat row, a row where half the slots tie with the sink (the first round's survivors do not
+    fit the list, so the search stays on the row), and a row whose kept set grows in later rounds."""
+    g = torch.Generator(device=DEV).manual_seed(n)
+    rows = []
+    a = torch.randn(n, generator=g, device=DEV) * 2.0
+    a[0] += 8.0
+    rows.append(a)
+    rows.append(torch.randn(n, generator=g, device=DEV) * 0.1)
+    t = torch.randn(n, generator=g, device=DEV)
+    t[: max(1, n // 2)] = 6.0
+    rows.append(t)
+    s = torch.randn(n, generator=g, device=DEV)
+    s[0] = 3.0
+    s[1: 1 + min(n - 1, 300)] = 5.0       # many tokens above the sink: low stays 0 in round one
+    rows.append(s)
+    scores = torch.stack(rows).reshape(1, 4, n).contiguous()
+    indptr, _, last, _ = PagedKVCache.page_table([n], DEV)
+    thr = torch.zeros(1, 4, 2, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    idx, bud, w = ops.prune_with_weights(scores, indptr, last, 0.9, mode="top_p", threshold=thr, status=status)
+    idx2, bud2 = ops.topp_prune(scores, indptr, last, 0.9)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(bud, bud2)
+    pages = np.arange(n // PAGE)
+    for r in range(4):
+        row = scores[0, r].cpu().numpy()
+        probs, keep, low = U.oracle_prune_row(row, pages, 0.9)
+        k = int(bud[0, r])
+        got = idx[0, r, :k].cpu().numpy()
+        assert np.array_equal(got, idx2[0, r, :k].cpu().numpy())
+        assert (np.diff(got) > 0).all()
+        d = U.check_index_parity(got, probs, keep, low, pages, P_TOL)
+        assert abs(k - int(keep.sum())) <= d
+        np.testing.assert_allclose(w[0, r, :k].cpu().numpy(), probs[got], rtol=2e-3, atol=1e-9)
+        assert abs(float(thr[0, r, 1]) - probs[0]) <= 2e-3 * probs[0] + 1e-9     # probability of token 0
+        assert abs(float(thr[0, r, 0]) - float(low)) <= P_TOL
+
+
 def test_prune_is_deterministic_and_per_row_threshold():
     lens = [2048] * 3
     hq = 4
