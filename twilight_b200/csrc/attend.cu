@@ -8,13 +8,23 @@
 // kept tokens of a (batch, query head) row are cut into chunks of `chunk` tokens, every block
 // first prefix-sums the rows' chunk counts in shared memory (all blocks compute the same
 // table, nothing is exchanged), and block x then takes work items x, x+grid, ... of the
-// flattened (row, chunk) list.  A warp takes 32 indices at a time: each lane resolves one token
-// to its K/V row through the page table (one group ahead of use); every lane owns 4 of the 128
-// channels and requests its 8 bytes of the K and V rows of 16 tokens before using any of them;
-// a transpose-reduce leaves the dot product of token u in lane u; softmax is online (running
-// max, sum, 4 accumulators per lane).  Warps merge through shared memory; chunks of a
-// row merge through the caller's workspace, and the block that finishes a row's last chunk
-// (an atomic ticket, nobody waits) writes the output.
+// flattened (row, chunk) list.  The four warps of a block split an item's tokens evenly.
+//
+// A warp with more than a handful of tokens streams them through a private ring in shared
+// memory: 8 tokens per stage (their 256-byte K rows and V rows, fetched with 16-byte
+// asynchronous copies), three stages, so two stages are always in flight while one is used and
+// the bytes in flight do not depend on how the compiler schedules loads.  Token -> K/V row
+// lookups (index list, page table) run a 32-token group ahead of the copies.  Four lanes share
+// a token: lane (t, part) multiplies 32 channels of q (chunks part, part+4, part+8, part+12 of
+// eight channels) with its token's K, two shuffles finish the dot product, and the same lane
+// accumulates its token's V into 32 private accumulators, which are added across the eight
+// tokens once per item.  Odd tokens store their chunks with bit 2 of the chunk number flipped,
+// which makes the 16-byte reads of a quarter warp hit eight different bank groups.  Softmax is
+// online (running max shared by the warp, per-lane partial sums).
+// A warp with at most four tokens (budgets of a few tokens are the common case after pruning)
+// reads them straight into registers instead.
+// Warps merge through shared memory; chunks of a row merge through the caller's workspace, and
+// the block that finishes a row's last chunk (an atomic ticket, nobody waits) writes the output.
 #include <algorithm>
 
 #include "common.cuh"
@@ -24,7 +34,12 @@ namespace twl {
 constexpr int kAttThreads = 128;
 constexpr int kAttWarps = kAttThreads / 32;
 constexpr int kMaxChunksPerRow = 32;     // partial slots per row in the workspace
-constexpr int kAttBlocksPerSM = 5;
+constexpr int kAttStageTokens = 8;
+constexpr int kAttStageBytes = kAttStageTokens * 2 * kD * 2;  // K rows, then V rows: 4 KiB
+constexpr int kAttStages = 3;
+constexpr int kAttRingBytes = kAttWarps * kAttStages * kAttStageBytes;  // 48 KiB per block
+constexpr int kAttBlocksPerSM = 4;       // what the ring leaves room for
+constexpr int kAttMaxRows = 40 * 1024;   // schedule table (rows + 1 ints) next to the ring
 constexpr float kNegBig = -3.0e38f;      // finite stand-in for -inf so that exp(m_old-m_new) is defined
 
 struct AttParams {
@@ -56,9 +71,10 @@ __device__ __forceinline__ int row_chunk_len(int budget, int chunk) {
 // USE_W: the caller supplies un-normalised softmax weights of the kept tokens (attention over
 // estimated weights, twilight/pyimpl/attention.py:295-296); K is then not read at all.
 template <typename T, bool USE_W = false>
-__global__ void __launch_bounds__(kAttThreads)
+__global__ void __launch_bounds__(kAttThreads, kAttBlocksPerSM)
 sparse_decode_attn_kernel(const AttParams p) {
-  extern __shared__ int sm_prefix[];  // rows + 1 exclusive prefix sums of chunk counts
+  extern __shared__ __align__(128) unsigned char sm_dyn[];  // the ring, then the schedule table
+  int* sm_prefix = reinterpret_cast<int*>(sm_dyn + kAttRingBytes);  // rows + 1 exclusive prefix sums
   __shared__ float sm_o[kAttWarps][kD];
   __shared__ float sm_m[kAttWarps], sm_l[kAttWarps];
   __shared__ int sm_scan[33];
@@ -96,6 +112,8 @@ sparse_decode_attn_kernel(const AttParams p) {
 
   const T* kbase = reinterpret_cast<const T*>(p.k);
   const T* vbase = reinterpret_cast<const T*>(p.v);
+  unsigned char* const my_ring = sm_dyn + warp * (kAttStages * kAttStageBytes);
+  const uint32_t my_ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
 
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
     // row of this item: last r with prefix[r] <= item
@@ -114,163 +132,221 @@ sparse_decode_attn_kernel(const AttParams p) {
     const int page_base = p.indptr[b];
     const int n_seq_pages = p.indptr[b + 1] - page_base;
     const int32_t* idx = p.idx + (size_t)row * p.index_stride;
+    const T* qrow = reinterpret_cast<const T*>(p.q) + (size_t)row * kD;
     T* out = reinterpret_cast<T*>(p.out) + (size_t)row * kD;
 
-    // this lane's 4 channels of q, pre-multiplied by the softmax scale
-    float qf[4];
-    {
-      uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const T*>(p.q) + (size_t)row * kD) + lane);
-      float2 a = Elem<T>::to_f2(u.x), bq = Elem<T>::to_f2(u.y);
-      qf[0] = a.x * p.sm_scale; qf[1] = a.y * p.sm_scale;
-      qf[2] = bq.x * p.sm_scale; qf[3] = bq.y * p.sm_scale;
-    }
+    // this warp's share of the item: whole stages of 8 tokens
+    const int per_warp = (((end - begin) + kAttWarps - 1) / kAttWarps + kAttStageTokens - 1) & ~(kAttStageTokens - 1);
+    const int w_begin = begin + warp * per_warp;
+    const int w_end = min(end, w_begin + per_warp);
+    const int n_my = max(w_end - w_begin, 0);
 
-    // token index -> row number inside the K/V page arrays (-1 = nothing to read).  Lookups run
-    // one 32-token group ahead and index loads two groups ahead, so the streaming loop never
-    // waits on them; bad indices are only remembered here and reported after the loop.
+    // token index -> row number inside the K/V page arrays (-1 = nothing to read); bad indices
+    // are only remembered here and reported after the loop
     bool bad = false;
-    auto load_tok = [&](int t) -> int { return (t < end) ? idx[t] : -1; };
-    auto lookup = [&](int tok, int t) -> int {
+    auto lookup = [&](int t) -> int {
       int ro = -1;
-      const int pg = tok >> 4;
-      if (tok >= 0 && pg < n_seq_pages) {
-        const int phys = p.indices[page_base + pg];
-        if (phys >= 0 && phys < p.num_pages_total) ro = (phys * p.Hkv + kvh) * kPage + (tok & 15);
+      if (t < w_end) {
+        const int tok = idx[t];
+        const int pg = tok >> 4;
+        if (tok >= 0 && pg < n_seq_pages) {
+          const int phys = p.indices[page_base + pg];
+          if (phys >= 0 && phys < p.num_pages_total) ro = (phys * p.Hkv + kvh) * kPage + (tok & 15);
+        }
+        bad = bad || ro < 0;
       }
-      bad = bad || (t < end && ro < 0);
       return ro;
     };
 
-    float m = USE_W ? 0.f : kNegBig, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-    const int t_first = begin + warp * 32, t_step = kAttWarps * 32;
-    int ro_next = lookup(load_tok(t_first + lane), t_first + lane);
-    int tok_next = load_tok(t_first + t_step + lane);
-    for (int t0 = t_first; t0 < end; t0 += t_step) {
-      const int ro = ro_next;
-      ro_next = lookup(tok_next, t0 + t_step + lane);
-      tok_next = load_tok(t0 + 2 * t_step + lane);
+    float m = USE_W ? 0.f : kNegBig, l = 0.f;
+    if (n_my == 0) {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int n_here = min(16, end - t0 - half * 16);
-        if (n_here <= 0) break;  // warp-uniform
-        if (USE_W) {
-          const int t = t0 + half * 16 + (lane & 15);
-          const int my_ro = __shfl_sync(0xffffffffu, ro, half * 16 + (lane & 15));
-          const float pw = (lane < 16 && t < end && my_ro >= 0)
-                               ? p.weights[(size_t)row * p.index_stride + t] : 0.f;
-          uint2 vw[16];
+      for (int d = 0; d < 4; ++d) sm_o[warp][lane * 4 + d] = 0.f;
+    } else if (!USE_W && n_my <= 4) {
+      // ---- a handful of tokens: four rows straight into registers, lane owns 4 channels ----
+      float qf[4];
+      {
+        const uint2 u = __ldg(reinterpret_cast<const uint2*>(qrow) + lane);
+        const float2 a = Elem<T>::to_f2(u.x), bq = Elem<T>::to_f2(u.y);
+        qf[0] = a.x * p.sm_scale; qf[1] = a.y * p.sm_scale;
+        qf[2] = bq.x * p.sm_scale; qf[3] = bq.y * p.sm_scale;
+      }
+      const int ro = lookup(w_begin + lane);  // lanes past the share get -1
+      uint2 k4[4], v4[4];
+      int r4[4];
 #pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            const int rv = max(__shfl_sync(0xffffffffu, ro, half * 16 + u), 0);
-            vw[u] = ldg_stream_u2(vbase + (size_t)rv * kD + lane * 4);
+      for (int u = 0; u < 4; ++u) {
+        // absent tokens read row 0 (always mapped) and get weight 0, so the loads carry no branch
+        r4[u] = __shfl_sync(0xffffffffu, ro, u);
+        const int rc = max(r4[u], 0);
+        k4[u] = ldg_stream_u2(kbase + (size_t)rc * kD + lane * 4);
+        v4[u] = ldg_stream_u2(vbase + (size_t)rc * kD + lane * 4);
+      }
+      float sc[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 k0 = Elem<T>::to_f2(k4[u].x), k1 = Elem<T>::to_f2(k4[u].y);
+        sc[u] = qf[0] * k0.x + qf[1] * k0.y + qf[2] * k1.x + qf[3] * k1.y;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        sc[u] = (r4[u] >= 0) ? sc[u] : -INFINITY;
+        m = fmaxf(m, sc[u]);
+      }
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float pu = __expf(sc[u] - m);
+        l += pu;
+        const float2 v0 = Elem<T>::to_f2(v4[u].x), v1 = Elem<T>::to_f2(v4[u].y);
+        acc[0] = fmaf(pu, v0.x, acc[0]);
+        acc[1] = fmaf(pu, v0.y, acc[1]);
+        acc[2] = fmaf(pu, v1.x, acc[2]);
+        acc[3] = fmaf(pu, v1.y, acc[3]);
+      }
+#pragma unroll
+      for (int d = 0; d < 4; ++d) sm_o[warp][lane * 4 + d] = acc[d];
+    } else {
+      // ---- streamed through the ring ----
+      const int t8 = lane >> 2, part = lane & 3;
+      const int flip = (t8 & 1) << 2;
+      float qv[USE_W ? 1 : 32];
+      if (!USE_W) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 u = __ldg(reinterpret_cast<const uint4*>(qrow) + part + 4 * j);
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = Elem<T>::to_f2(w[i]);
+            qv[8 * j + 2 * i] = f.x * p.sm_scale;
+            qv[8 * j + 2 * i + 1] = f.y * p.sm_scale;
           }
-          l += warp_sum(pw);
-#pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            const float pu = __shfl_sync(0xffffffffu, pw, u);
-            const float2 v0 = Elem<T>::to_f2(vw[u].x), v1 = Elem<T>::to_f2(vw[u].y);
-            acc[0] = fmaf(pu, v0.x, acc[0]);
-            acc[1] = fmaf(pu, v0.y, acc[1]);
-            acc[2] = fmaf(pu, v1.x, acc[2]);
-            acc[3] = fmaf(pu, v1.y, acc[3]);
-          }
-          continue;
         }
-        // K and V rows of 16 tokens are all requested before any is used
-        int rr[16];
-        uint2 kk[16], vv[16];
-        if (!USE_W && n_here <= 4) {
-          // short tail (budgets of a few tokens are the common case after pruning): four rows,
-          // plain warp sums, no transpose
-          uint2 k4[4], v4[4];
-          int r4[4];
+      }
+      float acc[32];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            r4[u] = __shfl_sync(0xffffffffu, ro, half * 16 + u);
-            const int rc = max(r4[u], 0);
-            k4[u] = ldg_stream_u2(kbase + (size_t)rc * kD + lane * 4);
-            v4[u] = ldg_stream_u2(vbase + (size_t)rc * kD + lane * 4);
+      for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+      const int n_stages = (n_my + kAttStageTokens - 1) / kAttStageTokens;
+      const float* wrow = USE_W ? p.weights + (size_t)row * p.index_stride : nullptr;
+      // lane i of a group resolves token w_begin + 32*group + i (and, USE_W, loads its weight)
+      int ro_cur = -1, ro_next = lookup(w_begin + lane);
+      float w_cur = 0.f, w_next = 0.f;
+      if (USE_W) w_next = (w_begin + lane < w_end) ? wrow[w_begin + lane] : 0.f;
+      unsigned valid = 0;           // 8 bits per ring slot: which tokens of the stage count
+      float pw0 = 0.f, pw1 = 0.f, pw2 = 0.f;  // USE_W: this lane's token weight, per ring slot
+      int issue_j = 0, issue_slot = 0;
+      auto issue = [&]() {
+        // stage issue_j -> slot issue_slot
+        if (issue_j < n_stages) {
+          const int sub = issue_j & 3;
+          if (sub == 0) {
+            ro_cur = ro_next;
+            w_cur = w_next;
+            const int t_next = w_begin + 32 * ((issue_j >> 2) + 1) + lane;
+            ro_next = lookup(t_next);
+            if (USE_W) w_next = (t_next < w_end) ? wrow[t_next] : 0.f;
           }
-          float sc[4];
+          const uint32_t dst = my_ring_s + issue_slot * kAttStageBytes;
+          const int cpos = lane & 15;
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float2 k0 = Elem<T>::to_f2(k4[u].x), k1 = Elem<T>::to_f2(k4[u].y);
-            sc[u] = qf[0] * k0.x + qf[1] * k0.y + qf[2] * k1.x + qf[3] * k1.y;
+          for (int i = 0; i < 4; ++i) {
+            const int tk = 2 * i + (lane >> 4);
+            const int rc = max(__shfl_sync(0xffffffffu, ro_cur, sub * 8 + tk), 0);
+            const uint32_t off = tk * 256 + ((cpos ^ ((tk & 1) << 2)) << 4);
+            if (!USE_W) cp_async16(dst + off, kbase + (size_t)rc * kD + cpos * 8);
+            cp_async16(dst + kAttStageTokens * 256 + off, vbase + (size_t)rc * kD + cpos * 8);
           }
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-            for (int u = 0; u < 4; ++u) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+          const unsigned vm = (__ballot_sync(0xffffffffu, ro_cur >= 0) >> (sub * 8)) & 0xFFu;
+          valid = (valid & ~(0xFFu << (8 * issue_slot))) | (vm << (8 * issue_slot));
+          if (USE_W) {
+            const float pw = __shfl_sync(0xffffffffu, w_cur, sub * 8 + t8);
+            if (issue_slot == 0) pw0 = pw; else if (issue_slot == 1) pw1 = pw; else pw2 = pw;
           }
-          float m_new = m;
+        }
+        cp_async_commit();  // always, so that group counting stays uniform
+        ++issue_j;
+        issue_slot = (issue_slot + 1 == kAttStages) ? 0 : issue_slot + 1;
+      };
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            sc[u] = (u < n_here && r4[u] >= 0) ? sc[u] : -INFINITY;
-            m_new = fmaxf(m_new, sc[u]);
+      for (int s0 = 0; s0 < kAttStages - 1; ++s0) issue();
+      int slot = 0;
+      for (int k = 0; k < n_stages; ++k) {
+        issue();
+        cp_async_wait<kAttStages - 1>();  // stage k has landed (this thread's copies)
+        __syncwarp();
+        const unsigned char* st = my_ring + slot * kAttStageBytes;
+        const bool ok = (valid >> (8 * slot + t8)) & 1u;
+        float pw;
+        if (!USE_W) {
+          const uint4* krow = reinterpret_cast<const uint4*>(st + t8 * 256);
+          float s = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 kv = krow[(part + 4 * j) ^ flip];
+            const uint32_t w[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = Elem<T>::to_f2(w[i]);
+              s = fmaf(qv[8 * j + 2 * i], f.x, s);
+              s = fmaf(qv[8 * j + 2 * i + 1], f.y, s);
+            }
           }
+          s += __shfl_xor_sync(0xffffffffu, s, 1);
+          s += __shfl_xor_sync(0xffffffffu, s, 2);
+          s = ok ? s : -INFINITY;
+          float mx = s;
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+          const float m_new = fmaxf(m, mx);
           const float scale = __expf(m - m_new);
-          l *= scale;
+          pw = __expf(s - m_new);
+          l = l * scale + pw;
+          if (scale != 1.f) {  // warp-uniform: m and m_new are the same in every lane
 #pragma unroll
-          for (int d = 0; d < 4; ++d) acc[d] *= scale;
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float pu = __expf(sc[u] - m_new);
-            l += pu;
-            const float2 v0 = Elem<T>::to_f2(v4[u].x), v1 = Elem<T>::to_f2(v4[u].y);
-            acc[0] = fmaf(pu, v0.x, acc[0]);
-            acc[1] = fmaf(pu, v0.y, acc[1]);
-            acc[2] = fmaf(pu, v1.x, acc[2]);
-            acc[3] = fmaf(pu, v1.y, acc[3]);
+            for (int i = 0; i < 32; ++i) acc[i] *= scale;
           }
           m = m_new;
-          break;  // a tail of at most four tokens is the last work of this warp in the chunk
+        } else {
+          pw = slot == 0 ? pw0 : (slot == 1 ? pw1 : pw2);
+          pw = ok ? pw : 0.f;
+          l += pw;
         }
+        const uint4* vrow = reinterpret_cast<const uint4*>(st + kAttStageTokens * 256 + t8 * 256);
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          // tokens that are absent or invalid read row 0 (always mapped) and get weight 0 below,
-          // so that the 32 loads carry no branch and overlap freely
-          rr[u] = max(__shfl_sync(0xffffffffu, ro, half * 16 + u), 0);
-          kk[u] = ldg_stream_u2(kbase + (size_t)rr[u] * kD + lane * 4);
-          vv[u] = ldg_stream_u2(vbase + (size_t)rr[u] * kD + lane * 4);
-        }
-        float s[16];
+        for (int j = 0; j < 4; ++j) {
+          const uint4 vv = vrow[(part + 4 * j) ^ flip];
+          const uint32_t w[4] = {vv.x, vv.y, vv.z, vv.w};
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const float2 k0 = Elem<T>::to_f2(kk[u].x), k1 = Elem<T>::to_f2(kk[u].y);
-          s[u] = qf[0] * k0.x + qf[1] * k0.y + qf[2] * k1.x + qf[3] * k1.y;
-        }
-        // the two 16-lane halves first add up, then 15 exchanges leave the dot product of token
-        // u in lanes u and u+16
-#pragma unroll
-        for (int u = 0; u < 16; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], 16);
-#pragma unroll
-        for (int o = 8; o >= 1; o >>= 1) {
-          const bool upper = (lane & o) != 0;
-#pragma unroll
-          for (int i = 0; i < o; ++i) {
-            const float send = upper ? s[i] : s[i + o];
-            const float keep = upper ? s[i + o] : s[i];
-            s[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = Elem<T>::to_f2(w[i]);
+            acc[8 * j + 2 * i] = fmaf(pw, f.x, acc[8 * j + 2 * i]);
+            acc[8 * j + 2 * i + 1] = fmaf(pw, f.y, acc[8 * j + 2 * i + 1]);
           }
         }
-        const int my_r = __shfl_sync(0xffffffffu, ro, half * 16 + (lane & 15));
-        const float mine = (my_r >= 0 && lane < 16) ? s[0] : -INFINITY;  // one copy per token
-        const float m_new = fmaxf(m, warp_max(mine));
-        const float scale = __expf(m - m_new);
-        const float pw = __expf(mine - m_new);
-        l = l * scale + warp_sum(pw);
+        __syncwarp();  // every lane is done with the slot before it is refilled
+        slot = (slot + 1 == kAttStages) ? 0 : slot + 1;
+      }
+      cp_async_wait<0>();
+      // add up the eight tokens' lanes; the four lanes of a token carried the same weight
 #pragma unroll
-        for (int d = 0; d < 4; ++d) acc[d] *= scale;
+      for (int o = 4; o < 32; o <<= 1) {
+        l += __shfl_xor_sync(0xffffffffu, l, o);
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const float pu = __shfl_sync(0xffffffffu, pw, u);
-          const float2 v0 = Elem<T>::to_f2(vv[u].x), v1 = Elem<T>::to_f2(vv[u].y);
-          acc[0] = fmaf(pu, v0.x, acc[0]);
-          acc[1] = fmaf(pu, v0.y, acc[1]);
-          acc[2] = fmaf(pu, v1.x, acc[2]);
-          acc[3] = fmaf(pu, v1.y, acc[3]);
+        for (int i = 0; i < 32; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+      }
+      if (t8 == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sm_o[warp][(part + 4 * j) * 8 + i] = acc[8 * j + i];
         }
-        m = m_new;
       }
     }
     if (__any_sync(0xffffffffu, bad) && lane == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
@@ -280,8 +356,6 @@ sparse_decode_attn_kernel(const AttParams p) {
       sm_m[warp] = m;
       sm_l[warp] = l;
     }
-#pragma unroll
-    for (int d = 0; d < 4; ++d) sm_o[warp][lane * 4 + d] = acc[d];
     __syncthreads();
     float bm = kNegBig;
 #pragma unroll
@@ -328,6 +402,38 @@ sparse_decode_attn_kernel(const AttParams p) {
   }
 }
 
+// Launch shared by the entry points.  `chain`: launch with programmatic stream serialization so
+// that the kernel's prologue overlaps the tail of the kernel before it.
+static int launch_attn(const AttParams& p, int dtype, size_t rows, int32_t index_stride, int32_t chunk,
+                       bool chain, cudaStream_t st) {
+  // enough blocks to give every row its own block when budgets are small, never more than the
+  // machine holds at once
+  const size_t max_items =
+      rows * std::min<size_t>(kMaxChunksPerRow, ((size_t)index_stride + chunk - 1) / chunk);
+  const unsigned grid = (unsigned)std::min<size_t>(max_items, (size_t)kNumSMs * kAttBlocksPerSM);
+  const size_t smem = kAttRingBytes + (rows + 1) * sizeof(int);
+#define TWL_LAUNCH_ATT(TYPE, W)                                                                    \
+  do {                                                                                             \
+    auto kern = sparse_decode_attn_kernel<TYPE, W>;                                                \
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); \
+    if (chain) {                                                                                   \
+      TWL_CUDA_TRY(launch_chain(kern, dim3(grid), dim3(kAttThreads), smem, st, p));                \
+    } else {                                                                                       \
+      kern<<<grid, kAttThreads, smem, st>>>(p);                                                    \
+    }                                                                                              \
+  } while (0)
+  if (dtype == TWL_F16) {
+    if (p.weights) TWL_LAUNCH_ATT(__half, true); else TWL_LAUNCH_ATT(__half, false);
+  } else if (dtype == TWL_BF16) {
+    if (p.weights) TWL_LAUNCH_ATT(__nv_bfloat16, true); else TWL_LAUNCH_ATT(__nv_bfloat16, false);
+  } else {
+    return TWL_ERR_UNSUPPORTED;
+  }
+#undef TWL_LAUNCH_ATT
+  TWL_CHECK_LAUNCH();
+  return TWL_OK;
+}
+
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 }  // namespace twl
@@ -363,7 +469,7 @@ static int attn_entry(const void* q, int dtype, const void* k_pages, const void*
   if (!aligned(workspace, 16)) return TWL_ERR_MISALIGNED;
   const size_t rows = (size_t)batch * num_q_heads;
   // the schedule table lives in shared memory; K/V row numbers are 32-bit
-  if (rows > 48 * 1024) return TWL_ERR_TOO_LARGE;
+  if (rows > (size_t)kAttMaxRows) return TWL_ERR_TOO_LARGE;
   if ((int64_t)num_pages_total * num_kv_heads * kPage >= (int64_t)1 << 31) return TWL_ERR_TOO_LARGE;
   AttParams p;
   p.q = q; p.k = k_pages; p.v = v_pages; p.indptr = kv_indptr; p.indices = kv_indices;
@@ -376,29 +482,7 @@ static int attn_entry(const void* q, int dtype, const void* k_pages, const void*
   p.part_o = reinterpret_cast<float*>(ws);
   p.index_stride = index_stride; p.rows = (int)rows; p.Hq = num_q_heads; p.Hkv = num_kv_heads;
   p.num_pages_total = num_pages_total; p.chunk = chunk; p.sm_scale = sm_scale;
-  // enough blocks to give every row its own block when budgets are small, never more than the
-  // machine holds at once
-  const size_t max_items =
-      rows * std::min<size_t>(kMaxChunksPerRow, ((size_t)index_stride + chunk - 1) / chunk);
-  const unsigned grid = (unsigned)std::min<size_t>(max_items, (size_t)kNumSMs * kAttBlocksPerSM);
-  const size_t smem = (rows + 1) * sizeof(int);
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-#define TWL_LAUNCH_ATT(TYPE, W)                                                                    \
-  do {                                                                                             \
-    auto kern = sparse_decode_attn_kernel<TYPE, W>;                                                \
-    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
-    TWL_CUDA_TRY(launch_chain(kern, dim3(grid), dim3(kAttThreads), smem, st, p));                  \
-  } while (0)
-  if (dtype == TWL_F16) {
-    if (weights) TWL_LAUNCH_ATT(__half, true); else TWL_LAUNCH_ATT(__half, false);
-  } else if (dtype == TWL_BF16) {
-    if (weights) TWL_LAUNCH_ATT(__nv_bfloat16, true); else TWL_LAUNCH_ATT(__nv_bfloat16, false);
-  } else {
-    return TWL_ERR_UNSUPPORTED;
-  }
-#undef TWL_LAUNCH_ATT
-  TWL_CHECK_LAUNCH();
-  return TWL_OK;
+  return launch_attn(p, dtype, rows, index_stride, chunk, true, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pages,
@@ -503,17 +587,5 @@ extern "C" int twl_sparse_decode_attn_static(const void* q, int dtype, const voi
   p.part_o = reinterpret_cast<float*>(ws + kStaticCounterBytes + kStaticMlBytes);
   p.index_stride = index_stride; p.rows = (int)rows; p.Hq = num_q_heads; p.Hkv = num_kv_heads;
   p.num_pages_total = num_pages_total; p.chunk = chunk; p.sm_scale = sm_scale;
-  const size_t max_items =
-      rows * std::min<size_t>(kMaxChunksPerRow, ((size_t)index_stride + chunk - 1) / chunk);
-  const unsigned grid = (unsigned)std::min<size_t>(max_items, (size_t)kNumSMs * kAttBlocksPerSM);
-  const size_t smem = (rows + 1) * sizeof(int);
-  if (dtype == TWL_F16) {
-    sparse_decode_attn_kernel<__half><<<grid, kAttThreads, smem, st>>>(p);
-  } else if (dtype == TWL_BF16) {
-    sparse_decode_attn_kernel<__nv_bfloat16><<<grid, kAttThreads, smem, st>>>(p);
-  } else {
-    return TWL_ERR_UNSUPPORTED;
-  }
-  TWL_CHECK_LAUNCH();
-  return TWL_OK;
+  return launch_attn(p, dtype, rows, index_stride, chunk, false, st);
 }

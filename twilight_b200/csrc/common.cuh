@@ -156,6 +156,15 @@ __device__ __forceinline__ uint4 ldg_stream_u4(const void* p) {
                : "l"(p));
   return r;
 }
+// 16-byte asynchronous copy global -> shared (L2 only), commit and wait of the issuing thread's groups
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ uint2 ldg_stream_u2(const void* p) {
   uint2 r;
   asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];"

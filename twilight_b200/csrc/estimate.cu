@@ -524,15 +524,6 @@ constexpr int kRingDepth = 5;
 constexpr int kWarpStageBytes = 2 * kSlab;   // two pages
 constexpr int kWarpPagesPerBlock = 128;
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
 template <typename T, int VARIANT>
 __global__ void __launch_bounds__(kEstThreads)
 estimate_int4_warp_kernel(const EstParams p) {
