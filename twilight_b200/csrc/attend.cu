@@ -7,8 +7,9 @@
 // Budgets differ by orders of magnitude between heads, so work is balanced on the device: the
 // kept tokens of a (batch, query head) row are cut into chunks of `chunk` tokens, every block
 // first prefix-sums the rows' chunk counts in shared memory (all blocks compute the same
-// table, nothing is exchanged), and block x then takes work items x, x+grid, ... of the
-// flattened (row, chunk) list.  The four warps of a block split an item's tokens evenly.
+// tables, nothing is exchanged), and block x then takes item x of every round of grid-size
+// items from the flattened (row, chunk) list, in which the full-length chunks of all rows come
+// before the rows' last chunks.  The four warps of a block split an item's tokens evenly.
 //
 // A warp with more than a handful of tokens streams them through a private ring in shared
 // memory: 8 tokens per stage (their 256-byte K rows and V rows, fetched with 16-byte
@@ -39,7 +40,7 @@ constexpr int kAttStageBytes = kAttStageTokens * 2 * kD * 2;  // K rows, then V 
 constexpr int kAttStages = 3;
 constexpr int kAttRingBytes = kAttWarps * kAttStages * kAttStageBytes;  // 48 KiB per block
 constexpr int kAttBlocksPerSM = 4;       // what the ring leaves room for
-constexpr int kAttMaxRows = 40 * 1024;   // schedule table (rows + 1 ints) next to the ring
+constexpr int kAttMaxRows = 64 * 1024;   // schedule tables (1.25 bytes a row) next to the ring
 constexpr float kNegBig = -3.0e38f;      // finite stand-in for -inf so that exp(m_old-m_new) is defined
 
 struct AttParams {
@@ -74,37 +75,64 @@ template <typename T, bool USE_W = false>
 __global__ void __launch_bounds__(kAttThreads, kAttBlocksPerSM)
 sparse_decode_attn_kernel(const AttParams p) {
   extern __shared__ __align__(128) unsigned char sm_dyn[];  // the ring, then the schedule table
-  int* sm_prefix = reinterpret_cast<int*>(sm_dyn + kAttRingBytes);  // rows + 1 exclusive prefix sums
-  __shared__ float sm_o[kAttWarps][kD];
+  // schedule tables: chunk count of every row (one byte each) and, per group of 32 rows, the
+  // exclusive prefix sums of the rows' leading (full) chunks and of their last chunks
+  const int n_groups = (p.rows + 31) >> 5;
+  int* sm_glead = reinterpret_cast<int*>(sm_dyn + kAttRingBytes);
+  int* sm_glast = sm_glead + n_groups + 1;
+  uint8_t* sm_cnt = reinterpret_cast<uint8_t*>(sm_glast + n_groups + 1);
   __shared__ float sm_m[kAttWarps], sm_l[kAttWarps];
-  __shared__ int sm_scan[33];
+  __shared__ int sm_scan[66];
   __shared__ int sm_ticket;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // a warp's 128 merged output channels sit at the start of its (then idle) part of the ring
+  auto warp_out = [&](int w) -> float* {
+    return reinterpret_cast<float*>(sm_dyn + w * (kAttStages * kAttStageBytes));
+  };
+  float* const my_out = warp_out(warp);
   pdl_wait();  // budgets and index lists come from the pruner launched before
-  // ---- schedule: chunk counts of all rows, prefix-summed (identical in every block) ----
+  // ---- schedule (identical in every block): a row of n chunks has n-1 leading chunks of full
+  // length and one last chunk.  Work items are numbered with all leading chunks first, then all
+  // last chunks, so that the long items are dealt out before the short ones ----
   {
-    int carry = 0;
-    for (int r0 = 0; r0 < p.rows; r0 += kAttThreads) {
-      const int r = r0 + tid;
-      int n = 0;
-      if (r < p.rows) {
-        const int bud = min(max(p.budget[r], 0), p.index_stride);
-        const int len = row_chunk_len(bud, p.chunk);
-        n = (bud + len - 1) / len;
+    constexpr int kPer = 4;  // consecutive rows per thread and pass: 8 threads cover a group
+    int carry_lead = 0, carry_last = 0;
+    for (int r0 = 0; r0 < p.rows; r0 += kAttThreads * kPer) {
+      int s_lead = 0, s_last = 0;
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) {
+        const int r = r0 + tid * kPer + j;
+        if (r < p.rows) {
+          const int bud = min(max(p.budget[r], 0), p.index_stride);
+          const int len = row_chunk_len(bud, p.chunk);
+          const int n = (bud + len - 1) / len;
+          sm_cnt[r] = (uint8_t)n;
+          s_lead += max(n - 1, 0);
+          s_last += n > 0 ? 1 : 0;
+        }
       }
-      int total;
-      const int excl = block_excl_scan<kAttThreads>(n, &total, sm_scan);
-      if (r < p.rows) sm_prefix[r] = carry + excl;
-      carry += total;
+      int t_lead, t_last, e_lead, e_last;
+      block_excl_scan2<kAttThreads>(s_lead, s_last, &e_lead, &e_last, &t_lead, &t_last, sm_scan);
+      const int first = r0 + tid * kPer;
+      if ((tid & 7) == 0 && first < p.rows) {
+        sm_glead[first >> 5] = carry_lead + e_lead;
+        sm_glast[first >> 5] = carry_last + e_last;
+      }
+      carry_lead += t_lead;
+      carry_last += t_last;
     }
-    if (tid == 0) sm_prefix[p.rows] = carry;
+    if (tid == 0) {
+      sm_glead[n_groups] = carry_lead;
+      sm_glast[n_groups] = carry_last;
+    }
     __syncthreads();
   }
-  const int n_items = sm_prefix[p.rows];
+  const int n_lead = sm_glead[n_groups];
+  const int n_items = n_lead + sm_glast[n_groups];
   // rows without kept tokens produce zeros (the reference never meets this case)
   for (int r = blockIdx.x * kAttThreads + tid; r < p.rows; r += gridDim.x * kAttThreads) {
-    if (sm_prefix[r + 1] == sm_prefix[r]) {
+    if (sm_cnt[r] == 0) {
       T* o = reinterpret_cast<T*>(p.out) + (size_t)r * kD;
       for (int d = 0; d < kD; ++d) o[d] = Elem<T>::from_f(0.f);
     }
@@ -115,15 +143,36 @@ sparse_decode_attn_kernel(const AttParams p) {
   unsigned char* const my_ring = sm_dyn + warp * (kAttStages * kAttStageBytes);
   const uint32_t my_ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
 
-  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-    // row of this item: last r with prefix[r] <= item
-    int lo = 0, hi = p.rows;
+  // block x takes item x of every round of gridDim.x items; odd rounds run backwards, so the
+  // blocks that got the long items of one round get the short ones of the next
+  for (int base = 0, round = 0; base < n_items; base += gridDim.x, ++round) {
+    const int item = base + ((round & 1) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x);
+    if (item >= n_items) continue;  // the same for the whole block
+    // group of this item: last g with prefix[g] <= position in its list; then the lanes of
+    // every warp (all warps do the same) scan the group's 32 rows for the one that holds it
+    const bool leading = item < n_lead;
+    const int* pref = leading ? sm_glead : sm_glast;
+    const int pos = leading ? item : item - n_lead;
+    int lo = 0, hi = n_groups;
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
-      if (sm_prefix[mid] <= item) lo = mid; else hi = mid;
+      if (pref[mid] <= pos) lo = mid; else hi = mid;
     }
-    const int row = lo, c = item - sm_prefix[row];
-    const int n_parts = sm_prefix[row + 1] - sm_prefix[row];
+    const int rem = pos - pref[lo];
+    const int cand_row = lo * 32 + lane;
+    const int n_mine = cand_row < p.rows ? (int)sm_cnt[cand_row] : 0;
+    const int mine = leading ? max(n_mine - 1, 0) : (n_mine > 0 ? 1 : 0);
+    int inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += t;
+    }
+    const unsigned hit = __ballot_sync(0xffffffffu, inc - mine <= rem && rem < inc);  // one lane
+    const int src = __ffs(hit) - 1;
+    const int row = lo * 32 + src;
+    const int n_parts = __shfl_sync(0xffffffffu, n_mine, src);
+    const int c = leading ? rem - __shfl_sync(0xffffffffu, inc - mine, src) : n_parts - 1;
     const int b = row / p.Hq, h = row % p.Hq;
     const int kvh = h / (p.Hq / p.Hkv);
     const int budget = min(p.budget[row], p.index_stride);
@@ -161,7 +210,7 @@ sparse_decode_attn_kernel(const AttParams p) {
     float m = USE_W ? 0.f : kNegBig, l = 0.f;
     if (n_my == 0) {
 #pragma unroll
-      for (int d = 0; d < 4; ++d) sm_o[warp][lane * 4 + d] = 0.f;
+      for (int d = 0; d < 4; ++d) my_out[lane * 4 + d] = 0.f;
     } else if (!USE_W && n_my <= 4) {
       // ---- a handful of tokens: four rows straight into registers, lane owns 4 channels ----
       float qf[4];
@@ -210,7 +259,7 @@ sparse_decode_attn_kernel(const AttParams p) {
         acc[3] = fmaf(pu, v1.y, acc[3]);
       }
 #pragma unroll
-      for (int d = 0; d < 4; ++d) sm_o[warp][lane * 4 + d] = acc[d];
+      for (int d = 0; d < 4; ++d) my_out[lane * 4 + d] = acc[d];
     } else {
       // ---- streamed through the ring ----
       const int t8 = lane >> 2, part = lane & 3;
@@ -334,6 +383,7 @@ sparse_decode_attn_kernel(const AttParams p) {
         slot = (slot + 1 == kAttStages) ? 0 : slot + 1;
       }
       cp_async_wait<0>();
+      __syncwarp();  // the ring is idle from here on; its first bytes take the warp's result
       // add up the eight tokens' lanes; the four lanes of a token carried the same weight
 #pragma unroll
       for (int o = 4; o < 32; o <<= 1) {
@@ -345,7 +395,7 @@ sparse_decode_attn_kernel(const AttParams p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) sm_o[warp][(part + 4 * j) * 8 + i] = acc[8 * j + i];
+          for (int i = 0; i < 8; ++i) my_out[(part + 4 * j) * 8 + i] = acc[8 * j + i];
         }
       }
     }
@@ -366,7 +416,7 @@ sparse_decode_attn_kernel(const AttParams p) {
     for (int w = 0; w < kAttWarps; ++w) {
       const float f = __expf(sm_m[w] - bm);
       bl += f * sm_l[w];
-      bo += f * sm_o[w][d];
+      bo += f * warp_out(w)[d];
     }
     if (n_parts == 1) {
       out[d] = Elem<T>::from_f(bl > 0.f ? bo / bl : 0.f);
@@ -407,15 +457,19 @@ sparse_decode_attn_kernel(const AttParams p) {
 static int launch_attn(const AttParams& p, int dtype, size_t rows, int32_t index_stride, int32_t chunk,
                        bool chain, cudaStream_t st) {
   // enough blocks to give every row its own block when budgets are small, never more than the
-  // machine holds at once
+  // machine holds at once (the schedule tables grow with the row count and may cost a block)
   const size_t max_items =
       rows * std::min<size_t>(kMaxChunksPerRow, ((size_t)index_stride + chunk - 1) / chunk);
-  const unsigned grid = (unsigned)std::min<size_t>(max_items, (size_t)kNumSMs * kAttBlocksPerSM);
-  const size_t smem = kAttRingBytes + (rows + 1) * sizeof(int);
+  const size_t n_groups = (rows + 31) / 32;
+  const size_t smem = (kAttRingBytes + 2 * (n_groups + 1) * sizeof(int) + rows + 15) & ~(size_t)15;
 #define TWL_LAUNCH_ATT(TYPE, W)                                                                    \
   do {                                                                                             \
     auto kern = sparse_decode_attn_kernel<TYPE, W>;                                                \
     TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); \
+    int per_sm = 0;                                                                                \
+    TWL_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kAttThreads, smem)); \
+    if (per_sm < 1) return TWL_ERR_TOO_LARGE;                                                      \
+    const unsigned grid = (unsigned)std::min<size_t>(max_items, (size_t)kNumSMs * per_sm);        \
     if (chain) {                                                                                   \
       TWL_CUDA_TRY(launch_chain(kern, dim3(grid), dim3(kAttThreads), smem, st, p));                \
     } else {                                                                                       \

@@ -156,6 +156,53 @@ __device__ __forceinline__ uint4 ldg_stream_u4(const void* p) {
                : "l"(p));
   return r;
 }
+// Two block-wide exclusive prefix sums in the same barriers.  wsum: 66 ints of shared scratch.
+template <int THREADS>
+__device__ __forceinline__ void block_excl_scan2(int a, int b, int* ea, int* eb, int* ta, int* tb, int* wsum) {
+  constexpr int NW = THREADS / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int ia = a, ib = b;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int x = __shfl_up_sync(0xffffffffu, ia, o), y = __shfl_up_sync(0xffffffffu, ib, o);
+    if (lane >= o) {
+      ia += x;
+      ib += y;
+    }
+  }
+  if (lane == 31) {
+    wsum[warp] = ia;
+    wsum[33 + warp] = ib;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int wa = lane < NW ? wsum[lane] : 0, wb = lane < NW ? wsum[33 + lane] : 0;
+    int ja = wa, jb = wb;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int x = __shfl_up_sync(0xffffffffu, ja, o), y = __shfl_up_sync(0xffffffffu, jb, o);
+      if (lane >= o) {
+        ja += x;
+        jb += y;
+      }
+    }
+    if (lane < NW) {
+      wsum[lane] = ja - wa;
+      wsum[33 + lane] = jb - wb;
+    }
+    if (lane == 31) {
+      wsum[32] = ja;
+      wsum[65] = jb;
+    }
+  }
+  __syncthreads();
+  *ea = wsum[warp] + ia - a;
+  *eb = wsum[33 + warp] + ib - b;
+  *ta = wsum[32];
+  *tb = wsum[65];
+  __syncthreads();
+}
+
 // 16-byte asynchronous copy global -> shared (L2 only), commit and wait of the issuing thread's groups
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
