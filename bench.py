@@ -56,6 +56,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--kernel-reps", type=int, default=5)
+    ap.add_argument("--ablation", action="store_true",
+                    help="also time the captured layer pass with each kernel left out (its marginal cost in the chain)")
     return ap.parse_args()
 
 
@@ -313,9 +315,10 @@ def main():
     q0, c0 = layers[0]
     names = ["quest_page_scores", "quest_topk_pages", "estimate_int4", "topp_prune", "sparse_decode_attn"]
     lib = _lib.load()
-    s = torch.cuda.current_stream().cuda_stream
+    launch_stream = [torch.cuda.current_stream().cuda_stream]
 
     def launch(kname, q, cache):
+        s = launch_stream[0]
         b, hq, hkv = args.batch, args.heads, args.kv_heads
         if kname == "quest_page_scores":
             return lib.twl_quest_page_scores(q.data_ptr(), 1, cache.kmeta.data_ptr(), cache.kv_indptr.data_ptr(),
@@ -376,7 +379,7 @@ def main():
     # DRAM traffic per (sequence, KV head) row from the ncu capture summarised in
     # profiles/kernels_config1_small_case_ncu_full.md (256 rows; traffic is proportional to rows);
     # only valid for the configuration that capture was taken on
-    ncu_bytes_per_row = {"quest_page_scores": 276.33e6 / 256, "estimate_int4": 176.96e6 / 256}
+    ncu_bytes_per_row = {"quest_page_scores": 274.31e6 / 256, "estimate_int4": 177.27e6 / 256}
     traffic = None
     if (args.ctx, args.token_budget, args.heads, args.kv_heads) == (32768, 8192, 32, 32) and dominant in ncu_bytes_per_row:
         traffic = ncu_bytes_per_row[dominant] * args.batch * args.kv_heads
@@ -390,6 +393,38 @@ def main():
                 "step": {"algorithmic_bytes_per_layer_pass": bytes_["total"], "achieved": step_gbs,
                          "frac": step_gbs / peak, "frac_of_8000_nominal": step_gbs / 8000.0}}
 
+    if args.ablation:
+        def chain_us(skip):
+            st = torch.cuda.Stream()
+            with torch.cuda.stream(st):
+                s_ = st.cuda_stream
+                launch_stream[0] = s_
+                def one_pass(i):
+                    q, cache = layers[i % R]
+                    for n in names:
+                        if n != skip and launch(n, q, cache) != 0:
+                            raise RuntimeError(n)
+                for i in range(R):
+                    one_pass(i)
+                st.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=st):
+                    for i in range(8 * R):
+                        one_pass(i)
+                for _ in range(3):
+                    g.replay()
+                a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(st)
+                for _ in range(10):
+                    g.replay()
+                b_.record(st)
+                st.synchronize()
+                g.reset()
+            return a.elapsed_time(b_) / (10 * 8 * R) * 1000.0
+        full_us = chain_us(None)
+        roofline["chain"] = {"layer_pass_us": round(full_us, 2),
+                             "marginal_us": {n: round(full_us - chain_us(n), 2) for n in names}}
+        launch_stream[0] = torch.cuda.current_stream().cuda_stream
     log("per-kernel timing done")
     # ---- end to end: q from pinned host memory in, output to pinned host memory out ------------
     e2e = None
