@@ -143,7 +143,8 @@ TWL_API int twl_estimate_int4(const void* q, int dtype, const uint8_t* k4_pages,
  * out_indices[row][0..budget) = kept token positions, ascending; out_budget[row].
  * out_threshold (nullable) [rows][2] = {low, p(token 0)}.  rows with no candidate get 0.
  * A top_p above 1 skips the search and keeps every candidate whose probability is non-zero
- * (the reference's pruner "none").  Only slots below 16*(candidate pages of the row) are read. */
+ * (the reference's pruner "none").  Only slots below 16*(candidate pages of the row) are read.
+ * Rows of up to 40960 slots are searched in shared memory, longer rows from global memory. */
 TWL_API int twl_topp_prune(const float* scores, int32_t score_stride, const int32_t* kv_indptr,
                    const int32_t* kv_last_page_len, const int32_t* cand_pages,
                    const int32_t* cand_npages, int32_t max_k, int32_t batch,
@@ -166,9 +167,10 @@ TWL_API int twl_threshold_prune(const float* scores, int32_t score_stride, const
  * Replaces attention.py:188-190 restricted to the kept tokens and :298-306 (masked fp32
  * softmax, P.V).  A row's kept tokens are cut into chunks of `chunk` tokens (a multiple of 32;
  * <= 0 selects 256; the chunk grows for rows that would need more than 32 of them) and the
- * (row, chunk) work items are dealt round-robin to a grid that fills the GPU once, so heads
- * with large budgets do not serialise.  The block that finishes a row's last chunk merges the
- * partial (max, sum, acc) triples; no block waits for another.
+ * (row, chunk) work items are dealt, long ones first, to a grid that fills the GPU once, so
+ * heads with large budgets do not serialise.  The block that finishes a row's last chunk merges
+ * the partial (max, sum, acc) triples; no block waits for another.
+ * Limit: batch*num_q_heads <= 65536 (TWL_ERR_TOO_LARGE above).
  * workspace: twl_sparse_attn_workspace_bytes(...) bytes, 16-byte aligned; its first
  * batch*num_q_heads int32 words are arrival counters that must be zero on entry and are
  * left zero on exit.  Rows with budget 0 produce zeros. */
