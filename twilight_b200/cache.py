@@ -62,6 +62,7 @@ class PagedKVCache:
     kv_indices: torch.Tensor         # int32 [sum pages]
     kv_last_page_len: torch.Tensor   # int32 [B]
     seq_lens: List[int]              # host copy of the token counts
+    capacity_pages: Optional[int] = None   # pages per sequence a growing cache reserves (sizes workspaces)
 
     @property
     def batch(self) -> int:
@@ -159,3 +160,64 @@ class PagedKVCache:
         phys = self._phys(b)
         m = self.kmeta[phys, kvh]
         return m[:, 0], m[:, 1]
+
+
+class GrowingPagedCache:
+    """A paged cache of one attention layer that grows by one token per sequence and step.
+
+    Every sequence owns ``ceil(max_len / 16)`` consecutive physical pages from the start, so growing
+    never moves data: only the page table (a few integers, rebuilt on the host) changes.  All
+    sequences have the same length, as in a batch without padding.  ``view`` is the
+    :class:`PagedKVCache` the kernels read."""
+
+    def __init__(self, batch: int, num_kv_heads: int, max_len: int, dtype: torch.dtype, device) -> None:
+        self.batch, self.max_len = batch, max_len
+        self.pages_per_seq = (max_len + PAGE - 1) // PAGE
+        total = batch * self.pages_per_seq
+        self.k_pages = torch.zeros(total, num_kv_heads, PAGE, HEAD_DIM, dtype=dtype, device=device)
+        self.v_pages = torch.zeros_like(self.k_pages)
+        self.k4_pages = torch.zeros(total, num_kv_heads, K4_SLAB_BYTES, dtype=torch.uint8, device=device)
+        self.kmeta = torch.zeros(total, num_kv_heads, 2, HEAD_DIM, dtype=dtype, device=device)
+        self.length = 0
+        self.view: Optional[PagedKVCache] = None
+
+    def _set_length(self, n: int) -> None:
+        if n > self.max_len:
+            raise ValueError(f"cache holds {self.max_len} tokens per sequence, asked for {n}")
+        dev = self.k_pages.device
+        npg = (n + PAGE - 1) // PAGE
+        if self.view is None or (self.length + PAGE - 1) // PAGE != npg:
+            first = torch.arange(self.batch, dtype=torch.int32)[:, None] * self.pages_per_seq
+            indices = (first + torch.arange(npg, dtype=torch.int32)[None, :]).reshape(-1).to(dev)
+            indptr = (torch.arange(self.batch + 1, dtype=torch.int32) * npg).to(dev)
+        else:
+            indptr, indices = self.view.kv_indptr, self.view.kv_indices
+        last = torch.full((self.batch,), (n - 1) % PAGE + 1, dtype=torch.int32, device=dev)
+        self.view = PagedKVCache(self.k_pages, self.v_pages, self.k4_pages, self.kmeta, indptr, indices, last,
+                                 [n] * self.batch, capacity_pages=self.pages_per_seq)
+        self.length = n
+
+    def load(self, k: torch.Tensor, v: torch.Tensor) -> None:
+        """Replaces the contents with ``k, v [B,H_kv,L,128]`` (a prefill) and builds the INT4 slabs
+        and the page metadata with the CUDA kernels."""
+        b, hkv, n, d = k.shape
+        assert b == self.batch and d == HEAD_DIM and n >= 1
+        self._set_length(n)
+        npg = (n + PAGE - 1) // PAGE
+        pad = npg * PAGE - n
+        for src, dst in ((k, self.k_pages), (v, self.v_pages)):
+            x = src.to(dst.dtype)
+            if pad:
+                x = torch.cat([x, torch.zeros(b, hkv, pad, d, dtype=x.dtype, device=x.device)], 2)
+            pages = dst.view(b, self.pages_per_seq, hkv, PAGE, d)
+            pages[:, :npg] = x.reshape(b, hkv, npg, PAGE, d).permute(0, 2, 1, 3, 4)
+        self.view.build_aux()
+
+    def append(self, new_k: torch.Tensor, new_v: torch.Tensor) -> None:
+        """Adds one token per sequence (``new_k, new_v [B,H_kv,128]``): K/V rows, INT4 codes and the
+        page's metadata, by the append kernel."""
+        from .kernel import ops
+        self._set_length(self.length + 1)
+        c = self.view
+        ops.append_kv(new_k.to(self.k_pages.dtype).contiguous(), new_v.to(self.k_pages.dtype).contiguous(),
+                      c.k_pages, c.v_pages, c.k4_pages, c.kmeta, c.kv_indptr, c.kv_indices, c.kv_last_page_len)

@@ -26,25 +26,31 @@ class SparseDecodeAttention:
         self.num_q_heads = num_q_heads
         self.budget_info: Optional[HistoryBudgetInfo] = HistoryBudgetInfo() if enable_budget_info else None
         self._ws: Dict[Tuple, DecodeWorkspace] = {}
-        self._dense: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._dense: Dict[Tuple, Tuple] = {}
 
     def _workspace(self, cache: PagedKVCache) -> DecodeWorkspace:
-        key = (cache.batch, cache.max_pages, cache.device, cache.dtype)
+        # a growing cache sizes the buffers once, for the pages it reserves per sequence
+        pages = cache.capacity_pages or cache.max_pages
+        key = (cache.batch, pages, cache.device, cache.dtype)
         if key not in self._ws:
-            self._ws[key] = DecodeWorkspace.for_cache(cache, self.num_q_heads, self.config)
+            self._ws[key] = DecodeWorkspace(cache.batch, self.num_q_heads, pages, self.config, cache.device,
+                                            cache.dtype)
         return self._ws[key]
 
     def _dense_lists(self, cache: PagedKVCache, ws: DecodeWorkspace) -> Tuple[torch.Tensor, torch.Tensor]:
         """Index lists that keep every token (layers that are not sparsified)."""
-        key = (tuple(cache.seq_lens), cache.device)
+        key = (cache.batch, ws.max_pages, cache.device)
         if key not in self._dense:
-            stride = cache.max_pages * PAGE
+            stride = ws.max_pages * PAGE
             idx = torch.arange(stride, dtype=torch.int32, device=cache.device)
             idx = idx.expand(cache.batch, self.num_q_heads, stride).contiguous()
-            bud = torch.tensor(cache.seq_lens, dtype=torch.int32, device=cache.device)
-            bud = bud[:, None].expand(cache.batch, self.num_q_heads).contiguous()
-            self._dense[key] = (idx, bud)
-        return self._dense[key]
+            self._dense[key] = (idx, torch.empty(cache.batch, self.num_q_heads, dtype=torch.int32,
+                                                 device=cache.device), [])
+        idx, bud, lens = self._dense[key]
+        if lens != list(cache.seq_lens):
+            bud.copy_(torch.tensor(cache.seq_lens, dtype=torch.int32)[:, None].expand(-1, self.num_q_heads))
+            lens[:] = cache.seq_lens
+        return idx, bud
 
     def forward(self, layer_id: int, query_states: torch.Tensor, cache: PagedKVCache) -> torch.Tensor:
         """query ``[B,H_q,1,128]`` or ``[B,H_q,128]`` -> attention output ``[B,H_q,128]`` (a buffer
