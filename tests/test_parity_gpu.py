@@ -336,6 +336,43 @@ def test_prune_synthetic_rows_all_paths(n):
         assert abs(float(thr[0, r, 0]) - float(low)) <= P_TOL
 
 
+def test_prune_randomised_rows_vs_oracle():
+    """Seeded random row lengths, score shapes and top-p values; every row against the oracle."""
+    rng = np.random.default_rng(123)
+    lens = [int(x) for x in rng.integers(1, 6000, size=14)] + [16, 17, 4096]
+    hq = 4
+    stride = ((max(lens) + PAGE - 1) // PAGE) * PAGE
+    g = torch.Generator(device=DEV).manual_seed(5)
+    scores = torch.full((len(lens), hq, stride), float("-inf"), device=DEV)
+    for b, n in enumerate(lens):
+        for h in range(hq):
+            kind = (b + h) % 4
+            row = torch.randn(n, generator=g, device=DEV) * (0.2, 1.0, 3.0, 6.0)[kind]
+            if kind >= 2:
+                row[0] += (2.0, 10.0)[kind - 2]
+            if (b * hq + h) % 5 == 0 and n > 8:
+                row[n // 2: n // 2 + n // 8 + 1] = row[0]          # a block of ties with token 0
+            scores[b, h, :n] = row
+    indptr, _, last, _ = PagedKVCache.page_table(lens, DEV)
+    top_p = torch.tensor(rng.choice([0.5, 0.8, 0.9, 0.95, 0.99, 1.0], size=len(lens) * hq), dtype=torch.float32,
+                         device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    idx, bud = ops.topp_prune(scores, indptr, last, top_p, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for b, n in enumerate(lens):
+        npg = (n + PAGE - 1) // PAGE
+        pages = np.arange(npg)
+        for h in range(hq):
+            row = scores[b, h, : npg * PAGE].cpu().numpy()
+            probs, keep, low = U.oracle_prune_row(row, pages, float(top_p[b * hq + h]))
+            k = int(bud[b, h])
+            got = idx[b, h, :k].cpu().numpy()
+            assert (np.diff(got) > 0).all() and (got < n).all()
+            d = U.check_index_parity(got, probs, keep, low, pages, P_TOL)
+            assert abs(k - int(keep.sum())) <= d
+
+
 def test_prune_is_deterministic_and_per_row_threshold():
     lens = [2048] * 3
     hq = 4
@@ -476,6 +513,35 @@ def test_sparse_attention_vs_oracle(dt, chunk):
     assert errs.max() <= ATOL_MAX and errs.mean() <= ATOL_MEAN
     # split-KV merge order may differ between runs only in the last bit of the fp32 partial sums
     assert (out.float() - out2.float()).abs().max() <= 2e-2
+
+
+def test_sparse_attention_every_small_budget():
+    """Budgets 1..64, one per row: the 1-4 token register path, single and multiple ring stages,
+    warps with and without tokens, tails that end inside a stage or a 32-token lookup group."""
+    b_n, hq, hkv, n = 8, 8, 4, 200
+    q, cache = make_decode_inputs(b_n, hq, hkv, [n] * b_n, rho=0.02, dtype=torch.bfloat16, device=DEV, seed=21,
+                                  recipe="calibrated", shuffle_pages=True)
+    stride = cache.max_pages * PAGE
+    g = torch.Generator().manual_seed(22)
+    indices = torch.zeros(b_n, hq, stride, dtype=torch.int32)
+    budget = torch.zeros(b_n, hq, dtype=torch.int32)
+    for r in range(b_n * hq):
+        nb = r + 1
+        budget[r // hq, r % hq] = nb
+        indices[r // hq, r % hq, :nb] = torch.sort(torch.randperm(n, generator=g)[:nb])[0].int()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for chunk in (32, 512):
+        out = ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices,
+                                     indices.to(DEV), budget.to(DEV), chunk=chunk, status=status)
+        assert int(status.item()) == 0
+        for r in range(b_n * hq):
+            b, h = r // hq, r % hq
+            k, v = cache.dense_kv(b, h // (hq // hkv))
+            want = O.sparse_attention_fp32(q[b, h].float().cpu().numpy(), k.float().cpu().numpy(),
+                                           v.float().cpu().numpy(), indices[b, h, : r + 1].numpy().astype(np.int64),
+                                           U.SM_SCALE)
+            err = np.abs(out[b, h].float().cpu().numpy() - want)
+            assert err.max() <= ATOL_MAX, (chunk, r + 1, float(err.max()))
 
 
 def test_attention_workspace_and_bad_index_handling():
