@@ -477,6 +477,31 @@ def test_mask_operator_argument_errors():
         top_p_fp32_return_mask(torch.rand(1, 2, 1, 16, device=DEV).half(), 0.9)
 
 
+def test_oracle_topk_selector_mask_interface():
+    """twilight/pyimpl/top_k.py:7-30 on the radix-select kernel: the k largest entries per row."""
+    from twilight_b200.pyimpl import oracle_topk_selector
+    g = torch.Generator(device=DEV).manual_seed(31)
+    for (b, h, l, k) in [(2, 4, 1000, 64), (1, 3, 37, 5), (2, 2, 5000, 4096), (1, 2, 20, 50)]:
+        w = torch.randn(b, h, 1, l, generator=g, device=DEV)
+        got = oracle_topk_selector(w.to(torch.bfloat16).float() if l == 37 else w, k)
+        ref_in = w.to(torch.bfloat16).float() if l == 37 else w
+        kk = min(k, l)
+        want = torch.zeros_like(ref_in, dtype=torch.bool)
+        want.scatter_(-1, ref_in.topk(kk, dim=-1).indices, True)         # the reference's own lines
+        assert got.dtype == torch.bool and got.shape == w.shape
+        assert torch.equal(got.sum(-1), want.sum(-1))
+        # equal up to ties at the cut: the kept values are the same multiset
+        assert torch.equal(torch.where(got, ref_in, 0).sum(-1), torch.where(want, ref_in, 0).sum(-1)) or \
+            torch.allclose(torch.where(got, ref_in, 0).sum(-1), torch.where(want, ref_in, 0).sum(-1), rtol=1e-6)
+        if l != 37:
+            assert torch.equal(got, want)                                # fp32 randn: no ties
+    # ties go to the lower positions
+    w = torch.zeros(1, 1, 1, 64, device=DEV)
+    w[..., 10] = 1.0
+    m = oracle_topk_selector(w, 4)
+    assert m[0, 0, 0].nonzero().flatten().tolist() == [0, 1, 2, 10]
+
+
 # ---- attention ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("chunk", [32, 256])

@@ -190,19 +190,18 @@ sparse_decode_attn_kernel(const AttParams p) {
     const int w_end = min(end, w_begin + per_warp);
     const int n_my = max(w_end - w_begin, 0);
 
-    // token index -> row number inside the K/V page arrays (-1 = nothing to read); bad indices
-    // are only remembered here and reported after the loop
+    // token index -> row number inside the K/V page arrays (-1 = nothing to read).  The two
+    // dependent loads (index list, page table) are issued a 32-token group apart and their
+    // results are looked at a group later still, so the streaming loop never waits on them;
+    // bad indices are only remembered and reported after the loop
     bool bad = false;
-    auto lookup = [&](int t) -> int {
+    auto load_tok = [&](int t) -> int { return (t < w_end) ? idx[t] : -1; };
+    auto table = [&](int tok) -> int {
       int ro = -1;
-      if (t < w_end) {
-        const int tok = idx[t];
-        const int pg = tok >> 4;
-        if (tok >= 0 && pg < n_seq_pages) {
-          const int phys = p.indices[page_base + pg];
-          if (phys >= 0 && phys < p.num_pages_total) ro = (phys * p.Hkv + kvh) * kPage + (tok & 15);
-        }
-        bad = bad || ro < 0;
+      const int pg = tok >> 4;
+      if (tok >= 0 && pg < n_seq_pages) {
+        const int phys = p.indices[page_base + pg];
+        if (phys >= 0 && phys < p.num_pages_total) ro = (phys * p.Hkv + kvh) * kPage + (tok & 15);
       }
       return ro;
     };
@@ -220,7 +219,8 @@ sparse_decode_attn_kernel(const AttParams p) {
         qf[0] = a.x * p.sm_scale; qf[1] = a.y * p.sm_scale;
         qf[2] = bq.x * p.sm_scale; qf[3] = bq.y * p.sm_scale;
       }
-      const int ro = lookup(w_begin + lane);  // lanes past the share get -1
+      const int ro = table(load_tok(w_begin + lane));  // lanes past the share get -1
+      bad = (w_begin + lane < w_end) && ro < 0;
       uint2 k4[4], v4[4];
       int r4[4];
 #pragma unroll
@@ -284,7 +284,8 @@ sparse_decode_attn_kernel(const AttParams p) {
       const int n_stages = (n_my + kAttStageTokens - 1) / kAttStageTokens;
       const float* wrow = USE_W ? p.weights + (size_t)row * p.index_stride : nullptr;
       // lane i of a group resolves token w_begin + 32*group + i (and, USE_W, loads its weight)
-      int ro_cur = -1, ro_next = lookup(w_begin + lane);
+      int ro_cur = -1, ro_next = table(load_tok(w_begin + lane));
+      int tok_next = load_tok(w_begin + 32 + lane);
       float w_cur = 0.f, w_next = 0.f;
       if (USE_W) w_next = (w_begin + lane < w_end) ? wrow[w_begin + lane] : 0.f;
       unsigned valid = 0;           // 8 bits per ring slot: which tokens of the stage count
@@ -295,10 +296,13 @@ sparse_decode_attn_kernel(const AttParams p) {
         if (issue_j < n_stages) {
           const int sub = issue_j & 3;
           if (sub == 0) {
+            const int group = issue_j >> 2;
             ro_cur = ro_next;
             w_cur = w_next;
-            const int t_next = w_begin + 32 * ((issue_j >> 2) + 1) + lane;
-            ro_next = lookup(t_next);
+            bad = bad || ((w_begin + 32 * group + lane < w_end) && ro_cur < 0);
+            ro_next = table(tok_next);
+            tok_next = load_tok(w_begin + 32 * (group + 2) + lane);
+            const int t_next = w_begin + 32 * (group + 1) + lane;
             if (USE_W) w_next = (t_next < w_end) ? wrow[t_next] : 0.f;
           }
           const uint32_t dst = my_ring_s + issue_slot * kAttStageBytes;

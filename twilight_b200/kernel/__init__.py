@@ -4,6 +4,7 @@ from .ops import (  # noqa: F401
     top_p_fp16_return_mask,
     top_p_fp32_return_mask,
     quest_select,
+    quest_topk,
     estimate_int4,
     topp_prune,
     threshold_prune,

@@ -140,6 +140,27 @@ def quest_select(q, kmeta, kv_indptr, kv_indices, token_budget: int, *, max_page
     return cand_pages, cand_npages, page_scores
 
 
+def quest_topk(page_scores, kv_indptr, token_budget: int, *, max_pages: int, cand_pages=None,
+               cand_npages=None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The selection half of :func:`quest_select` on given fp32 scores ``[B,H,max_pages]``:
+    ascending positions of the ``max(1, budget//16) + (budget%16 != 0)`` best entries of each row
+    (twilight/pyimpl/quest.py:93-99), ties to the lower position."""
+    lib = _lib.load()
+    _cuda_contig(page_scores, "page_scores")
+    b, hq, stride = page_scores.shape
+    assert stride == max_pages and page_scores.dtype == torch.float32
+    max_k = min(max(1, token_budget // PAGE) + (1 if token_budget % PAGE else 0), max_pages)
+    dev = page_scores.device
+    if cand_pages is None:
+        cand_pages = torch.empty(b, hq, max_k, dtype=torch.int32, device=dev)
+    if cand_npages is None:
+        cand_npages = torch.empty(b, hq, dtype=torch.int32, device=dev)
+    _lib.check(lib.twl_quest_topk_pages(page_scores.data_ptr(), max_pages, kv_indptr.data_ptr(), b, hq,
+                                        token_budget, cand_pages.data_ptr(), cand_npages.data_ptr(),
+                                        cand_pages.shape[-1], _stream(dev)), "quest_topk_pages")
+    return cand_pages, cand_npages, page_scores
+
+
 def estimate_int4(q, k4_pages, kv_indptr, kv_indices, kv_last_page_len, *, max_pages: int,
                   cand_pages=None, cand_npages=None, sm_scale: Optional[float] = None,
                   scores=None, variant: int = 0, status=None) -> torch.Tensor:

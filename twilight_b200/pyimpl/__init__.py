@@ -4,4 +4,5 @@ from .attention import SparseDecodeAttention, enable_sparse_attention  # noqa: F
 from .quest import quest_selector  # noqa: F401
 from .state import (CompressorType, HistoryBudgetInfo, IndexSelectorType,  # noqa: F401
                     WeightEstimatorType, WeightPrunerType)
+from .top_k import oracle_topk_selector, top_k  # noqa: F401
 from .top_p import top_p_unnormalized  # noqa: F401
