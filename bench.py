@@ -56,6 +56,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--kernel-reps", type=int, default=5)
+    ap.add_argument("--attn-chunk", type=int, default=512, help="tokens per split-KV work item of the attention kernel")
     ap.add_argument("--ablation", action="store_true",
                     help="also time the captured layer pass with each kernel left out (its marginal cost in the chain)")
     return ap.parse_args()
@@ -232,7 +233,7 @@ def main():
                                       recipe=args.recipe, shuffle_pages=True)
         layers.append((q, cache))
     log(f"{R} resident layers generated")
-    ws = DecodeWorkspace.for_cache(layers[0][1], args.heads, cfg)
+    ws = DecodeWorkspace.for_cache(layers[0][1], args.heads, cfg, attn_chunk=args.attn_chunk)
     # Outputs of all layer passes of one token.  A rank's heads feed its own slice of the output
     # projection, so nothing has to cross GPUs between layers; the per-token result is gathered
     # once (NCCL all-gather), or after every layer pass with --gather-per-layer.
