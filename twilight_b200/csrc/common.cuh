@@ -43,11 +43,15 @@ void set_last_cuda_error(cudaError_t e);
 // stream-serialisation attribute, the next kernel of the chain may be set up and may run its own
 // prologue (reading q, the page table) while the previous one drains; it calls pdl_wait() before it
 // touches anything the previous kernel wrote.  Without the attribute the call does nothing.
-// (Letting blocks release their dependents early, griddepcontrol.launch_dependents at block start,
-// was measured 9 % slower per step: the waiting blocks of the next kernel crowd the last wave.)
+// The two small grids in front of a streaming kernel (page top-k, pruner) also release their
+// dependents at block start (pdl_release), so the next kernel's blocks are resident and past their
+// prologue when the small grid ends: 0.7 % per step.  The streaming kernels and the attention
+// kernel do not: their dependents' waiting blocks crowd them (9 % slower when every kernel did it,
+// 6 % slower for the attention kernel alone).
 bool pdl_enabled();  // TWL_PDL=0 in the environment switches it off
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <typename Params>
 inline cudaError_t launch_chain(void (*kernel)(Params), dim3 grid, dim3 block, size_t smem,

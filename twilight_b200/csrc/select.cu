@@ -315,6 +315,7 @@ __global__ void __launch_bounds__(kTopkThreads)
 quest_topk_pages_kernel(const TopkParams p) {
   extern __shared__ __align__(16) uint32_t keys[];  // max_pages keys
   __shared__ TopkScratch sc;
+  pdl_release();  // the estimator's blocks may move in and set up while this small grid works
   const int row = blockIdx.x, b = row / p.Hq;
   const int n = min(p.indptr[b + 1] - p.indptr[b], p.max_pages);
   int k = max(1, p.token_budget / kPage) + ((p.token_budget % kPage) != 0 ? 1 : 0);  // quest.py:93-95

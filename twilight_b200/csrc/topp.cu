@@ -391,6 +391,7 @@ topp_prune_kernel(const PruneParams p) {
   int* wsum = reinterpret_cast<int*>(smem + 256);     // 96 ints: 33 of scan scratch, 32 segment counts
   float* row = smem + 352;                            // the row when IN_SMEM, then the working list
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_release();  // the attention kernel's blocks may move in while this small grid works
   const int r = blockIdx.x;
   const int b = r / p.Hq;
   const bool has_cand = p.cand_pages != nullptr;
