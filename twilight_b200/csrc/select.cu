@@ -63,8 +63,6 @@ quest_page_scores_kernel(const ScoreParams p) {
   // Query heads of the group: in registers for small groups; for 4 or more heads the registers
   // would cost too much occupancy, so q (as fp32) sits in shared memory and each head's 16 values
   // are fetched per page with four 128-bit loads (the 8 lanes of a page read 8 distinct pieces).
-  // (Splitting q into positive and negative parts to use two FMAs per channel was measured
-  // slower: it doubles the shared-memory reads.)
   constexpr bool kQInSmem = G > 2;
   __shared__ __align__(16) float sm_qf[kQInSmem ? G : 1][kD];
   float qf[kQInSmem ? 1 : G][16];
@@ -107,71 +105,142 @@ quest_page_scores_kernel(const ScoreParams p) {
   __syncthreads();
   pdl_wait();     // page_scores may still be read by an earlier launch
 
-  constexpr int kU = 1;  // page quads in flight per warp (2 was measured slower)
-  for (int l0 = warp * 4; l0 < n_here; l0 += (kSelThreads / 32) * 4 * kU) {
-    uint4 mn[kU][2], mx[kU][2];
-    bool ok[kU], live[kU];
+  if constexpr (kQInSmem) {
+    // A warp takes four pages per step (8 lanes per page), 32 pages apart from its next step.
+    // With a group in shared memory the shared-memory reads of q bound the kernel (four 16-byte
+    // reads per head and step: 65 % of the shared-memory pipe at G = 8), so two steps are loaded
+    // together and every q vector that is fetched is used for both.
+    constexpr int kStep = (kSelThreads / 32) * 4;
+    constexpr int kPair = 2;
+    for (int l0 = warp * 4; l0 < n_here; l0 += kPair * kStep) {
+      uint4 mn[kPair][2], mx[kPair][2];
+      bool ok[kPair], live[kPair];
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const int l = l0 + u * (kSelThreads / 32) * 4 + pg_in_step;
-      live[u] = l < n_here;
-      const int phys = live[u] ? sm_phys[l] : -1;
-      ok[u] = phys >= 0;
-      if (ok[u]) {
-        const T* slab = reinterpret_cast<const T*>(p.kmeta) + ((size_t)phys * p.Hkv + kvh) * 2 * kD;
+      for (int u = 0; u < kPair; ++u) {
+        const int l = l0 + u * kStep + pg_in_step;
+        live[u] = l < n_here;
+        const int phys = live[u] ? sm_phys[l] : -1;
+        ok[u] = phys >= 0;
+        if (ok[u]) {
+          const T* slab = reinterpret_cast<const T*>(p.kmeta) + ((size_t)phys * p.Hkv + kvh) * 2 * kD;
 #pragma unroll
-        for (int part = 0; part < 2; ++part) {
-          mn[u][part] = ldg_stream_u4(reinterpret_cast<const uint4*>(slab) + sub + 8 * part);
-          mx[u][part] = ldg_stream_u4(reinterpret_cast<const uint4*>(slab + kD) + sub + 8 * part);
+          for (int part = 0; part < 2; ++part) {
+            mn[u][part] = ldg_stream_u4(reinterpret_cast<const uint4*>(slab) + sub + 8 * part);
+            mx[u][part] = ldg_stream_u4(reinterpret_cast<const uint4*>(slab + kD) + sub + 8 * part);
+          }
         }
       }
-    }
+      // per channel {centre, half-width} of the page's range: max(q*hi, q*lo) =
+      // q*(hi+lo)/2 + |q|*(hi-lo)/2 for hi >= lo, i.e. two FMAs per head instead of two products,
+      // a max and an add
+      float va[kPair][16], vb[kPair][16];
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const int lp = first + l0 + u * (kSelThreads / 32) * 4 + pg_in_step;
-      float acc[G];
-#pragma unroll
-      for (int g = 0; g < G; ++g) acc[g] = 0.f;
-      if (ok[u]) {
-        float lo16[16], hi16[16];
+      for (int u = 0; u < kPair; ++u) {
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
           const uint32_t un[4] = {mn[u][part].x, mn[u][part].y, mn[u][part].z, mn[u][part].w};
           const uint32_t ux[4] = {mx[u][part].x, mx[u][part].y, mx[u][part].z, mx[u][part].w};
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const float2 lo = Elem<T>::to_f2(un[k]), hi = Elem<T>::to_f2(ux[k]);
-            lo16[8 * part + 2 * k] = lo.x; lo16[8 * part + 2 * k + 1] = lo.y;
-            hi16[8 * part + 2 * k] = hi.x; hi16[8 * part + 2 * k + 1] = hi.y;
+            const float2 lo = ok[u] ? Elem<T>::to_f2(un[k]) : make_float2(0.f, 0.f);
+            const float2 hi = ok[u] ? Elem<T>::to_f2(ux[k]) : make_float2(0.f, 0.f);
+            va[u][8 * part + 2 * k] = 0.5f * (hi.x + lo.x); va[u][8 * part + 2 * k + 1] = 0.5f * (hi.y + lo.y);
+            vb[u][8 * part + 2 * k] = 0.5f * (hi.x - lo.x); vb[u][8 * part + 2 * k + 1] = 0.5f * (hi.y - lo.y);
+          }
+        }
+      }
+      float acc[kPair][G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float qv[16];
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          const float4 a = *reinterpret_cast<const float4*>(&sm_qf[g][64 * part + 8 * sub]);
+          const float4 c = *reinterpret_cast<const float4*>(&sm_qf[g][64 * part + 8 * sub + 4]);
+          qv[8 * part + 0] = a.x; qv[8 * part + 1] = a.y; qv[8 * part + 2] = a.z; qv[8 * part + 3] = a.w;
+          qv[8 * part + 4] = c.x; qv[8 * part + 5] = c.y; qv[8 * part + 6] = c.z; qv[8 * part + 7] = c.w;
+        }
+#pragma unroll
+        for (int u = 0; u < kPair; ++u) {
+          float t = 0.f;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            t = fmaf(qv[i], va[u][i], t);
+            t = fmaf(fabsf(qv[i]), vb[u][i], t);
+          }
+          acc[u][g] = t;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kPair; ++u) {
+        const int lp = first + l0 + u * kStep + pg_in_step;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float t = acc[u][g];
+          t += __shfl_xor_sync(0xffffffffu, t, 1);
+          t += __shfl_xor_sync(0xffffffffu, t, 2);
+          t += __shfl_xor_sync(0xffffffffu, t, 4);
+          if (live[u] && (g & 7) == sub)
+            p.page_scores[(size_t)(b * p.Hq + h0 + g) * p.max_pages + lp] = ok[u] ? t : -INFINITY;
+        }
+      }
+    }
+  } else {
+    constexpr int kU = 1;  // page quads in flight per warp (2 was measured slower)
+    for (int l0 = warp * 4; l0 < n_here; l0 += (kSelThreads / 32) * 4 * kU) {
+      uint4 mn[kU][2], mx[kU][2];
+      bool ok[kU], live[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int l = l0 + u * (kSelThreads / 32) * 4 + pg_in_step;
+        live[u] = l < n_here;
+        const int phys = live[u] ? sm_phys[l] : -1;
+        ok[u] = phys >= 0;
+        if (ok[u]) {
+          const T* slab = reinterpret_cast<const T*>(p.kmeta) + ((size_t)phys * p.Hkv + kvh) * 2 * kD;
+#pragma unroll
+          for (int part = 0; part < 2; ++part) {
+            mn[u][part] = ldg_stream_u4(reinterpret_cast<const uint4*>(slab) + sub + 8 * part);
+            mx[u][part] = ldg_stream_u4(reinterpret_cast<const uint4*>(slab + kD) + sub + 8 * part);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int lp = first + l0 + u * (kSelThreads / 32) * 4 + pg_in_step;
+        float acc[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) acc[g] = 0.f;
+        if (ok[u]) {
+          float lo16[16], hi16[16];
+#pragma unroll
+          for (int part = 0; part < 2; ++part) {
+            const uint32_t un[4] = {mn[u][part].x, mn[u][part].y, mn[u][part].z, mn[u][part].w};
+            const uint32_t ux[4] = {mx[u][part].x, mx[u][part].y, mx[u][part].z, mx[u][part].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float2 lo = Elem<T>::to_f2(un[k]), hi = Elem<T>::to_f2(ux[k]);
+              lo16[8 * part + 2 * k] = lo.x; lo16[8 * part + 2 * k + 1] = lo.y;
+              hi16[8 * part + 2 * k] = hi.x; hi16[8 * part + 2 * k + 1] = hi.y;
+            }
+          }
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            float qv[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) qv[i] = qf[g][i];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[g] += fmaxf(qv[i] * hi16[i], qv[i] * lo16[i]);
           }
         }
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-          float qv[16];
-          if (kQInSmem) {
-#pragma unroll
-            for (int part = 0; part < 2; ++part) {
-              const float4 a = *reinterpret_cast<const float4*>(&sm_qf[g][64 * part + 8 * sub]);
-              const float4 c = *reinterpret_cast<const float4*>(&sm_qf[g][64 * part + 8 * sub + 4]);
-              qv[8 * part + 0] = a.x; qv[8 * part + 1] = a.y; qv[8 * part + 2] = a.z; qv[8 * part + 3] = a.w;
-              qv[8 * part + 4] = c.x; qv[8 * part + 5] = c.y; qv[8 * part + 6] = c.z; qv[8 * part + 7] = c.w;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) qv[i] = qf[g][i];
-          }
-          // same order of additions in both forms
-#pragma unroll
-          for (int i = 0; i < 16; ++i) acc[g] += fmaxf(qv[i] * hi16[i], qv[i] * lo16[i]);
+          acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 1);
+          acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 2);
+          acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 4);
+          if (live[u] && (g & 7) == sub)
+            p.page_scores[(size_t)(b * p.Hq + h0 + g) * p.max_pages + lp] = ok[u] ? acc[g] : -INFINITY;
         }
-      }
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 1);
-        acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 2);
-        acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 4);
-        if (live[u] && (g & 7) == sub)
-          p.page_scores[(size_t)(b * p.Hq + h0 + g) * p.max_pages + lp] = ok[u] ? acc[g] : -INFINITY;
       }
     }
   }
