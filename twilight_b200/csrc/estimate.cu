@@ -13,6 +13,8 @@
 // so the inner loop touches only codes.
 #include <cstdlib>
 
+#include <cstddef>
+
 #include "common.cuh"
 
 namespace twl {
@@ -129,7 +131,7 @@ __device__ __forceinline__ uint32_t dp4a_u8_u8(uint32_t a, uint32_t b, uint32_t 
 }
 
 template <>
-struct QRegs<VAR_DP4A> {
+struct __align__(16) QRegs<VAR_DP4A> {
   // q_d ~= (256*qh_d + ql_d) * inv with |256*qh+ql| < 2^13, qh a signed byte, ql an unsigned
   // byte.  Even channels sit in the low nibbles, odd channels in the high nibbles; the odd ones
   // are used unshifted (16*code), which the final >>4 undoes exactly.
@@ -186,6 +188,9 @@ struct QRegs<VAR_DP4A> {
     return (__int_as_float(0x4B400000 + idot(w)) - 12582912.f) * inv;
   }
 };
+static_assert(sizeof(QRegs<VAR_DP4A>) == 80 && offsetof(QRegs<VAR_DP4A>, inv) == 64 &&
+                  offsetof(QRegs<VAR_DP4A>, qsum) == 68,
+              "the group kernel reads this structure from shared memory as four uint4 and one float2");
 
 template <typename T>
 __device__ __forceinline__ void load_q_group(const T* q, float* qf) {
@@ -795,20 +800,26 @@ estimate_int4_warp_group_kernel(const EstParams p) {
       }
 #pragma unroll
       for (int hh = 0; hh < G; ++hh) {
-        const QRegs<VARIANT>& qs = sm_q[hh][g];  // same address in every lane: broadcast reads
+        // same address in every lane: broadcast reads, as four 16-byte loads and one 8-byte load
+        // (word-wise reads made the shared-memory pipe the limit: 72 % busy at G = 4)
+        const uint4* qp = reinterpret_cast<const uint4*>(&sm_q[hh][g]);
+        const uint4 qhe = qp[0], qho = qp[1], qle = qp[2], qlo = qp[3];
+        const float2 inv_sum = *reinterpret_cast<const float2*>(qp + 4);  // {inv, qsum}
+        const uint32_t ahe[4] = {qhe.x, qhe.y, qhe.z, qhe.w}, aho[4] = {qho.x, qho.y, qho.z, qho.w};
+        const uint32_t ale[4] = {qle.x, qle.y, qle.z, qle.w}, alo[4] = {qlo.x, qlo.y, qlo.z, qlo.w};
         int he = 0, ho = 0;
         uint32_t le = 0, lo = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          he = dp4a_u8_s8(even[j], qs.qh_even[j], he);
-          ho = dp4a_u8_s8(odd16[j], qs.qh_odd[j], ho);
-          le = dp4a_u8_u8(even[j], qs.ql_even[j], le);
-          lo = dp4a_u8_u8(odd16[j], qs.ql_odd[j], lo);
+          he = dp4a_u8_s8(even[j], ahe[j], he);
+          ho = dp4a_u8_s8(odd16[j], aho[j], ho);
+          le = dp4a_u8_u8(even[j], ale[j], le);
+          lo = dp4a_u8_u8(odd16[j], alo[j], lo);
         }
         const int tot = (he + (ho >> 4)) * 256 + (int)(le + (lo >> 4));
-        const float dot = (__int_as_float(0x4B400000 + tot) - 12582912.f) * qs.inv;
+        const float dot = (__int_as_float(0x4B400000 + tot) - 12582912.f) * inv_sum.x;
         acc[hh] = fmaf(szf.x, dot, acc[hh]);
-        acc[hh] = fmaf(szf.y, qs.qsum, acc[hh]);
+        acc[hh] = fmaf(szf.y, inv_sum.y, acc[hh]);
       }
     }
     __syncwarp();      // all lanes are done reading the slot that the next issue overwrites
