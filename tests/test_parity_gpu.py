@@ -233,6 +233,45 @@ def test_gemv_entry_with_the_reference_call_signature():
                                        cache.kv_indptr, cache.kv_last_page_len)
 
 
+def test_corrupt_page_table_is_flagged_not_followed():
+    """A page-table entry outside the cache must never be dereferenced: the selector scores the
+    page -inf, the estimator leaves its slots alone, both raise FLAG_BAD_INDEX, and every other
+    page comes out as without the corruption."""
+    lens = [700, 300]
+    hq, hkv = 4, 2
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, dtype=torch.bfloat16, device=DEV, seed=41)
+    good_scores = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
+                                    max_pages=cache.max_pages).clone()
+    _, _, good_ps = ops.quest_select(q, cache.kmeta, cache.kv_indptr, cache.kv_indices, 64,
+                                     max_pages=cache.max_pages)
+    good_ps = good_ps.clone()
+    bad = cache.kv_indices.clone()
+    victim = 5                                       # page 5 of sequence 0
+    bad[victim] = cache.k_pages.shape[0] + 123
+    for entry in (bad, torch.where(torch.arange(bad.numel(), device=DEV) == victim, -7, cache.kv_indices).int()):
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        scores = torch.full_like(good_scores, 777.0)
+        ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, entry, cache.kv_last_page_len,
+                          max_pages=cache.max_pages, scores=scores, status=status)
+        assert int(status.item()) & ops.FLAG_BAD_INDEX
+        lo, hi = victim * PAGE, (victim + 1) * PAGE
+        assert (scores[0, :, lo:hi] == 777.0).all()                       # untouched
+        keep = torch.ones(scores.shape[-1], dtype=torch.bool, device=DEV)
+        keep[lo:hi] = False
+        n1 = ((lens[1] + PAGE - 1) // PAGE) * PAGE     # slots past a sequence's pages are not written
+        assert torch.equal(scores[0][:, keep].nan_to_num(neginf=-1e30), good_scores[0][:, keep].nan_to_num(neginf=-1e30))
+        assert torch.equal(scores[1][:, :n1].nan_to_num(neginf=-1e30), good_scores[1][:, :n1].nan_to_num(neginf=-1e30))
+        assert (scores[1][:, n1:] == 777.0).all()
+        status.zero_()
+        _, _, ps = ops.quest_select(q, cache.kmeta, cache.kv_indptr, entry, 64, max_pages=cache.max_pages,
+                                    status=status)
+        assert int(status.item()) & ops.FLAG_BAD_INDEX
+        assert torch.isinf(ps[0, :, victim]).all() and (ps[0, :, victim] < 0).all()
+        n0 = (lens[0] + PAGE - 1) // PAGE
+        others = [i for i in range(n0) if i != victim]
+        assert torch.equal(ps[0][:, others], good_ps[0][:, others])
+
+
 # ---- pruner ------------------------------------------------------------------------------------------
 def _prune_parity(q, cache, hq, top_p, cand_pages=None, cand_npages=None):
     scores = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices,
