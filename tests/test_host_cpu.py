@@ -124,3 +124,23 @@ def test_operators_fail_loudly_without_cuda_tensors():
     from twilight_b200.kernel import top_p_fp32_return_mask
     with pytest.raises(_lib.TwilightError, match="CUDA tensor"):
         top_p_fp32_return_mask(torch.rand(1, 1, 1, 8), 0.9)
+
+
+def test_growing_cache_page_table_follows_the_length():
+    """Host side of the growing cache: every sequence owns consecutive pages from the start, the
+    CSR table lists the pages in use, and its tensors are only rebuilt when a page is added."""
+    from twilight_b200.cache import GrowingPagedCache, PAGE
+    c = GrowingPagedCache(batch=3, num_kv_heads=2, max_len=100, dtype=torch.float16, device="cpu")
+    assert c.pages_per_seq == 7 and c.k_pages.shape == (21, 2, PAGE, 128) and c.k4_pages.shape == (21, 2, 1280)
+    c._set_length(16)
+    v16 = c.view
+    assert v16.kv_indptr.tolist() == [0, 1, 2, 3] and v16.kv_indices.tolist() == [0, 7, 14]
+    assert v16.kv_last_page_len.tolist() == [16, 16, 16] and v16.seq_lens == [16, 16, 16]
+    c._set_length(17)
+    assert c.view.kv_indptr.tolist() == [0, 2, 4, 6] and c.view.kv_indices.tolist() == [0, 1, 7, 8, 14, 15]
+    assert c.view.kv_last_page_len.tolist() == [1, 1, 1] and c.view.capacity_pages == 7 and c.view.max_pages == 2
+    idx17 = c.view.kv_indices
+    c._set_length(18)
+    assert c.view.kv_indices is idx17 and c.view.kv_last_page_len.tolist() == [2, 2, 2]   # same page count: reused
+    with pytest.raises(ValueError):
+        c._set_length(101)
