@@ -205,7 +205,6 @@ def main():
 
     from twilight_b200 import _lib
     from twilight_b200.gen import make_decode_inputs
-    from twilight_b200.kernel import ops
     from twilight_b200.step import (DecodeWorkspace, SparseConfig, select_prune_attend_step,
                                     step_algorithmic_bytes)
     _lib.load()  # fail loudly if the CUDA library is missing

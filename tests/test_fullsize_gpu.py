@@ -6,7 +6,7 @@ import torch
 
 from oracle import twilight_oracle as O
 from tests import util as U
-from twilight_b200.cache import PAGE, PagedKVCache, pack_k4, quest_max_k
+from twilight_b200.cache import PAGE, PagedKVCache, quest_max_k
 from twilight_b200.gen import make_decode_inputs, ragged_lengths
 from twilight_b200.kernel import ops
 from twilight_b200.step import DecodeWorkspace, SparseConfig, select_prune_attend_step

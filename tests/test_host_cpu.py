@@ -5,7 +5,6 @@ import ctypes
 import re
 from pathlib import Path
 
-import numpy as np
 import pytest
 import torch
 

@@ -2,8 +2,6 @@
 same seeded inputs.  Integer results (codes, page lists, index lists, budgets, masks) must be
 bit-exact, except kept-token sets, where tokens whose probability lies within 1e-4 of the
 threshold are exempt; attention outputs must agree within 2e-2 max-abs / 1e-3 mean-abs."""
-import math
-
 import numpy as np
 import pytest
 import torch

@@ -1,7 +1,6 @@
 """The attention entry point that brings its own scratch memory (for hosts that cannot allocate
 device memory after start-up) must give what the ordinary entry point gives.  Collected last on
 purpose: a run that stops at the first failure has then already run everything else."""
-import numpy as np
 import pytest
 import torch
 

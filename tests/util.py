@@ -5,7 +5,7 @@ import numpy as np
 import torch
 
 from oracle import twilight_oracle as O
-from twilight_b200.cache import PAGE, quest_max_k
+from twilight_b200.cache import PAGE
 
 SM_SCALE = 1.0 / math.sqrt(128)
 

@@ -17,7 +17,7 @@ Everything is generated directly in the paged layout on the target device.
 from __future__ import annotations
 
 import math
-from typing import List, Optional, Sequence, Tuple, Union
+from typing import List, Sequence, Tuple, Union
 
 import torch
 

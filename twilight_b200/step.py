@@ -6,7 +6,6 @@ paged cache.  ``SparseConfig`` takes the reference's config dictionary
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass, field
 from typing import Dict, Optional
 
