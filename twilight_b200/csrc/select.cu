@@ -11,7 +11,7 @@
 namespace twl {
 
 constexpr int kSelThreads = 256;
-constexpr int kSelPagesPerBlock = 128;  // 64 KiB of metadata per block
+constexpr int kSelPagesPerBlock = 256;  // 128 KiB of metadata per block (64 / 128 / 512 pages: 103 / 95 / 96 us against 91 us on config 1)
 
 struct ScoreParams {
   const void* q;
@@ -91,16 +91,16 @@ quest_page_scores_kernel(const ScoreParams p) {
   // has no dependent index loads
   __shared__ int sm_phys[kSelPagesPerBlock];
   const int n_here = min(kSelPagesPerBlock, n_pages - first);
-  if (threadIdx.x < kSelPagesPerBlock) {
+  for (int i = threadIdx.x; i < kSelPagesPerBlock; i += kSelThreads) {
     int phys = -1;
-    if ((int)threadIdx.x < n_here) {
-      phys = p.indices[page_base + first + threadIdx.x];
+    if (i < n_here) {
+      phys = p.indices[page_base + first + i];
       if (phys < 0 || phys >= p.num_pages_total) {
         phys = -1;
         raise_flag(p.status, TWL_FLAG_BAD_INDEX);
       }
     }
-    sm_phys[threadIdx.x] = phys;
+    sm_phys[i] = phys;
   }
   __syncthreads();
   pdl_wait();     // page_scores may still be read by an earlier launch
