@@ -529,12 +529,12 @@ constexpr int kRingDepth = 5;
 constexpr int kWarpStageBytes = 2 * kSlab;   // two pages
 constexpr int kWarpPagesPerBlock = 128;
 
-template <typename T, int VARIANT, int NW, int DEPTH>
+template <typename T, int VARIANT, int NW, int DEPTH, int PPB>
 __global__ void __launch_bounds__(NW * 32, (220 * 1024) / (NW * DEPTH * kWarpStageBytes + 2048))
 estimate_int4_warp_kernel(const EstParams p) {
   extern __shared__ __align__(128) uint8_t sm_ring[];  // NW * DEPTH * kWarpStageBytes
-  __shared__ int sm_phys[kWarpPagesPerBlock];
-  __shared__ int sm_ntok[kWarpPagesPerBlock];
+  __shared__ int sm_phys[PPB];
+  __shared__ int sm_ntok[PPB];
   __shared__ QRegs<VARIANT> sm_q[4];
 
   const int row = blockIdx.y;
@@ -557,9 +557,9 @@ estimate_int4_warp_kernel(const EstParams p) {
     n_pages = p.stride / kPage;
     if (threadIdx.x == 0 && blockIdx.x == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
   }
-  const int first = blockIdx.x * kWarpPagesPerBlock;
+  const int first = blockIdx.x * PPB;
   if (first >= n_pages) return;
-  const int n_here = min(kWarpPagesPerBlock, n_pages - first);
+  const int n_here = min(PPB, n_pages - first);
 
   const int tid = threadIdx.x;
   // four threads fetch q now and convert it later, after the first copies are on their way
@@ -568,7 +568,7 @@ estimate_int4_warp_kernel(const EstParams p) {
   if (q_thread)
     load_q_group<T>(reinterpret_cast<const T*>(p.q) + ((size_t)(b * p.Hq + h)) * kD +
                         (tid - ((NW * 32) - 4)) * kGroup, qf);
-  if (tid < kWarpPagesPerBlock) {
+  if (tid < PPB) {
     int phys = -1, ntok = 0;
     if (tid < n_here) {
       const int seq_page = has_cand ? p.cand_pages[(size_t)(b * p.Hq + h) * p.max_k + first + tid] : first + tid;
@@ -850,10 +850,11 @@ static int launch_one(const EstParams& p, int rows, int max_row_pages, bool ldg,
   } else if (G == 1 && !p.force_ring) {
     // four warps per block, four blocks per SM: the same 16 warps and bytes in flight as two
     // blocks of eight warps, with the blocks' set-up phases spread out more (1 % faster)
-    constexpr int kWarps = 4;
+    // 64 pages per block (32 / 64 / 128: 69.9 / 64.7 / 65.5 us on config 1)
+    constexpr int kWarps = 4, kPages = 64;
     constexpr int kBytes = kWarps * kRingDepth * kWarpStageBytes;
-    dim3 grid((max_row_pages + kWarpPagesPerBlock - 1) / kWarpPagesPerBlock, rows);
-    auto kern = estimate_int4_warp_kernel<T, VARIANT, kWarps, kRingDepth>;
+    dim3 grid((max_row_pages + kPages - 1) / kPages, rows);
+    auto kern = estimate_int4_warp_kernel<T, VARIANT, kWarps, kRingDepth, kPages>;
     TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
     TWL_CUDA_TRY(launch_chain(kern, grid, dim3(kWarps * 32), kBytes, st, p));
   } else {
