@@ -40,8 +40,10 @@ __device__ void topk_row(const float* src, int n, int k, int32_t* out, uint32_t*
 // Eight lanes share a page: lane `sub` reads 16-byte pieces sub and sub+8 of the 256-byte min
 // row and of the max row (channels 8*sub..8*sub+7 and 64+8*sub..), so a warp step covers four
 // pages = 2 KiB contiguous per page pair of rows.  G query heads share the loaded metadata.
+// A single head per row is all loads: five blocks per SM (48 registers) beat four (56) and six (42)
+// by 1-2 %.
 template <typename T, int G>
-__global__ void __launch_bounds__(kSelThreads)
+__global__ void __launch_bounds__(kSelThreads, G == 1 ? 5 : 1)
 quest_page_scores_kernel(const ScoreParams p) {
   // blocks that run side by side take the same pages of different KV heads: their 512-byte slabs
   // are neighbours inside one 512*H_kv-byte page record, which keeps DRAM rows open
