@@ -848,10 +848,10 @@ static int launch_one(const EstParams& p, int rows, int max_row_pages, bool ldg,
     dim3 grid((max_row_pages + kWarpPagesPerBlock - 1) / kWarpPagesPerBlock, rows);
     TWL_CUDA_TRY(launch_chain(kern, grid, dim3(kEstThreads), kBytes, st, p));
   } else if (G == 1 && !p.force_ring) {
-    // four warps per block, four blocks per SM: the same 16 warps and bytes in flight as two
-    // blocks of eight warps, with the blocks' set-up phases spread out more (1 % faster)
-    // 64 pages per block (32 / 64 / 128: 69.9 / 64.7 / 65.5 us on config 1)
-    constexpr int kWarps = 4, kPages = 64;
+    // Small blocks: 16 warps and the same bytes in flight per SM whatever the block size, but the
+    // blocks' set-up phases spread out more.  Per step of config 1: 8 warps x 128 pages 5.45 ms,
+    // 4 x 64 5.38, 2 x 32 5.32, 1 x 16 5.34 (16 pages = 8 ring stages per warp in every case).
+    constexpr int kWarps = 2, kPages = 32;
     constexpr int kBytes = kWarps * kRingDepth * kWarpStageBytes;
     dim3 grid((max_row_pages + kPages - 1) / kPages, rows);
     auto kern = estimate_int4_warp_kernel<T, VARIANT, kWarps, kRingDepth, kPages>;
