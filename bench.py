@@ -379,7 +379,7 @@ def main():
     # DRAM traffic per (sequence, KV head) row from the ncu capture summarised in
     # profiles/kernels_config1_small_case_ncu_full.md (256 rows; traffic is proportional to rows);
     # only valid for the configuration that capture was taken on
-    ncu_bytes_per_row = {"quest_page_scores": 274.31e6 / 256, "estimate_int4": 177.27e6 / 256}
+    ncu_bytes_per_row = {"quest_page_scores": 274.49e6 / 256, "estimate_int4": 175.33e6 / 256}
     traffic = None
     if (args.ctx, args.token_budget, args.heads, args.kv_heads) == (32768, 8192, 32, 32) and dominant in ncu_bytes_per_row:
         traffic = ncu_bytes_per_row[dominant] * args.batch * args.kv_heads
