@@ -90,7 +90,8 @@ TWL_API int twl_top_p_return_mask_f16(const void* probs, int dtype, uint8_t* mas
 
 /* ---- selector: Quest page scores + top-k pages ---------------------------------------
  * Replaces quest_selector of twilight/pyimpl/quest.py:17-122 using stored page metadata:
- * score(page) = sum_d max(q_d*kmax_d, q_d*kmin_d) in fp32 (quest.py:37-84), then the
+ * score(page) = sum_d max(q_d*kmax_d, q_d*kmin_d) in fp32 (quest.py:37-84; for groups of 4 or 8
+ * query heads per KV head evaluated as [min|max] . [min(q,0);max(q,0)] on tensor cores), then the
  * max(1,budget/16)+(budget%16!=0) best pages per query head (quest.py:93-99), ties to the
  * lower page number.  page_scores: caller scratch [B][H_q][max_pages] fp32 (kept as an
  * output for inspection).  cand_pages rows are ascending. */
@@ -126,8 +127,10 @@ TWL_API int twl_quest_select(const void* q, int dtype, const void* kmeta, const 
  * variant: arithmetic 0 = library default (3), 1 = fp32 FMA, 2 = packed-half FMA (about 1e-2
  * off in the logit), 3 = integer dot product; add 16 for the kernel that uses direct 128-bit
  * global loads, add 128 for the block-wide bulk-copy (TMA) ring even when a row has a single
- * query head (by default such rows use warp-private 16-byte async copies).  The non-default
- * variants exist for measurement. */
+ * query head (by default such rows use warp-private 16-byte async copies), add 32 for the
+ * integer-dot kernel on query-head groups (by default groups of 2, 4 or 8 heads that share a KV
+ * head's pages are scored with 16-bit tensor-core tiles: codes and q are exact in the model dtype,
+ * accumulation is fp32).  The non-default variants exist for measurement. */
 TWL_API int twl_estimate_int4(const void* q, int dtype, const uint8_t* k4_pages,
                       const int32_t* kv_indptr, const int32_t* kv_indices,
                       const int32_t* kv_last_page_len, const int32_t* cand_pages,
@@ -210,10 +213,14 @@ TWL_API int twl_sparse_decode_attn_weighted(const void* q, int dtype, const void
 /* ---- kernel #3 without a caller workspace -------------------------------------------------
  * No counterpart in the reference.  Same computation and arguments as twl_sparse_decode_attn,
  * minus workspace/workspace_bytes: the split-KV scratch is a fixed array inside the library
- * image (about 8.4 MB per GPU that loads the library, kept until the process exits), so this
- * call performs no device allocation of any kind.  It exists for hosts that cannot allocate
- * after start-up: a serving process whose memory pool already owns all free device memory, or
- * a plugin that may only be called where cudaMalloc is forbidden.
+ * image (about 8.4 MB per GPU that loads the library, kept until the process exits), so the
+ * call itself never asks for device memory.  The array's memory is taken by the CUDA runtime when
+ * the library's attention code is loaded onto a device, which (with CUDA's lazy module loading)
+ * happens at the first attention call on that device, this one included: make one call per device
+ * during start-up, before a memory pool claims what is left, or run with CUDA_MODULE_LOADING=EAGER.
+ * It exists for hosts that cannot allocate after start-up: a serving process whose memory pool
+ * already owns all free device memory, or a plugin that may only be called where cudaMalloc is
+ * forbidden.
  * Limit: batch*num_q_heads <= TWL_STATIC_ATTN_MAX_ROWS, else TWL_ERR_TOO_LARGE.
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  * that device current); make that first call outside any stream capture.
@@ -227,6 +234,63 @@ TWL_API int twl_sparse_decode_attn_static(const void* q, int dtype, const void* 
                                           int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
                                           int32_t num_pages_total, float sm_scale, void* out,
                                           int32_t chunk, int32_t* status, void* stream);
+
+/* ---- the whole step behind one call -------------------------------------------------------
+ * Replaces the decode branch of attention_forward, twilight/pyimpl/attention.py:188-306, with the
+ * selector / estimator / pruner choices of its config dictionary (attention.py:360-376):
+ * Quest page scores and top-k pages (token_budget > 0; <= 0 means selector "none"), the INT4
+ * estimate, the pruner (TWL_PRUNER_TOP_P with pruner_value = p or the per-row top_p_arr,
+ * TWL_PRUNER_THRESHOLD with pruner_value = the threshold, TWL_PRUNER_NONE) and the sparse
+ * attention, as three launches (five with Quest) on `stream`.
+ * flags: TWL_STEP_ESTIMATED_WEIGHTS = attend with the estimated weights (attention.py:295-296);
+ *        TWL_STEP_ROUND_TO_DTYPE = round the Quest page scores and the estimated logits to the model
+ *        dtype where the reference's matmuls return that dtype (quest.py:76-84; attention.py:252-254,
+ *        logits rounded before and after the division by sqrt(D)); two small extra launches, meant for
+ *        comparisons with the reference's dtype path, not for speed.
+ * All intermediates live in one caller-owned workspace of twl_step_workspace_bytes(...) bytes,
+ * 256-byte aligned, ZEROED ONCE by the caller after allocation (the attention kernel's arrival
+ * counters must start at zero; every call leaves them zero).  twl_step_workspace_layout gives the
+ * byte offset of every part, so that a host can read the budgets (int32 [B][H_q]), the kept tokens
+ * (int32 [B][H_q][stride], ascending, first budget entries valid), the candidate pages and the
+ * scores after the call.  max_pages = the largest page count of a sequence (sizes the rows).
+ * estimator_variant as for twl_estimate_int4 (0 = default); attn_chunk as for
+ * twl_sparse_decode_attn (<= 0 selects 256). */
+typedef enum { TWL_PRUNER_TOP_P = 0, TWL_PRUNER_THRESHOLD = 1, TWL_PRUNER_NONE = 2 } twl_pruner;
+typedef enum { TWL_STEP_ESTIMATED_WEIGHTS = 1, TWL_STEP_ROUND_TO_DTYPE = 2 } twl_step_flag;
+typedef struct {
+  uint64_t attn, attn_bytes;     /* split-KV scratch of the attention kernel (first in the buffer) */
+  uint64_t page_scores;          /* float [B][H_q][max_pages]          (Quest only) */
+  uint64_t cand_pages;           /* int32 [B][H_q][max_k]              (Quest only) */
+  uint64_t cand_npages;          /* int32 [B][H_q]                     (Quest only) */
+  uint64_t scores;               /* float [B][H_q][stride] estimated logits */
+  uint64_t indices;              /* int32 [B][H_q][stride] kept tokens */
+  uint64_t budget;               /* int32 [B][H_q] */
+  uint64_t threshold;            /* float [B][H_q][2] {cut, value of token 0} */
+  uint64_t weights;              /* float [B][H_q][stride] (TWL_STEP_ESTIMATED_WEIGHTS only) */
+  uint64_t total;                /* bytes of the whole workspace */
+  int32_t max_k;                 /* candidate pages per row (0 without Quest) */
+  int32_t stride;                /* slots per row of scores / indices / weights */
+  int32_t kernels;               /* launches one call makes */
+  int32_t reserved;
+} twl_step_layout;
+TWL_API int twl_step_workspace_layout(int32_t batch, int32_t num_q_heads, int32_t max_pages,
+                                      int32_t token_budget, int32_t attn_chunk, int32_t flags,
+                                      twl_step_layout* out);
+TWL_API size_t twl_step_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t max_pages,
+                                        int32_t token_budget, int32_t attn_chunk, int32_t flags);
+TWL_API int twl_select_prune_attend_step(
+    const void* q, int dtype, const void* k_pages, const void* v_pages, const uint8_t* k4_pages,
+    const void* kmeta, const int32_t* kv_indptr, const int32_t* kv_indices,
+    const int32_t* kv_last_page_len, int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+    int32_t num_pages_total, int32_t max_pages, int32_t token_budget, int32_t pruner,
+    float pruner_value, const float* top_p_arr, float sm_scale, int32_t flags,
+    int32_t estimator_variant, int32_t attn_chunk, void* out, void* workspace,
+    size_t workspace_bytes, int32_t* status, void* stream);
+
+/* scores[i] <- round(round(scores[i]) * post_scale), both roundings to `dtype` (fp16 or bf16), in
+ * place on n fp32 values; the step above uses it for TWL_STEP_ROUND_TO_DTYPE.  Stands in for the
+ * model-dtype results of the reference's matmuls (quest.py:76-84, attention.py:252-254). */
+TWL_API int twl_round_scores(float* scores, int64_t n, int dtype, float post_scale, void* stream);
 
 /* ---- cache-append side ------------------------------------------------------------------
  * twl_quantize_k_pages: min/max asymmetric 4-bit quantiser of quantize.py:4-13 applied per

@@ -45,7 +45,20 @@ SIGNATURES = {
     "twl_append_kv": (C.c_int, [ptr, ptr, C.c_int, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i32, i32, i32,
                                 ptr, ptr]),
     "twl_indices_to_mask": (C.c_int, [ptr, i32, ptr, i32, ptr, i32, ptr]),
+    "twl_step_workspace_layout": (C.c_int, [i32, i32, i32, i32, i32, i32, ptr]),
+    "twl_step_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),
+    "twl_select_prune_attend_step": (C.c_int, [ptr, C.c_int, ptr, ptr, ptr, ptr, ptr, ptr, ptr, i32, i32, i32,
+                                               i32, i32, i32, i32, f32, ptr, f32, i32, i32, i32, ptr, ptr, sz,
+                                               ptr, ptr]),
+    "twl_round_scores": (C.c_int, [ptr, i64, C.c_int, f32, ptr]),
 }
+
+
+class StepLayout(C.Structure):
+    """``twl_step_layout`` of include/twilight_b200.h: byte offsets of the parts of the step workspace."""
+    _fields_ = [(n, C.c_uint64) for n in ("attn", "attn_bytes", "page_scores", "cand_pages", "cand_npages",
+                                          "scores", "indices", "budget", "threshold", "weights", "total")] + \
+               [(n, C.c_int32) for n in ("max_k", "stride", "kernels", "reserved")]
 
 _lib = None
 

@@ -16,7 +16,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIBDIR = PKG / "lib"
 LIB = LIBDIR / "libtwilight_b200.so"
-SOURCES = ["capi.cu", "estimate.cu", "topp.cu", "attend.cu", "select.cu", "kvappend.cu"]
+SOURCES = ["capi.cu", "estimate.cu", "topp.cu", "attend.cu", "select.cu", "kvappend.cu", "step.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

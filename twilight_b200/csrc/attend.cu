@@ -473,7 +473,7 @@ static int launch_attn(const AttParams& p, int dtype, size_t rows, int32_t index
     int per_sm = 0;                                                                                \
     TWL_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kAttThreads, smem)); \
     if (per_sm < 1) return TWL_ERR_TOO_LARGE;                                                      \
-    const unsigned grid = (unsigned)std::min<size_t>(max_items, (size_t)kNumSMs * per_sm);        \
+    const unsigned grid = (unsigned)std::min<size_t>(max_items, (size_t)num_sms() * per_sm);        \
     if (chain) {                                                                                   \
       TWL_CUDA_TRY(launch_chain(kern, dim3(grid), dim3(kAttThreads), smem, st, p));                \
     } else {                                                                                       \

@@ -13,9 +13,22 @@ bool pdl_enabled() {
   }();
   return on;
 }
+int num_sms() {
+  // One slot per device ordinal; a value is written once and is the same from any thread.
+  constexpr int kMaxDev = 64;
+  static int cache[kMaxDev] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return 148;
+  int n = __atomic_load_n(&cache[dev], __ATOMIC_RELAXED);
+  if (n <= 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    __atomic_store_n(&cache[dev], n, __ATOMIC_RELAXED);
+  }
+  return n;
+}
 }  // namespace twl
 
-extern "C" int twl_version(void) { return 100; }
+extern "C" int twl_version(void) { return 200; }
 
 extern "C" const char* twl_status_string(int status) {
   switch (status) {

@@ -15,7 +15,9 @@ constexpr int kD = TWL_HEAD_DIM;            // head dimension
 constexpr int kGroup = TWL_QUANT_GROUP;     // channels per quantisation group
 constexpr int kSlab = TWL_K4_SLAB_BYTES;    // bytes of one INT4 (page, kv-head) slab
 constexpr int kSlabCodes = kPage * kD / 2;  // 1024 code bytes, then 256 bytes of scale/min
-constexpr int kNumSMs = 148;
+
+// Streaming multiprocessors of the current device (queried once per device, then cached).
+int num_sms();
 
 // Records the last CUDA launch error for twl_last_cuda_error().
 void set_last_cuda_error(cudaError_t e);
@@ -228,5 +230,34 @@ __device__ __forceinline__ uint32_t ldg_stream_u32(const void* p) {
   asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(r) : "l"(p));
   return r;
 }
+
+
+// ---- warp-level tensor-core tile: D(16x8, fp32) += A(16x16, row) * B(16x8, col), 16-bit inputs ----
+// Lane l = 4*g + t holds A rows g and g+8 (a0/a2: row g, k-slots {2t,2t+1} / {2t+8,2t+9}; a1/a3 the
+// same slots of row g+8), B column g (b0: k-slots {2t,2t+1}, b1: {2t+8,2t+9}) and D elements
+// (g, 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1).  Which channel sits in which k-slot is free as long
+// as A and B agree, which is what lets both operands be taken from memory in 16-byte pieces.
+template <typename T>
+struct MmaTile;
+template <>
+struct MmaTile<__half> {
+  static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
+template <>
+struct MmaTile<__nv_bfloat16> {
+  static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
 
 }  // namespace twl

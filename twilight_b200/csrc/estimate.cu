@@ -36,7 +36,7 @@ struct EstParams {
   const int32_t* cand_npages;
   float* scores;
   int32_t* status;
-  int max_k, B, Hq, Hkv, num_pages_total, stride, pages_per_block, force_ring;
+  int max_k, B, Hq, Hkv, num_pages_total, stride, pages_per_block, force_ring, simt_group;
   float sm_scale;
 };
 
@@ -458,12 +458,12 @@ estimate_int4_tma_kernel(const EstParams p) {
         }
         issued = st + 1;
       }
-      if (!ok) {
-        raise_flag(p.status, TWL_FLAG_WAIT_LIMIT);
-        // drain: every stage issued so far completes its transaction count sooner or later
-        for (int st = max(0, issued - kStages); st < issued; ++st)
-          mbar_wait(&sm_full[st % kStages], (st / kStages) & 1);
-      }
+      if (!ok) raise_flag(p.status, TWL_FLAG_WAIT_LIMIT);
+      // Drain on every path: the copies of the last stages may still be writing into this block's
+      // shared memory, and a consumer whose own bounded wait ran out has returned without them.
+      // The block must not end before they have landed (bounded waits again).
+      for (int st = max(0, issued - kStages); st < issued; ++st)
+        mbar_wait(&sm_full[st % kStages], (st / kStages) & 1);
     }
     return;
   }
@@ -549,9 +549,9 @@ estimate_int4_warp_kernel(const EstParams p) {
     kvh = row % p.Hkv;
     h = kvh;
   }
+  pdl_wait();  // candidate lists (and maybe q, the page table) come from the kernel before; nothing is read earlier
   const int page_base = p.indptr[b];
   const int n_seq_pages = p.indptr[b + 1] - page_base;
-  pdl_wait();  // candidate lists come from the kernel before; scores may still be read by an older one
   int n_pages = has_cand ? min(p.cand_npages[b * p.Hq + h], p.max_k) : n_seq_pages;
   if (n_pages > p.stride / kPage) {
     n_pages = p.stride / kPage;
@@ -663,7 +663,8 @@ estimate_int4_warp_kernel(const EstParams p) {
     issue(i + DEPTH - 1, fill_slot);
     use_slot = (use_slot + 1 == DEPTH) ? 0 : use_slot + 1;
     fill_slot = (fill_slot + 1 == DEPTH) ? 0 : fill_slot + 1;
-    if (present) out_row[(pg0 + pgl) * kPage + tl] = (tl < ntok) ? acc * p.sm_scale : -INFINITY;
+    // a page whose table entry was out of range scores -inf in all sixteen slots (ntok is 0 there)
+    if (pg0 + pgl < n_here) out_row[(pg0 + pgl) * kPage + tl] = (present && tl < ntok) ? acc * p.sm_scale : -INFINITY;
   }
   cp_async_wait<0>();
 }
@@ -684,9 +685,9 @@ estimate_int4_warp_group_kernel(const EstParams p) {
   constexpr bool has_cand = false;
   const int b = row / p.Hkv, kvh = row % p.Hkv;
   const int h = kvh * G;  // first query head of the group
+  pdl_wait();  // candidate lists (and maybe q, the page table) come from the kernel before; nothing is read earlier
   const int page_base = p.indptr[b];
   const int n_seq_pages = p.indptr[b + 1] - page_base;
-  pdl_wait();  // candidate lists come from the kernel before; scores may still be read by an older one
   int n_pages = has_cand ? min(p.cand_npages[b * p.Hq + h], p.max_k) : n_seq_pages;
   if (n_pages > p.stride / kPage) {
     n_pages = p.stride / kPage;
@@ -826,10 +827,234 @@ estimate_int4_warp_group_kernel(const EstParams p) {
     issue(i + kRingDepth - 1, fill_slot);
     use_slot = (use_slot + 1 == kRingDepth) ? 0 : use_slot + 1;
     fill_slot = (fill_slot + 1 == kRingDepth) ? 0 : fill_slot + 1;
-    if (present) {
+    if (pg0 + pgl < n_here) {
 #pragma unroll
       for (int hh = 0; hh < G; ++hh)
-        out_row[(size_t)hh * p.stride + (pg0 + pgl) * kPage + tl] = (tl < ntok) ? acc[hh] * p.sm_scale : -INFINITY;
+        out_row[(size_t)hh * p.stride + (pg0 + pgl) * kPage + tl] =
+            (present && tl < ntok) ? acc[hh] * p.sm_scale : -INFINITY;
+    }
+  }
+  cp_async_wait<0>();
+}
+
+// ---- query-head groups on the tensor cores ---------------------------------------------------------
+// The same warp-private rings, but a staged page (16 tokens) is scored against the whole group with
+// m16n8k16 tiles: A = the page's codes of one 32-channel quantisation group, turned into 16-bit
+// floats in registers, B = the group's queries for those channels (exact: q already has the model
+// dtype), fp32 accumulators; then score += scale * acc + min * sum(q) per (token, group) as in the
+// other kernels.  The work per staged byte no longer grows with the number of query heads.
+//
+// Lane 4*g + t owns tokens g and g+8 of the page and word t of their 16-byte group chunk: eight
+// nibbles, channels 8t..8t+7 of the group.  Two codes at a time (bits 0-3 and 16-19 of the word,
+// after a shift by 0, 4, 8 or 12) are or-ed into the mantissas of a pair of 16-bit floats:
+//   bf16  0x4300 | c = 128 + c (exact); the 128 is not subtracted but folded into the minimum,
+//         scale*(acc - 128*sum q) + min*sum q = scale*acc + (min - 128*scale)*sum q;
+//   fp16  0x6400 | c = 1024 + c and 0x5400 | (c << 4) = 64 + c, brought back to c by one exact
+//         subtraction each.
+// The k-slots of a tile thus hold channels in the order the nibbles come out; B is built once per
+// block in the same order.  Reads of the ring are conflict-free: the eight tokens of a quarter
+// warp's request sit in eight different 16-byte bank groups (the chunk rotation of the copy).
+template <typename T>
+struct CodePairs;
+template <>
+struct CodePairs<__nv_bfloat16> {
+  static constexpr float kOffset = 128.f;
+  // r[j] = codes of channels (j, j+4) of the word's eight, each as 128 + c
+  static __device__ __forceinline__ void unpack(uint32_t w, uint32_t (&r)[4]) {
+    r[0] = (w & 0x000F000Fu) | 0x43004300u;
+    r[1] = ((w >> 4) & 0x000F000Fu) | 0x43004300u;
+    r[2] = ((w >> 8) & 0x000F000Fu) | 0x43004300u;
+    r[3] = ((w >> 12) & 0x000F000Fu) | 0x43004300u;
+  }
+};
+template <>
+struct CodePairs<__half> {
+  static constexpr float kOffset = 0.f;
+  static __device__ __forceinline__ void unpack(uint32_t w, uint32_t (&r)[4]) {
+    const __half2 b1024 = __half2half2(__ushort_as_half(0x6400));
+    const __half2 b64 = __half2half2(__ushort_as_half(0x5400));
+    const uint32_t w8 = w >> 8;
+    uint32_t u0 = (w & 0x000F000Fu) | 0x64006400u, u1 = (w & 0x00F000F0u) | 0x54005400u;
+    uint32_t u2 = (w8 & 0x000F000Fu) | 0x64006400u, u3 = (w8 & 0x00F000F0u) | 0x54005400u;
+    __half2 c0 = __hsub2(*reinterpret_cast<__half2*>(&u0), b1024);
+    __half2 c1 = __hsub2(*reinterpret_cast<__half2*>(&u1), b64);
+    __half2 c2 = __hsub2(*reinterpret_cast<__half2*>(&u2), b1024);
+    __half2 c3 = __hsub2(*reinterpret_cast<__half2*>(&u3), b64);
+    r[0] = *reinterpret_cast<uint32_t*>(&c0);
+    r[1] = *reinterpret_cast<uint32_t*>(&c1);
+    r[2] = *reinterpret_cast<uint32_t*>(&c2);
+    r[3] = *reinterpret_cast<uint32_t*>(&c3);
+  }
+};
+
+template <typename T, int G>
+__global__ void __launch_bounds__(kEstThreads)
+estimate_int4_mma_group_kernel(const EstParams p) {
+  static_assert(G >= 2 && G <= 8, "one n8 tile holds the group");
+  extern __shared__ __align__(128) uint8_t sm_ring[];  // kEstWarps * kRingDepth * kWarpStageBytes
+  __shared__ int sm_phys[kWarpPagesPerBlock];
+  __shared__ int sm_ntok[kWarpPagesPerBlock];
+
+  const int row = blockIdx.y;
+  const int b = row / p.Hkv, kvh = row % p.Hkv;
+  const int h = kvh * G;  // first query head of the group
+  pdl_wait();  // q and the page table may come from the kernel before; scores may still be read by an older one
+  const int page_base = p.indptr[b];
+  const int n_seq_pages = p.indptr[b + 1] - page_base;
+  int n_pages = n_seq_pages;
+  if (n_pages > p.stride / kPage) {
+    n_pages = p.stride / kPage;
+    if (threadIdx.x == 0 && blockIdx.x == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+  }
+  const int first = blockIdx.x * kWarpPagesPerBlock;
+  if (first >= n_pages) return;
+  const int n_here = min(kWarpPagesPerBlock, n_pages - first);
+
+  const int tid = threadIdx.x;
+  if (tid < kWarpPagesPerBlock) {
+    int phys = -1, ntok = 0;
+    if (tid < n_here) {
+      const int seq_page = first + tid;
+      phys = p.indices[page_base + seq_page];
+      if (phys < 0 || phys >= p.num_pages_total) phys = -1;
+      if (phys < 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+      ntok = (seq_page == n_seq_pages - 1) ? p.last_len[b] : kPage;
+    }
+    sm_phys[tid] = phys;
+    sm_ntok[tid] = phys < 0 ? 0 : ntok;
+  }
+  __syncthreads();
+
+  const int lane = tid & 31, warp = tid >> 5;
+  const int gq = lane >> 2, t = lane & 3;
+  uint8_t* const ring = sm_ring + (size_t)warp * kRingDepth * kWarpStageBytes;
+  const uint32_t ring_u32 = smem_u32(ring);
+  const int n_pairs = (n_here + 1) >> 1;
+  const int my_pairs = (n_pairs > warp) ? (n_pairs - warp + kEstWarps - 1) / kEstWarps : 0;
+
+  // Per-lane constants of the five 16-byte copies of a stage: chunk c = c5*32+lane of the pair,
+  // i.e. page c/80 and chunk r = c%80 of its slab (0..63 codes, 64..79 scale/min).
+  uint32_t src16[5], dst_off[5];
+  bool second[5];
+#pragma unroll
+  for (int c5 = 0; c5 < 5; ++c5) {
+    const int c = c5 * 32 + lane;
+    const int pgl = c >= 80 ? 1 : 0;
+    const int r = c - pgl * 80;
+    second[c5] = pgl != 0;
+    src16[c5] = r;
+    if (r < 64) {
+      const int tk = pgl * 16 + (r >> 2), g4 = r & 3;
+      dst_off[c5] = tk * 64 + (((g4 + (tk >> 1)) & 3) << 4);
+    } else {
+      dst_off[c5] = 2048 + (pgl * 16 + (r - 64)) * 16;
+    }
+  }
+  const uint4* const k4_head16 = reinterpret_cast<const uint4*>(p.k4 + (size_t)kvh * kSlab);
+  const uint32_t page_stride16 = (uint32_t)(p.Hkv * (kSlab / 16));
+
+  auto issue = [&](int i, int slot) {
+    if (i < my_pairs) {
+      const int pg0 = (warp + i * kEstWarps) * 2;
+      const uint32_t dst0 = ring_u32 + slot * kWarpStageBytes;
+      const int phys0 = sm_phys[pg0], phys1 = sm_phys[pg0 + 1];  // missing pages hold -1
+#pragma unroll
+      for (int c5 = 0; c5 < 5; ++c5) {
+        const int phys = second[c5] ? phys1 : phys0;
+        if (phys >= 0)
+          cp_async16(dst0 + dst_off[c5], k4_head16 + ((size_t)phys * page_stride16 + src16[c5]));
+      }
+    }
+    cp_async_commit();  // always commit so that group counting stays uniform
+  };
+
+#pragma unroll
+  for (int i = 0; i < kRingDepth - 1; ++i) issue(i, i);
+
+  // B fragments (head gq of the group, this lane's channels 8t..8t+7 of every quantisation group)
+  // and the channel sums of heads 2t and 2t+1, whose scores this lane ends up owning
+  uint32_t bq[4][4];
+  float qs0[4], qs1[4];
+  {
+    const T* qrow = reinterpret_cast<const T*>(p.q) + (size_t)(b * p.Hq + h + (gq < G ? gq : 0)) * kD;
+#pragma unroll
+    for (int grp = 0; grp < 4; ++grp) {
+      uint4 v = __ldg(reinterpret_cast<const uint4*>(qrow) + 4 * grp + t);
+      if (gq >= G) v = make_uint4(0u, 0u, 0u, 0u);
+      // elements e0..e7 = channels 8t..8t+7; the tiles want the pairs (e0,e4) (e1,e5) (e2,e6) (e3,e7)
+      bq[grp][0] = __byte_perm(v.x, v.z, 0x5410);
+      bq[grp][1] = __byte_perm(v.x, v.z, 0x7632);
+      bq[grp][2] = __byte_perm(v.y, v.w, 0x5410);
+      bq[grp][3] = __byte_perm(v.y, v.w, 0x7632);
+      const float2 f0 = Elem<T>::to_f2(v.x), f1 = Elem<T>::to_f2(v.y), f2 = Elem<T>::to_f2(v.z),
+                   f3 = Elem<T>::to_f2(v.w);
+      float sum = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);  // sum of q over the group's 32 channels, head gq
+      qs0[grp] = __shfl_sync(0xffffffffu, sum, (2 * t) * 4);
+      qs1[grp] = __shfl_sync(0xffffffffu, sum, (2 * t + 1) * 4);
+    }
+  }
+
+  float* const out_row = p.scores + (size_t)(b * p.Hq + h + 2 * t) * p.stride + (size_t)first * kPage;
+  constexpr float kOff = CodePairs<T>::kOffset;
+  int use_slot = 0, fill_slot = kRingDepth - 1;
+  for (int i = 0; i < my_pairs; ++i) {
+    cp_async_wait<kRingDepth - 2>();  // pair i has landed (this thread's copies)
+    __syncwarp();                     // ... and every other lane's
+    const int pg0 = (warp + i * kEstWarps) * 2;
+    const uint8_t* stage = ring + use_slot * kWarpStageBytes;
+    float res[2][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {  // one page = one m16 tile
+      const int ta = mt * 16 + gq, tb = ta + 8;
+      const uint4 sza = *reinterpret_cast<const uint4*>(stage + 2048 + ta * 16);
+      const uint4 szb = *reinterpret_cast<const uint4*>(stage + 2048 + tb * 16);
+      const uint32_t sa[4] = {sza.x, sza.y, sza.z, sza.w}, sb[4] = {szb.x, szb.y, szb.z, szb.w};
+      float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
+#pragma unroll
+      for (int grp = 0; grp < 4; ++grp) {
+        const uint32_t wa = *reinterpret_cast<const uint32_t*>(stage + ta * 64 + (((grp + (ta >> 1)) & 3) << 4) + t * 4);
+        const uint32_t wb = *reinterpret_cast<const uint32_t*>(stage + tb * 64 + (((grp + (tb >> 1)) & 3) << 4) + t * 4);
+        uint32_t ca[4], cb[4];
+        CodePairs<T>::unpack(wa, ca);
+        CodePairs<T>::unpack(wb, cb);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        MmaTile<T>::run(acc, ca[0], cb[0], ca[1], cb[1], bq[grp][0], bq[grp][1]);
+        MmaTile<T>::run(acc, ca[2], cb[2], ca[3], cb[3], bq[grp][2], bq[grp][3]);
+        float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&sa[grp]));  // {scale, min}
+        float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&sb[grp]));
+        if (kOff != 0.f) {
+          fa.y = fmaf(-kOff, fa.x, fa.y);
+          fb.y = fmaf(-kOff, fb.x, fb.y);
+        }
+        r0 = fmaf(fa.x, acc[0], fmaf(fa.y, qs0[grp], r0));
+        r1 = fmaf(fa.x, acc[1], fmaf(fa.y, qs1[grp], r1));
+        r2 = fmaf(fb.x, acc[2], fmaf(fb.y, qs0[grp], r2));
+        r3 = fmaf(fb.x, acc[3], fmaf(fb.y, qs1[grp], r3));
+      }
+      res[mt][0] = r0; res[mt][1] = r1; res[mt][2] = r2; res[mt][3] = r3;
+    }
+    __syncwarp();      // all lanes are done reading the slot that the next issue overwrites
+    issue(i + kRingDepth - 1, fill_slot);
+    use_slot = (use_slot + 1 == kRingDepth) ? 0 : use_slot + 1;
+    fill_slot = (fill_slot + 1 == kRingDepth) ? 0 : fill_slot + 1;
+    if (2 * t < G) {
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const int pg = pg0 + mt;
+        if (pg < n_here) {
+          const int ntok = sm_ntok[pg];  // 0 for a page whose table entry was out of range
+          float* o0 = out_row + pg * kPage;
+          float* o1 = o0 + p.stride;
+          o0[gq] = gq < ntok ? res[mt][0] * p.sm_scale : -INFINITY;
+          o0[gq + 8] = gq + 8 < ntok ? res[mt][2] * p.sm_scale : -INFINITY;
+          if (2 * t + 1 < G) {
+            o1[gq] = gq < ntok ? res[mt][1] * p.sm_scale : -INFINITY;
+            o1[gq + 8] = gq + 8 < ntok ? res[mt][3] * p.sm_scale : -INFINITY;
+          }
+        }
+      }
     }
   }
   cp_async_wait<0>();
@@ -841,6 +1066,12 @@ static int launch_one(const EstParams& p, int rows, int max_row_pages, bool ldg,
   if (ldg) {
     dim3 grid((max_row_pages + kPagesPerBlock - 1) / kPagesPerBlock, rows);
     estimate_int4_kernel<T, G, VARIANT><<<grid, kEstThreads, 0, st>>>(p);
+  } else if (G > 1 && VARIANT == VAR_DP4A && !p.force_ring && !p.simt_group) {
+    constexpr int kBytes = kEstWarps * kRingDepth * kWarpStageBytes;
+    auto kern = estimate_int4_mma_group_kernel<T, (G > 1 ? G : 2)>;
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+    dim3 grid((max_row_pages + kWarpPagesPerBlock - 1) / kWarpPagesPerBlock, rows);
+    TWL_CUDA_TRY(launch_chain(kern, grid, dim3(kEstThreads), kBytes, st, p));
   } else if (G > 1 && VARIANT == VAR_DP4A && !p.force_ring) {
     constexpr int kBytes = kEstWarps * kRingDepth * kWarpStageBytes;
     auto kern = estimate_int4_warp_group_kernel<T, G>;
@@ -887,6 +1118,7 @@ static int launch_dtype(const EstParams& p, bool has_cand, int max_row_pages, in
                         cudaStream_t st) {
   // +16: direct global loads; +128: the block-wide bulk-copy ring even for a single query head
   const_cast<EstParams&>(p).force_ring = (variant & 128) != 0;
+  const_cast<EstParams&>(p).simt_group = (variant & 32) != 0;  // +32: integer-dot kernel for query-head groups
   const bool ldg = (variant & 16) != 0;
   switch (variant & 15) {
     case VAR_F32: return launch_variant<T, VAR_F32>(p, has_cand, max_row_pages, ldg, st);

@@ -6,6 +6,8 @@
 //   score(page) = sum_d max(q_d*kmax_d, q_d*kmin_d)            (== |q| . max_t sign(q)*K_t)
 // is evaluated in fp32.  The page count kept is quest.py:93-98; ties at the last kept score
 // go to the lower page number (torch.topk, quest.py:99, leaves them unspecified).
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace twl {
@@ -49,11 +51,14 @@ quest_page_scores_kernel(const ScoreParams p) {
   // are neighbours inside one 512*H_kv-byte page record, which keeps DRAM rows open
   const int row = blockIdx.x;  // (b, kv head), kv head fastest
   const int b = row / p.Hkv, kvh = row % p.Hkv;
+  // This is the first kernel of a layer pass: q and the page table may have been written by the
+  // kernel launched just before it (a projection, a cache append), so nothing is read before the
+  // wait.  Every block waits, so that this grid never completes before the one before it.
+  pdl_wait();
   const int page_base = p.indptr[b];
   const int n_pages = min(p.indptr[b + 1] - page_base, p.max_pages);
   const int first = blockIdx.y * kSelPagesPerBlock;
   if (first >= n_pages) {
-    pdl_wait();  // every block waits, so that this grid never completes before the one before it
     if (p.counters != nullptr && n_pages <= 0 && blockIdx.y == 0 && threadIdx.x < G)
       p.cand_npages[b * p.Hq + kvh * G + threadIdx.x] = 0;
     return;
@@ -105,7 +110,6 @@ quest_page_scores_kernel(const ScoreParams p) {
     sm_phys[i] = phys;
   }
   __syncthreads();
-  pdl_wait();     // page_scores may still be read by an earlier launch
 
   if constexpr (kQInSmem) {
     // A warp takes four pages per step (8 lanes per page), 32 pages apart from its next step.
@@ -276,6 +280,101 @@ quest_page_scores_kernel(const ScoreParams p) {
   }
 }
 
+// ---- query-head groups of 4 or 8: the scores as a tensor-core contraction -----------------------
+// sum_d max(q_d*hi_d, q_d*lo_d) = sum_d (min(q_d,0)*lo_d + max(q_d,0)*hi_d) because hi >= lo, i.e.
+//   score[page][head] = sum_k A[page][k] * B[k][head],   k = 0..255,
+// where row `page` of A is the 512-byte metadata slab exactly as it lies in memory ([min | max],
+// model dtype) and B = [min(q,0) ; max(q,0)] is exact in the model dtype.  A warp takes 16 pages
+// per step: lane 4*g + t reads the 16-byte pieces t, t+4, .., t+28 of the slabs of pages g and g+8
+// straight into the A fragments of sixteen m16n8k16 tiles (two per piece) (the channel-to-slot assignment this
+// gives is applied to B as well), accumulates in fp32 and owns the scores of pages g, g+8 for
+// heads 2t, 2t+1.  With four heads the upper four columns of B are zero.
+template <typename T, int G>
+__global__ void __launch_bounds__(kSelThreads, 3)
+quest_page_scores_mma_kernel(const ScoreParams p) {
+  static_assert(G == 4 || G == 8, "one n8 tile holds the group");
+  const int row = blockIdx.x;  // (b, kv head), kv head fastest
+  const int b = row / p.Hkv, kvh = row % p.Hkv;
+  pdl_wait();  // q and the page table may come from the kernel launched just before
+  const int page_base = p.indptr[b];
+  const int n_pages = min(p.indptr[b + 1] - page_base, p.max_pages);
+  const int first = blockIdx.y * kSelPagesPerBlock;
+  if (first >= n_pages) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int h0 = kvh * G;
+
+  // B fragments of head g.  The slab is 32 pieces of 16 bytes (16 of minima, 16 of maxima); this
+  // lane holds pieces t, t+4, .., t+28 of it, so its B pieces are those of [min(q,0) | max(q,0)]
+  uint32_t bq[8][4];
+  {
+    const T* qrow = reinterpret_cast<const T*>(p.q) + (size_t)(b * p.Hq + h0 + (g < G ? g : 0)) * kD;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(qrow) + 4 * c + t);
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        // a 16-bit float is negative iff its sign bit is set; -0 and +0 both give a zero product
+        const uint32_t lo_neg = (u[k] & 0x00008000u) ? 0x0000ffffu : 0u;
+        const uint32_t hi_neg = (u[k] & 0x80000000u) ? 0xffff0000u : 0u;
+        const uint32_t neg = lo_neg | hi_neg;
+        bq[c][k] = (g < G) ? (u[k] & neg) : 0u;       // min(q,0): pairs with the page minima
+        bq[4 + c][k] = (g < G) ? (u[k] & ~neg) : 0u;  // max(q,0): pairs with the page maxima
+      }
+    }
+  }
+
+  __shared__ int sm_phys[kSelPagesPerBlock];
+  const int n_here = min(kSelPagesPerBlock, n_pages - first);
+  for (int i = threadIdx.x; i < kSelPagesPerBlock; i += kSelThreads) {
+    int phys = -1;
+    if (i < n_here) {
+      phys = p.indices[page_base + first + i];
+      if (phys < 0 || phys >= p.num_pages_total) {
+        phys = -1;
+        raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+      }
+    }
+    sm_phys[i] = phys;
+  }
+  __syncthreads();
+
+  const uint4* const meta16 = reinterpret_cast<const uint4*>(p.kmeta);
+  const size_t slab16 = 2 * kD * sizeof(T) / 16;  // 32 pieces per (page, kv-head) slab
+  for (int l0 = warp * 16; l0 < n_here; l0 += (kSelThreads / 32) * 16) {
+    const int la = l0 + g, lb = l0 + g + 8;
+    const int pa = la < n_here ? sm_phys[la] : -1, pb = lb < n_here ? sm_phys[lb] : -1;
+    // absent pages read the slab of physical page 0 (always mapped); their scores are not used
+    const uint4* sa = meta16 + ((size_t)max(pa, 0) * p.Hkv + kvh) * slab16 + t;
+    const uint4* sb = meta16 + ((size_t)max(pb, 0) * p.Hkv + kvh) * slab16 + t;
+    uint4 va[8], vb[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      va[c] = ldg_stream_u4(sa + 4 * c);
+      vb[c] = ldg_stream_u4(sb + 4 * c);
+    }
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      MmaTile<T>::run(acc, va[c].x, vb[c].x, va[c].y, vb[c].y, bq[c][0], bq[c][1]);
+      MmaTile<T>::run(acc, va[c].z, vb[c].z, va[c].w, vb[c].w, bq[c][2], bq[c][3]);
+    }
+    if (2 * t < G) {
+      float* const o0 = p.page_scores + (size_t)(b * p.Hq + h0 + 2 * t) * p.max_pages + first;
+      float* const o1 = o0 + p.max_pages;
+      if (la < n_here) {
+        o0[la] = pa >= 0 ? acc[0] : -INFINITY;
+        o1[la] = pa >= 0 ? acc[1] : -INFINITY;
+      }
+      if (lb < n_here) {
+        o0[lb] = pb >= 0 ? acc[2] : -INFINITY;
+        o1[lb] = pb >= 0 ? acc[3] : -INFINITY;
+      }
+    }
+  }
+}
+
 // ---- top-k pages of one (batch, query head) row ---------------------------------------------
 __device__ __forceinline__ uint32_t order_key(float f) {
   const uint32_t u = __float_as_uint(f);
@@ -388,11 +487,11 @@ quest_topk_pages_kernel(const TopkParams p) {
   __shared__ TopkScratch sc;
   pdl_release();  // the estimator's blocks may move in and set up while this small grid works
   const int row = blockIdx.x, b = row / p.Hq;
+  pdl_wait();  // the page scores come from the kernel launched just before; nothing is read earlier
   const int n = min(p.indptr[b + 1] - p.indptr[b], p.max_pages);
   int k = max(1, p.token_budget / kPage) + ((p.token_budget % kPage) != 0 ? 1 : 0);  // quest.py:93-95
   k = min(min(k, n), p.max_k);                                                       // quest.py:98
   int32_t* out = p.cand_pages + (size_t)row * p.max_k;
-  pdl_wait();  // the page scores come from the kernel launched just before
   if (threadIdx.x == 0) p.cand_npages[row] = k;
   if (k <= 0) return;
   if (k == n) {  // every page is kept
@@ -419,8 +518,28 @@ static int launch_scores(const ScoreParams& p, cudaStream_t st) {
   return TWL_OK;
 }
 
+template <typename T, int G>
+static int launch_scores_mma(const ScoreParams& p, cudaStream_t st) {
+  const int rows = p.B * p.Hkv;
+  const int chunks = (p.max_pages + kSelPagesPerBlock - 1) / kSelPagesPerBlock;
+  if (chunks > 65535) return TWL_ERR_TOO_LARGE;
+  TWL_CUDA_TRY(launch_chain(quest_page_scores_mma_kernel<T, G>, dim3(rows, chunks), dim3(kSelThreads), 0, st, p));
+  TWL_CHECK_LAUNCH();
+  return TWL_OK;
+}
+
 template <typename T>
 static int launch_scores_g(const ScoreParams& p, cudaStream_t st) {
+  // Groups of four and eight query heads go to the tensor-core kernel (the per-head FMA form is
+  // bound by shared-memory reads of q there); TWL_SCORES_SIMT=1 keeps the FMA form for comparison.
+  static const bool simt = [] {
+    const char* e = getenv("TWL_SCORES_SIMT");
+    return e && e[0] == '1';
+  }();
+  if (p.counters == nullptr && !simt) {
+    if (p.Hq / p.Hkv == 4) return launch_scores_mma<T, 4>(p, st);
+    if (p.Hq / p.Hkv == 8) return launch_scores_mma<T, 8>(p, st);
+  }
   switch (p.Hq / p.Hkv) {
     case 1: return launch_scores<T, 1>(p, st);
     case 2: return launch_scores<T, 2>(p, st);

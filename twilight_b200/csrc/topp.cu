@@ -395,8 +395,8 @@ topp_prune_kernel(const PruneParams p) {
   const int r = blockIdx.x;
   const int b = r / p.Hq;
   const bool has_cand = p.cand_pages != nullptr;
+  pdl_wait();  // scores and candidate lists come from the kernels launched before; nothing is read earlier
   const int n_seq_pages = p.indptr[b + 1] - p.indptr[b];
-  pdl_wait();  // scores and candidate lists come from the kernels launched before
   int n_pages = has_cand ? min(p.cand_npages[r], p.max_k) : n_seq_pages;
   n_pages = min(n_pages, p.stride / kPage);
   const int n = n_pages * kPage;  // candidate slots; slots past the sequence end hold -inf
@@ -691,8 +691,8 @@ static int run_prune(PruneParams& p, int batch, int num_q_heads, int score_strid
                                : score_stride;
   // one block per row.  More threads per row shorten a row's latency, but only pay while all rows
   // still run at the same time (3 blocks of 512 threads per SM, 6 of 256): a second wave costs more
-  const bool one_wave_512 = rows <= 3 * kNumSMs;
-  const bool one_wave_1024 = rows <= kNumSMs;
+  const bool one_wave_512 = rows <= 3 * num_sms();
+  const bool one_wave_1024 = rows <= num_sms();
   if (n_max <= 2048) return launch_prune<256>(p, rows, n_max, st);
   if (n_max <= 8192) return one_wave_512 ? launch_prune<512>(p, rows, n_max, st) : launch_prune<256>(p, rows, n_max, st);
   if (n_max <= 16384) return one_wave_1024 ? launch_prune<1024>(p, rows, n_max, st) : launch_prune<512>(p, rows, n_max, st);

@@ -38,6 +38,25 @@ def _stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+def _same_device(dev: torch.device, **tensors: Optional[torch.Tensor]) -> None:
+    """Every tensor that crosses the C ABI in one call must live on the device the kernels run on."""
+    for name, t in tensors.items():
+        if t is not None and t.device != dev:
+            raise _lib.TwilightError(f"{name} is on {t.device}, the call runs on {dev}")
+
+
+def _on(t: torch.Tensor, **others: Optional[torch.Tensor]):
+    """Context in which ``t``'s device is the current CUDA device, as the reference's operators do
+    with ``with probs.device`` (twilight/kernel/cuda/sampling.py:68).  The library launches on the
+    current device, so a tensor on cuda:1 while cuda:0 is current (Hugging Face ``device_map="auto"``,
+    benchmark/LongBench/pred.py:272-274) needs this guard; ``others`` are checked to be on that
+    device too."""
+    if not t.is_cuda:
+        raise _lib.TwilightError("the operators take CUDA tensors only (there is no CPU path)")
+    _same_device(t.device, **others)
+    return torch.cuda.device(t.device)
+
+
 def _cuda_contig(t: torch.Tensor, name: str) -> None:
     # same checks as CHECK_INPUT in csrc/src/pytorch_extension_utils.h:220-233
     if not t.is_cuda:
@@ -61,19 +80,18 @@ def _q3(q: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------------
 # reference-compatible mask operators
 # ---------------------------------------------------------------------------------------------
-def _top_p_return_mask(probs: torch.Tensor, top_p: Union[torch.Tensor, float], half: bool
+def _top_p_return_mask(probs: torch.Tensor, arr: Optional[torch.Tensor], val: float, half: bool
                        ) -> torch.Tensor:
     _cuda_contig(probs, "probs")
     if probs.dim() != 4:
         raise _lib.TwilightError("probs must be a 4D tensor")  # CHECK_DIM(4, probs)
     lib = _lib.load()
     b, h, _, d = probs.shape
-    arr, val = (top_p, 0.0) if isinstance(top_p, torch.Tensor) else (None, float(top_p))
     if arr is not None:
         arr = arr.to(device=probs.device, dtype=torch.float32).contiguous()
         if arr.numel() != b * h:
             raise _lib.TwilightError("top_p tensor must have batch*num_heads elements")
-    with torch.cuda.device(probs.device):
+    with _on(probs):
         mask = torch.zeros_like(probs, dtype=torch.bool)
         if half:
             st = lib.twl_top_p_return_mask_f16(probs.data_ptr(), _dtype_code(probs), mask.data_ptr(),
@@ -87,15 +105,52 @@ def _top_p_return_mask(probs: torch.Tensor, top_p: Union[torch.Tensor, float], h
     return mask
 
 
+# The reference registers its two mask operators as torch custom ops without mutated arguments
+# (``flashinfer::top_p_fp{16,32}_return_mask``, twilight/kernel/cuda/sampling.py:62-100), which is
+# what lets them sit inside traced or compiled graphs.  Same here, under this library's namespace:
+# ``torch.ops.twilight_b200.top_p_fp32_return_mask(probs, maybe_top_p_arr, top_p_val)``.
+@torch.library.custom_op("twilight_b200::top_p_fp32_return_mask", mutates_args=())
+def _op_top_p_fp32(probs: torch.Tensor, maybe_top_p_arr: Optional[torch.Tensor], top_p_val: float
+                   ) -> torch.Tensor:
+    return _top_p_return_mask(probs, maybe_top_p_arr, top_p_val, half=False)
+
+
+@torch.library.custom_op("twilight_b200::top_p_fp16_return_mask", mutates_args=())
+def _op_top_p_fp16(probs: torch.Tensor, maybe_top_p_arr: Optional[torch.Tensor], top_p_val: float
+                   ) -> torch.Tensor:
+    return _top_p_return_mask(probs, maybe_top_p_arr, top_p_val, half=True)
+
+
+@_op_top_p_fp32.register_fake
+@_op_top_p_fp16.register_fake
+def _fake_top_p_mask(probs, maybe_top_p_arr, top_p_val):
+    return torch.empty_like(probs, dtype=torch.bool)
+
+
+def _to_tensor_scalar_tuple(x):
+    # twilight/kernel/cuda/sampling.py:111-115
+    return (x, 0.0) if isinstance(x, torch.Tensor) else (None, float(x))
+
+
 def top_p_fp32_return_mask(probs: torch.Tensor, top_p: Union[torch.Tensor, float]) -> torch.Tensor:
     """probs ``[B,H,1,L]`` fp32 -> bool mask of the tokens the top-p search keeps
     (twilight/kernel/cuda/sampling.py:127-133, csrc/src/sampling.cu:45-63)."""
-    return _top_p_return_mask(probs, top_p, half=False)
+    return torch.ops.twilight_b200.top_p_fp32_return_mask(probs, *_to_tensor_scalar_tuple(top_p))
 
 
 def top_p_fp16_return_mask(probs: torch.Tensor, top_p: Union[torch.Tensor, float]) -> torch.Tensor:
     """fp16/bf16 form (twilight/kernel/cuda/sampling.py:118-124, csrc/src/sampling.cu:22-43)."""
-    return _top_p_return_mask(probs, top_p, half=True)
+    return torch.ops.twilight_b200.top_p_fp16_return_mask(probs, *_to_tensor_scalar_tuple(top_p))
+
+
+def _launch(name: str, on: torch.Tensor, *args, **same_device: Optional[torch.Tensor]) -> None:
+    """Calls entry point ``twl_<name>`` with ``on``'s device current (the library launches on the
+    current device); the keyword tensors are checked to live on that device.  Raises
+    :class:`TwilightError` on a non-zero status."""
+    lib = _lib.load()
+    with _on(on, **same_device):
+        st = getattr(lib, "twl_" + name)(*args)
+    _lib.check(st, name)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -108,7 +163,6 @@ def quest_select(q, kmeta, kv_indptr, kv_indices, token_budget: int, *, max_page
 
     Returns ``(cand_pages[B,H,max_k] int32 ascending, cand_npages[B,H] int32, page_scores)``.
     With ``counters`` (zeroed int32 ``[B*H_kv]``) scoring and selection run as one kernel."""
-    lib = _lib.load()
     q = _q3(q)
     b, hq, _ = q.shape
     n_total, hkv = kmeta.shape[0], kmeta.shape[1]
@@ -123,20 +177,17 @@ def quest_select(q, kmeta, kv_indptr, kv_indices, token_budget: int, *, max_page
         cand_npages = torch.empty(b, hq, dtype=torch.int32, device=dev)
     s = _stream(dev)
     if counters is not None:
-        _lib.check(lib.twl_quest_select(q.data_ptr(), _dtype_code(q), kmeta.data_ptr(), kv_indptr.data_ptr(),
-                                        kv_indices.data_ptr(), b, hq, hkv, n_total, token_budget,
-                                        page_scores.data_ptr(), max_pages, cand_pages.data_ptr(),
-                                        cand_npages.data_ptr(), cand_pages.shape[-1], counters.data_ptr(),
-                                        _p(status), s), "quest_select")
+        _launch("quest_select", q, q.data_ptr(), _dtype_code(q), kmeta.data_ptr(), kv_indptr.data_ptr(),
+                kv_indices.data_ptr(), b, hq, hkv, n_total, token_budget, page_scores.data_ptr(), max_pages,
+                cand_pages.data_ptr(), cand_npages.data_ptr(), cand_pages.shape[-1], counters.data_ptr(),
+                _p(status), s, kmeta=kmeta, page_scores=page_scores, cand_pages=cand_pages, status=status)
         return cand_pages, cand_npages, page_scores
-    _lib.check(lib.twl_quest_page_scores(q.data_ptr(), _dtype_code(q), kmeta.data_ptr(),
-                                         kv_indptr.data_ptr(), kv_indices.data_ptr(), b, hq, hkv,
-                                         n_total, page_scores.data_ptr(), max_pages, _p(status), s),
-               "quest_page_scores")
-    _lib.check(lib.twl_quest_topk_pages(page_scores.data_ptr(), max_pages, kv_indptr.data_ptr(), b,
-                                        hq, token_budget, cand_pages.data_ptr(),
-                                        cand_npages.data_ptr(), cand_pages.shape[-1], s),
-               "quest_topk_pages")
+    _launch("quest_page_scores", q, q.data_ptr(), _dtype_code(q), kmeta.data_ptr(), kv_indptr.data_ptr(),
+            kv_indices.data_ptr(), b, hq, hkv, n_total, page_scores.data_ptr(), max_pages, _p(status), s,
+            kmeta=kmeta, page_scores=page_scores, status=status)
+    _launch("quest_topk_pages", page_scores, page_scores.data_ptr(), max_pages, kv_indptr.data_ptr(), b, hq,
+            token_budget, cand_pages.data_ptr(), cand_npages.data_ptr(), cand_pages.shape[-1], s,
+            cand_pages=cand_pages, cand_npages=cand_npages)
     return cand_pages, cand_npages, page_scores
 
 
@@ -145,7 +196,6 @@ def quest_topk(page_scores, kv_indptr, token_budget: int, *, max_pages: int, can
     """The selection half of :func:`quest_select` on given fp32 scores ``[B,H,max_pages]``:
     ascending positions of the ``max(1, budget//16) + (budget%16 != 0)`` best entries of each row
     (twilight/pyimpl/quest.py:93-99), ties to the lower position."""
-    lib = _lib.load()
     _cuda_contig(page_scores, "page_scores")
     b, hq, stride = page_scores.shape
     assert stride == max_pages and page_scores.dtype == torch.float32
@@ -155,9 +205,9 @@ def quest_topk(page_scores, kv_indptr, token_budget: int, *, max_pages: int, can
         cand_pages = torch.empty(b, hq, max_k, dtype=torch.int32, device=dev)
     if cand_npages is None:
         cand_npages = torch.empty(b, hq, dtype=torch.int32, device=dev)
-    _lib.check(lib.twl_quest_topk_pages(page_scores.data_ptr(), max_pages, kv_indptr.data_ptr(), b, hq,
-                                        token_budget, cand_pages.data_ptr(), cand_npages.data_ptr(),
-                                        cand_pages.shape[-1], _stream(dev)), "quest_topk_pages")
+    _launch("quest_topk_pages", page_scores, page_scores.data_ptr(), max_pages, kv_indptr.data_ptr(), b, hq,
+            token_budget, cand_pages.data_ptr(), cand_npages.data_ptr(), cand_pages.shape[-1], _stream(dev),
+            cand_pages=cand_pages, cand_npages=cand_npages)
     return cand_pages, cand_npages, page_scores
 
 
@@ -167,7 +217,6 @@ def estimate_int4(q, k4_pages, kv_indptr, kv_indices, kv_last_page_len, *, max_p
     """INT4 K-cache estimator (twilight/pyimpl/attention.py:247-255): fp32 scores
     ``[B,H,stride]``; slot s of a row is token ``cand_pages[s//16]*16+s%16`` (or token s when
     no candidate list is given)."""
-    lib = _lib.load()
     q = _q3(q)
     b, hq, _ = q.shape
     n_total, hkv = k4_pages.shape[0], k4_pages.shape[1]
@@ -177,12 +226,10 @@ def estimate_int4(q, k4_pages, kv_indptr, kv_indices, kv_last_page_len, *, max_p
         scores = torch.empty(b, hq, stride, dtype=torch.float32, device=q.device)
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(HEAD_DIM)
-    _lib.check(lib.twl_estimate_int4(q.data_ptr(), _dtype_code(q), k4_pages.data_ptr(),
-                                     kv_indptr.data_ptr(), kv_indices.data_ptr(),
-                                     kv_last_page_len.data_ptr(), _p(cand_pages), _p(cand_npages),
-                                     max_k, b, hq, hkv, n_total, sm_scale, scores.data_ptr(),
-                                     scores.shape[-1], variant, _p(status), _stream(q.device)),
-               "estimate_int4")
+    _launch("estimate_int4", q, q.data_ptr(), _dtype_code(q), k4_pages.data_ptr(), kv_indptr.data_ptr(),
+            kv_indices.data_ptr(), kv_last_page_len.data_ptr(), _p(cand_pages), _p(cand_npages), max_k, b,
+            hq, hkv, n_total, sm_scale, scores.data_ptr(), scores.shape[-1], variant, _p(status),
+            _stream(q.device), k4_pages=k4_pages, scores=scores, cand_pages=cand_pages, status=status)
     return scores
 
 
@@ -192,7 +239,6 @@ def topp_prune(scores, kv_indptr, kv_last_page_len, top_p: Union[torch.Tensor, f
     """fp32 softmax + top-p search + compaction (twilight/pyimpl/top_p.py:10-15 and
     attention.py:280-285).  Returns ``(indices[B,H,stride] int32, budget[B,H] int32)``; the first
     ``budget`` entries of a row are the kept token positions in ascending order."""
-    lib = _lib.load()
     _cuda_contig(scores, "scores")
     b, hq, stride = scores.shape
     dev = scores.device
@@ -204,11 +250,10 @@ def topp_prune(scores, kv_indptr, kv_last_page_len, top_p: Union[torch.Tensor, f
     if arr is not None:
         arr = arr.to(device=dev, dtype=torch.float32).contiguous()
     max_k = 0 if cand_pages is None else cand_pages.shape[-1]
-    _lib.check(lib.twl_topp_prune(scores.data_ptr(), stride, kv_indptr.data_ptr(),
-                                  kv_last_page_len.data_ptr(), _p(cand_pages), _p(cand_npages),
-                                  max_k, b, hq, _p(arr), val, indices.data_ptr(),
-                                  indices.shape[-1], budget.data_ptr(), _p(threshold), _p(status),
-                                  _stream(dev)), "topp_prune")
+    _launch("topp_prune", scores, scores.data_ptr(), stride, kv_indptr.data_ptr(),
+            kv_last_page_len.data_ptr(), _p(cand_pages), _p(cand_npages), max_k, b, hq, _p(arr), val,
+            indices.data_ptr(), indices.shape[-1], budget.data_ptr(), _p(threshold), _p(status),
+            _stream(dev), indices=indices, budget=budget, cand_pages=cand_pages, status=status)
     return indices, budget
 
 
@@ -217,7 +262,6 @@ def threshold_prune(scores, kv_indptr, kv_last_page_len, threshold: float, *, ca
                     ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Element-wise threshold pruner (twilight/pyimpl/elementwise_threshold.py:9-18) in index-list
     form: keeps candidates whose score exceeds ``score(token 0) - threshold``."""
-    lib = _lib.load()
     _cuda_contig(scores, "scores")
     b, hq, stride = scores.shape
     dev = scores.device
@@ -226,11 +270,10 @@ def threshold_prune(scores, kv_indptr, kv_last_page_len, threshold: float, *, ca
     if budget is None:
         budget = torch.empty(b, hq, dtype=torch.int32, device=dev)
     max_k = 0 if cand_pages is None else cand_pages.shape[-1]
-    _lib.check(lib.twl_threshold_prune(scores.data_ptr(), stride, kv_indptr.data_ptr(),
-                                       kv_last_page_len.data_ptr(), _p(cand_pages), _p(cand_npages),
-                                       max_k, b, hq, float(threshold), indices.data_ptr(),
-                                       indices.shape[-1], budget.data_ptr(), _p(cut), _p(status),
-                                       _stream(dev)), "threshold_prune")
+    _launch("threshold_prune", scores, scores.data_ptr(), stride, kv_indptr.data_ptr(),
+            kv_last_page_len.data_ptr(), _p(cand_pages), _p(cand_npages), max_k, b, hq, float(threshold),
+            indices.data_ptr(), indices.shape[-1], budget.data_ptr(), _p(cut), _p(status), _stream(dev),
+            indices=indices, budget=budget, cand_pages=cand_pages, status=status)
     return indices, budget
 
 
@@ -241,7 +284,6 @@ def prune_with_weights(scores, kv_indptr, kv_last_page_len, value, *, mode: str 
     returns, for every kept token, its un-normalised softmax weight over the estimated logits
     (for attention with ``use_estimated_weights_in_attn``, twilight/pyimpl/attention.py:295-296).
     Returns ``(indices, budget, weights[B,H,stride] fp32)``."""
-    lib = _lib.load()
     _cuda_contig(scores, "scores")
     b, hq, stride = scores.shape
     dev = scores.device
@@ -255,12 +297,11 @@ def prune_with_weights(scores, kv_indptr, kv_last_page_len, value, *, mode: str 
     if arr is not None:
         arr = arr.to(device=dev, dtype=torch.float32).contiguous()
     max_k = 0 if cand_pages is None else cand_pages.shape[-1]
-    _lib.check(lib.twl_prune_with_weights({"top_p": 0, "threshold": 1}[mode], scores.data_ptr(), stride,
-                                          kv_indptr.data_ptr(), kv_last_page_len.data_ptr(),
-                                          _p(cand_pages), _p(cand_npages), max_k, b, hq, _p(arr), val,
-                                          indices.data_ptr(), indices.shape[-1], budget.data_ptr(),
-                                          _p(threshold), weights.data_ptr(), _p(status), _stream(dev)),
-               "prune_with_weights")
+    _launch("prune_with_weights", scores, {"top_p": 0, "threshold": 1}[mode], scores.data_ptr(), stride,
+            kv_indptr.data_ptr(), kv_last_page_len.data_ptr(), _p(cand_pages), _p(cand_npages), max_k, b,
+            hq, _p(arr), val, indices.data_ptr(), indices.shape[-1], budget.data_ptr(), _p(threshold),
+            weights.data_ptr(), _p(status), _stream(dev), indices=indices, budget=budget, weights=weights,
+            status=status)
     return indices, budget, weights
 
 
@@ -277,7 +318,6 @@ def sparse_decode_attn(q, k_pages, v_pages, kv_indptr, kv_indices, indices, budg
     ``workspace``: zero-initialised uint8 tensor of ``sparse_attn_workspace_bytes`` bytes.
     ``weights`` (from :func:`prune_with_weights`): attend with these weights instead of exact
     q.k logits (attention.py:295-296); K is then not read."""
-    lib = _lib.load()
     q = _q3(q)
     b, hq, _ = q.shape
     n_total, hkv = k_pages.shape[0], k_pages.shape[1]
@@ -290,19 +330,18 @@ def sparse_decode_attn(q, k_pages, v_pages, kv_indptr, kv_indices, indices, budg
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(HEAD_DIM)
     if weights is not None:
-        _lib.check(lib.twl_sparse_decode_attn_weighted(
-            q.data_ptr(), _dtype_code(q), k_pages.data_ptr(), v_pages.data_ptr(), kv_indptr.data_ptr(),
-            kv_indices.data_ptr(), indices.data_ptr(), stride, budget.data_ptr(), weights.data_ptr(), b, hq,
-            hkv, n_total, sm_scale, out.data_ptr(), workspace.data_ptr(), workspace.numel(), chunk,
-            _p(status), _stream(q.device)), "sparse_decode_attn_weighted")
+        _launch("sparse_decode_attn_weighted", q, q.data_ptr(), _dtype_code(q), k_pages.data_ptr(),
+                v_pages.data_ptr(), kv_indptr.data_ptr(), kv_indices.data_ptr(), indices.data_ptr(), stride,
+                budget.data_ptr(), weights.data_ptr(), b, hq, hkv, n_total, sm_scale, out.data_ptr(),
+                workspace.data_ptr(), workspace.numel(), chunk, _p(status), _stream(q.device),
+                k_pages=k_pages, v_pages=v_pages, out=out, workspace=workspace, indices=indices,
+                status=status)
         return out
-    _lib.check(lib.twl_sparse_decode_attn(q.data_ptr(), _dtype_code(q), k_pages.data_ptr(),
-                                          v_pages.data_ptr(), kv_indptr.data_ptr(),
-                                          kv_indices.data_ptr(), indices.data_ptr(), stride,
-                                          budget.data_ptr(), b, hq, hkv, n_total, sm_scale,
-                                          out.data_ptr(), workspace.data_ptr(), workspace.numel(),
-                                          chunk, _p(status), _stream(q.device)),
-               "sparse_decode_attn")
+    _launch("sparse_decode_attn", q, q.data_ptr(), _dtype_code(q), k_pages.data_ptr(), v_pages.data_ptr(),
+            kv_indptr.data_ptr(), kv_indices.data_ptr(), indices.data_ptr(), stride, budget.data_ptr(), b,
+            hq, hkv, n_total, sm_scale, out.data_ptr(), workspace.data_ptr(), workspace.numel(), chunk,
+            _p(status), _stream(q.device), k_pages=k_pages, v_pages=v_pages, out=out, workspace=workspace,
+            indices=indices, status=status)
     return out
 
 
@@ -318,18 +357,70 @@ def sparse_decode_attn_static(q, k_pages, v_pages, kv_indptr, kv_indices, indice
     allocated here or in the library.  At most ``STATIC_ATTN_MAX_ROWS`` (batch x query heads) rows.
     All calls on a device share one scratch array, so calls that could overlap on the GPU must
     not be issued; make the first call on a device outside any stream capture."""
-    lib = _lib.load()
     q = _q3(q)
     b, hq, _ = q.shape
     n_total, hkv = k_pages.shape[0], k_pages.shape[1]
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(HEAD_DIM)
-    _lib.check(lib.twl_sparse_decode_attn_static(q.data_ptr(), _dtype_code(q), k_pages.data_ptr(),
-                                                 v_pages.data_ptr(), kv_indptr.data_ptr(),
-                                                 kv_indices.data_ptr(), indices.data_ptr(),
-                                                 indices.shape[-1], budget.data_ptr(), b, hq, hkv,
-                                                 n_total, sm_scale, out.data_ptr(), chunk, _p(status),
-                                                 _stream(q.device)), "sparse_decode_attn_static")
+    _launch("sparse_decode_attn_static", q, q.data_ptr(), _dtype_code(q), k_pages.data_ptr(),
+            v_pages.data_ptr(), kv_indptr.data_ptr(), kv_indices.data_ptr(), indices.data_ptr(),
+            indices.shape[-1], budget.data_ptr(), b, hq, hkv, n_total, sm_scale, out.data_ptr(), chunk,
+            _p(status), _stream(q.device), k_pages=k_pages, v_pages=v_pages, out=out, indices=indices,
+            status=status)
+    return out
+
+
+def round_scores(scores: torch.Tensor, dtype: torch.dtype, post_scale: float = 1.0) -> torch.Tensor:
+    """In place: ``scores <- round(round(scores) * post_scale)``, rounding to ``dtype`` (fp16/bf16), on
+    an fp32 tensor.  Reproduces the model-dtype results of the reference's matmuls
+    (twilight/pyimpl/quest.py:76-84, attention.py:252-254) on this library's fp32 scores."""
+    _cuda_contig(scores, "scores")
+    if scores.dtype != torch.float32:
+        raise _lib.TwilightError("round_scores works on float32 scores")
+    code = _dtype_code(torch.empty(0, dtype=dtype))
+    _launch("round_scores", scores, scores.data_ptr(), scores.numel(), code, float(post_scale),
+            _stream(scores.device))
+    return scores
+
+
+PRUNER_CODES = {"top_p": 0, "threshold": 1, "none": 2}
+STEP_ESTIMATED_WEIGHTS, STEP_ROUND_TO_DTYPE = 1, 2
+
+
+def step_workspace_layout(batch: int, num_q_heads: int, max_pages: int, token_budget: int,
+                          attn_chunk: int = 256, flags: int = 0) -> "_lib.StepLayout":
+    """Byte offsets of the parts of the one-buffer workspace of :func:`select_prune_attend_step`
+    (``twl_step_workspace_layout``)."""
+    lay = _lib.StepLayout()
+    import ctypes
+    _lib.check(_lib.load().twl_step_workspace_layout(batch, num_q_heads, max_pages, token_budget, attn_chunk,
+                                                     flags, ctypes.addressof(lay)), "step_workspace_layout")
+    return lay
+
+
+def select_prune_attend_step(q, k_pages, v_pages, k4_pages, kmeta, kv_indptr, kv_indices, kv_last_page_len, *,
+                             max_pages: int, token_budget: int, pruner: str, pruner_value: float,
+                             out: torch.Tensor, workspace: torch.Tensor, top_p_arr=None,
+                             sm_scale: Optional[float] = None, flags: int = 0, variant: int = 0,
+                             attn_chunk: int = 256, status=None) -> torch.Tensor:
+    """The decode step of one layer as ONE C-ABI call (``twl_select_prune_attend_step``): Quest
+    selection when ``token_budget > 0``, INT4 estimate, pruner, sparse attention
+    (twilight/pyimpl/attention.py:188-306).  ``workspace``: uint8 tensor of
+    ``step_workspace_layout(...).total`` bytes, zeroed once after allocation."""
+    q = _q3(q)
+    b, hq, _ = q.shape
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(HEAD_DIM)
+    arr = None
+    if top_p_arr is not None:
+        arr = top_p_arr.to(device=q.device, dtype=torch.float32).contiguous()
+    _launch("select_prune_attend_step", q, q.data_ptr(), _dtype_code(q), k_pages.data_ptr(), v_pages.data_ptr(),
+            k4_pages.data_ptr(), _p(kmeta), kv_indptr.data_ptr(), kv_indices.data_ptr(),
+            kv_last_page_len.data_ptr(), b, hq, k_pages.shape[1], k_pages.shape[0], max_pages, token_budget,
+            PRUNER_CODES[pruner], float(pruner_value), _p(arr), sm_scale, flags, variant, attn_chunk,
+            out.data_ptr(), workspace.data_ptr(), workspace.numel(), _p(status), _stream(q.device),
+            k_pages=k_pages, v_pages=v_pages, k4_pages=k4_pages, kmeta=kmeta, out=out, workspace=workspace,
+            status=status, kv_indptr=kv_indptr, kv_indices=kv_indices)
     return out
 
 
@@ -339,14 +430,12 @@ def sparse_decode_attn_static(q, k_pages, v_pages, kv_indptr, kv_indices, indice
 def quantize_k_pages(k_pages: torch.Tensor, k4_pages: Optional[torch.Tensor] = None) -> torch.Tensor:
     """K pages ``[P,Hkv,16,128]`` -> INT4 slabs ``[P,Hkv,1280]`` uint8, group 32
     (twilight/pyimpl/quantize.py:4-13 per group, arithmetic in the cache dtype)."""
-    lib = _lib.load()
     _cuda_contig(k_pages, "k_pages")
     p, hkv = k_pages.shape[0], k_pages.shape[1]
     if k4_pages is None:
         k4_pages = torch.empty(p, hkv, K4_SLAB_BYTES, dtype=torch.uint8, device=k_pages.device)
-    _lib.check(lib.twl_quantize_k_pages(k_pages.data_ptr(), _dtype_code(k_pages),
-                                        k4_pages.data_ptr(), p * hkv, _stream(k_pages.device)),
-               "quantize_k_pages")
+    _launch("quantize_k_pages", k_pages, k_pages.data_ptr(), _dtype_code(k_pages), k4_pages.data_ptr(),
+            p * hkv, _stream(k_pages.device), k4_pages=k4_pages)
     return k4_pages
 
 
@@ -354,16 +443,14 @@ def build_page_meta(k_pages, kv_indptr, kv_indices, kv_last_page_len, *, max_pag
                     kmeta: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Channel-wise (min,max) of every page ``[P,Hkv,2,128]`` (stored form of the chunk maxima of
     twilight/pyimpl/quest.py:39-74)."""
-    lib = _lib.load()
     _cuda_contig(k_pages, "k_pages")
     p, hkv = k_pages.shape[0], k_pages.shape[1]
     b = kv_indptr.numel() - 1
     if kmeta is None:
         kmeta = torch.zeros(p, hkv, 2, HEAD_DIM, dtype=k_pages.dtype, device=k_pages.device)
-    _lib.check(lib.twl_build_page_meta(k_pages.data_ptr(), _dtype_code(k_pages), kmeta.data_ptr(),
-                                       kv_indptr.data_ptr(), kv_indices.data_ptr(),
-                                       kv_last_page_len.data_ptr(), b, hkv, p, max_pages,
-                                       _stream(k_pages.device)), "build_page_meta")
+    _launch("build_page_meta", k_pages, k_pages.data_ptr(), _dtype_code(k_pages), kmeta.data_ptr(),
+            kv_indptr.data_ptr(), kv_indices.data_ptr(), kv_last_page_len.data_ptr(), b, hkv, p, max_pages,
+            _stream(k_pages.device), kmeta=kmeta)
     return kmeta
 
 
@@ -371,25 +458,21 @@ def append_kv(new_k, new_v, k_pages, v_pages, k4_pages, kmeta, kv_indptr, kv_ind
               kv_last_page_len, status=None) -> None:
     """Writes one token per sequence (``new_k/new_v [B,Hkv,128]``) at the last position the page
     table describes, with its INT4 codes and the page metadata update."""
-    lib = _lib.load()
     _cuda_contig(new_k, "new_k")
     _cuda_contig(new_v, "new_v")
     b, hkv, _ = new_k.shape
-    _lib.check(lib.twl_append_kv(new_k.data_ptr(), new_v.data_ptr(), _dtype_code(new_k),
-                                 k_pages.data_ptr(), v_pages.data_ptr(), _p(k4_pages), _p(kmeta),
-                                 kv_indptr.data_ptr(), kv_indices.data_ptr(),
-                                 kv_last_page_len.data_ptr(), b, hkv, k_pages.shape[0], _p(status),
-                                 _stream(new_k.device)), "append_kv")
+    _launch("append_kv", new_k, new_k.data_ptr(), new_v.data_ptr(), _dtype_code(new_k), k_pages.data_ptr(),
+            v_pages.data_ptr(), _p(k4_pages), _p(kmeta), kv_indptr.data_ptr(), kv_indices.data_ptr(),
+            kv_last_page_len.data_ptr(), b, hkv, k_pages.shape[0], _p(status), _stream(new_k.device),
+            k_pages=k_pages, v_pages=v_pages, k4_pages=k4_pages, kmeta=kmeta, status=status)
 
 
 def indices_to_mask(indices, budget, seq_len: int) -> torch.Tensor:
     """Index lists -> the reference's mask layout ``bool[B,H,1,L]`` (attention.py:199-281)."""
-    lib = _lib.load()
     b, hq, stride = indices.shape
     mask = torch.zeros(b, hq, 1, seq_len, dtype=torch.bool, device=indices.device)
-    _lib.check(lib.twl_indices_to_mask(indices.data_ptr(), stride, budget.data_ptr(), b * hq,
-                                       mask.data_ptr(), seq_len, _stream(indices.device)),
-               "indices_to_mask")
+    _launch("indices_to_mask", indices, indices.data_ptr(), stride, budget.data_ptr(), b * hq,
+            mask.data_ptr(), seq_len, _stream(indices.device), budget=budget, mask=mask)
     return mask
 
 

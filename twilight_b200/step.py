@@ -28,6 +28,9 @@ class SparseConfig:
     threshold: float = 0.95
     use_estimated_weights_in_attn: bool = False
     skip_first_two_layers: bool = True
+    # not a reference key: round Quest page scores and estimated logits to the model dtype where the
+    # reference's matmuls return that dtype (quest.py:76-84, attention.py:252-254); for comparisons
+    round_to_dtype: bool = False
 
     @classmethod
     def from_dict(cls, cfg: Dict) -> "SparseConfig":
@@ -43,7 +46,8 @@ class SparseConfig:
         prn, prn_args = split("weight_pruner")
         out = cls(selector=sel, weight_estimator=est, weight_pruner=prn,
                   use_estimated_weights_in_attn=bool(cfg.get("use_estimated_weights_in_attn", False)),
-                  skip_first_two_layers=bool(cfg.get("skip_first_two_layers", True)))
+                  skip_first_two_layers=bool(cfg.get("skip_first_two_layers", True)),
+                  round_to_dtype=bool(cfg.get("round_to_dtype", False)))
         if sel == "quest":
             out.token_budget = int(sel_args.get("token_budget", -1))
             out.chunk_size = int(sel_args.get("chunk_size", PAGE))
@@ -67,7 +71,9 @@ class SparseConfig:
 
 @dataclass
 class DecodeWorkspace:
-    """Every intermediate of one decode step, allocated once (so a step can be graph-captured)."""
+    """Every intermediate of one decode step in ONE device buffer, allocated (and zeroed) once, so
+    that a step is a single C-ABI call and can be graph-captured.  The attributes are views of the
+    buffer at the offsets ``twl_step_workspace_layout`` reports."""
     batch: int
     num_q_heads: int
     max_pages: int
@@ -78,6 +84,7 @@ class DecodeWorkspace:
     page_scores: Optional[torch.Tensor] = None
     cand_pages: Optional[torch.Tensor] = None
     cand_npages: Optional[torch.Tensor] = None
+    buffer: torch.Tensor = field(init=False)
     scores: torch.Tensor = field(init=False)
     indices: torch.Tensor = field(init=False)
     budget: torch.Tensor = field(init=False)
@@ -88,25 +95,36 @@ class DecodeWorkspace:
     status: torch.Tensor = field(init=False)
 
     def __post_init__(self) -> None:
-        b, h, dev = self.batch, self.num_q_heads, self.device
-        if self.config.selector == "quest":
-            max_k = quest_max_k(self.config.token_budget, self.max_pages)
-            self.page_scores = torch.empty(b, h, self.max_pages, dtype=torch.float32, device=dev)
-            self.cand_pages = torch.empty(b, h, max_k, dtype=torch.int32, device=dev)
-            self.cand_npages = torch.empty(b, h, dtype=torch.int32, device=dev)
-            stride = max_k * PAGE
-        else:
-            stride = self.max_pages * PAGE
-        self.scores = torch.empty(b, h, stride, dtype=torch.float32, device=dev)
-        self.indices = torch.empty(b, h, stride, dtype=torch.int32, device=dev)
-        self.budget = torch.zeros(b, h, dtype=torch.int32, device=dev)
-        self.threshold = torch.zeros(b, h, 2, dtype=torch.float32, device=dev)
-        self.out = torch.empty(b, h, HEAD_DIM, dtype=self.dtype, device=dev)
-        self.attn_ws = torch.zeros(ops.sparse_attn_workspace_bytes(b, h, stride, self.attn_chunk),
-                                   dtype=torch.uint8, device=dev)
-        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
-        if self.config.use_estimated_weights_in_attn:
-            self.weights = torch.empty(b, h, stride, dtype=torch.float32, device=dev)
+        b, h, dev, cfg = self.batch, self.num_q_heads, self.device, self.config
+        self.flags = (ops.STEP_ESTIMATED_WEIGHTS if cfg.use_estimated_weights_in_attn else 0) | \
+                     (ops.STEP_ROUND_TO_DTYPE if cfg.round_to_dtype else 0)
+        self.token_budget = cfg.token_budget if cfg.selector == "quest" else 0
+        lay = ops.step_workspace_layout(b, h, self.max_pages, self.token_budget, self.attn_chunk, self.flags)
+        self.layout = lay
+        with torch.cuda.device(dev):
+            self.buffer = torch.zeros(int(lay.total), dtype=torch.uint8, device=dev)
+            self.out = torch.empty(b, h, HEAD_DIM, dtype=self.dtype, device=dev)
+            self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+        def view(off: int, dtype: torch.dtype, *shape: int) -> torch.Tensor:
+            n = 1
+            for x in shape:
+                n *= x
+            nbytes = n * torch.empty(0, dtype=dtype).element_size()
+            return self.buffer[off: off + nbytes].view(dtype).view(*shape)
+
+        stride = int(lay.stride)
+        if cfg.selector == "quest":
+            self.page_scores = view(lay.page_scores, torch.float32, b, h, self.max_pages)
+            self.cand_pages = view(lay.cand_pages, torch.int32, b, h, int(lay.max_k))
+            self.cand_npages = view(lay.cand_npages, torch.int32, b, h)
+        self.scores = view(lay.scores, torch.float32, b, h, stride)
+        self.indices = view(lay.indices, torch.int32, b, h, stride)
+        self.budget = view(lay.budget, torch.int32, b, h)
+        self.threshold = view(lay.threshold, torch.float32, b, h, 2)
+        self.attn_ws = self.buffer[lay.attn: lay.attn + lay.attn_bytes]
+        if cfg.use_estimated_weights_in_attn:
+            self.weights = view(lay.weights, torch.float32, b, h, stride)
 
     @classmethod
     def for_cache(cls, cache: PagedKVCache, num_q_heads: int, config: SparseConfig,
@@ -116,46 +134,22 @@ class DecodeWorkspace:
 
     @property
     def kernels_per_step(self) -> int:
-        return (2 if self.config.selector == "quest" else 0) + 3
+        return int(self.layout.kernels)
 
 
 def select_prune_attend_step(q: torch.Tensor, cache: PagedKVCache, ws: DecodeWorkspace,
                              variant: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One decode step of one attention layer.  q ``[B,H_q,128]`` (or ``[B,H_q,1,128]``);
     returns ``ws.out [B,H_q,128]`` (or ``out`` when given).  ``ws.budget`` holds the per-head pruned budgets and
-    ``ws.indices`` the kept tokens afterwards.  Launches 3 kernels (5 with the Quest selector)
-    on the current stream and nothing else."""
+    ``ws.indices`` the kept tokens afterwards.  One C-ABI call (``twl_select_prune_attend_step``), which
+    launches 3 kernels (5 with the Quest selector) on the current stream and nothing else."""
     cfg = ws.config
-    cand_pages = cand_npages = None
-    if cfg.selector == "quest":
-        cand_pages, cand_npages, _ = ops.quest_select(
-            q, cache.kmeta, cache.kv_indptr, cache.kv_indices, cfg.token_budget,
-            max_pages=ws.max_pages, page_scores=ws.page_scores, cand_pages=ws.cand_pages,
-            cand_npages=ws.cand_npages, status=ws.status)
-    ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
-                      max_pages=ws.max_pages, cand_pages=cand_pages, cand_npages=cand_npages,
-                      scores=ws.scores, variant=variant, status=ws.status)
-    # pruner "none" keeps every candidate with non-zero probability: a top-p above 1 does that
-    mode = "threshold" if cfg.weight_pruner == "threshold" else "top_p"
-    value = cfg.threshold if cfg.weight_pruner in ("top_p", "threshold") else 2.0
-    if cfg.use_estimated_weights_in_attn:  # attention.py:295-296
-        ops.prune_with_weights(ws.scores, cache.kv_indptr, cache.kv_last_page_len, value, mode=mode,
-                               cand_pages=cand_pages, cand_npages=cand_npages, indices=ws.indices,
-                               budget=ws.budget, weights=ws.weights, threshold=ws.threshold,
-                               status=ws.status)
-    elif mode == "threshold":
-        ops.threshold_prune(ws.scores, cache.kv_indptr, cache.kv_last_page_len, value,
-                            cand_pages=cand_pages, cand_npages=cand_npages, indices=ws.indices,
-                            budget=ws.budget, cut=ws.threshold, status=ws.status)
-    else:
-        ops.topp_prune(ws.scores, cache.kv_indptr, cache.kv_last_page_len, value,
-                       cand_pages=cand_pages, cand_npages=cand_npages, indices=ws.indices,
-                       budget=ws.budget, threshold=ws.threshold, status=ws.status)
-    ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices,
-                           ws.indices, ws.budget, out=ws.out if out is None else out,
-                           workspace=ws.attn_ws, chunk=ws.attn_chunk, status=ws.status,
-                           weights=ws.weights)
-    return ws.out if out is None else out
+    pruner = {"top_p": "top_p", "threshold": "threshold"}.get(cfg.weight_pruner, "none")
+    return ops.select_prune_attend_step(
+        q, cache.k_pages, cache.v_pages, cache.k4_pages, cache.kmeta, cache.kv_indptr, cache.kv_indices,
+        cache.kv_last_page_len, max_pages=ws.max_pages, token_budget=ws.token_budget, pruner=pruner,
+        pruner_value=cfg.threshold, out=ws.out if out is None else out, workspace=ws.buffer, flags=ws.flags,
+        variant=variant, attn_chunk=ws.attn_chunk, status=ws.status)
 
 
 def step_algorithmic_bytes(cache: PagedKVCache, num_q_heads: int, config: SparseConfig,
