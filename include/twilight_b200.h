@@ -79,8 +79,11 @@ TWL_API const char* twl_last_cuda_error(void);
  * probs: [rows][d] contiguous probabilities (rows = batch*num_heads); mask: [rows][d]
  * bytes, written 0/1; top_p_arr: [rows] fp32 or NULL (then top_p_val is used).
  * Same search as the reference: low=0, high=probs[row][0], eps=1e-5, mask = probs > low.
- * The f16 form takes fp16 or bf16 probabilities; low/high/mid/p are rounded to that type
- * as in the reference, partial sums are kept in fp32. */
+ * The f16 form takes fp16 or bf16 probabilities and reproduces the reference's arithmetic in that
+ * type: p, eps, low, high, mid and the stop width are rounded to it, and the mass above the pivot
+ * is added in it, in the order of the reference's 1024-thread block reduction (per chunk of
+ * 1024*gcd(8,d) elements: the thread's items in order, a shuffle-down tree per warp, the warp
+ * totals in order).  The masks equal the reference kernel's bit for bit. */
 TWL_API int twl_top_p_return_mask_f32(const float* probs, uint8_t* mask, const float* top_p_arr,
                               float top_p_val, uint32_t rows, uint32_t d, int32_t* status,
                               void* stream);

@@ -30,7 +30,11 @@ def build(ref_root: str = "/root/reference", verbose: bool = False):
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
     ext.load(name=NAME, sources=[str(src)],
              extra_include_paths=[str(ref / "csrc" / "include"), str(ref / "csrc" / "src"), str(inc)],
+             # FLASHINFER_ENABLE_BF16 is the reference's own switch for the bf16 branch of its fp16 entry
+             # point (csrc/src/pytorch_extension_utils.h:23-57)
+             extra_cflags=["-DFLASHINFER_ENABLE_BF16"],
              extra_cuda_cflags=["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo",
+                                "-DFLASHINFER_ENABLE_BF16",
                                 # torch's default -D__CUDA_NO_HALF_*: the FlashInfer headers need them off
                                 "-U__CUDA_NO_HALF_OPERATORS__", "-U__CUDA_NO_HALF_CONVERSIONS__",
                                 "-U__CUDA_NO_HALF2_OPERATORS__", "-U__CUDA_NO_BFLOAT16_CONVERSIONS__",

@@ -143,3 +143,64 @@ def test_growing_cache_page_table_follows_the_length():
     assert c.view.kv_indices is idx17 and c.view.kv_last_page_len.tolist() == [2, 2, 2]   # same page count: reused
     with pytest.raises(ValueError):
         c._set_length(101)
+
+
+def test_device_guard_helpers():
+    """Every C-ABI call runs with the tensors' device current and refuses tensors of other devices."""
+    from twilight_b200.kernel import ops
+    cpu = torch.zeros(4)
+    with pytest.raises(_lib.TwilightError, match="CUDA tensors only"):
+        ops._on(cpu)
+    meta0 = torch.empty(1, device="meta")
+    with pytest.raises(_lib.TwilightError, match="out is on meta"):
+        ops._same_device(torch.device("cuda", 1), q=None, out=meta0)
+    ops._same_device(torch.device("cpu"), a=cpu, b=None)      # same device, None is skipped
+    with pytest.raises(_lib.TwilightError, match="CUDA tensors only"):
+        ops._launch("version", cpu)
+
+
+def test_mask_operators_are_registered_custom_ops_with_shape_inference():
+    """The reference registers both mask operators as torch custom ops without mutated arguments
+    (twilight/kernel/cuda/sampling.py:62-100); here they live under ``torch.ops.twilight_b200`` and
+    carry a fake-tensor rule, so tracing needs no GPU."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from twilight_b200 import kernel
+    for name in ("top_p_fp32_return_mask", "top_p_fp16_return_mask"):
+        op = getattr(torch.ops.twilight_b200, name)
+        schema = op.default._schema
+        assert [a.name for a in schema.arguments] == ["probs", "maybe_top_p_arr", "top_p_val"]
+        assert not any(a.alias_info is not None and a.alias_info.is_write for a in schema.arguments)
+    with FakeTensorMode():
+        probs = torch.empty(2, 3, 1, 64, device="cuda", dtype=torch.float16)
+        m = kernel.top_p_fp16_return_mask(probs, 0.9)
+        assert m.shape == probs.shape and m.dtype == torch.bool and m.device == probs.device
+        m = kernel.top_p_fp32_return_mask(probs.float(), torch.empty(6, device="cuda"))
+        assert m.shape == probs.shape and m.dtype == torch.bool
+
+
+def test_step_workspace_layout_is_consistent():
+    from twilight_b200.kernel import ops
+    lib = _lib.load()
+    for (b, h, pages, budget, flags) in [(16, 32, 2048, 8192, 0), (64, 32, 2048, 0, 0), (2, 8, 7, 1000, 3),
+                                         (1, 1, 1, 16, 1)]:
+        lay = ops.step_workspace_layout(b, h, pages, budget, 256, flags)
+        assert lay.total == lib.twl_step_workspace_bytes(b, h, pages, budget, 256, flags)
+        k = quest_max_k(budget, pages) if budget > 0 else 0
+        stride = (k if budget > 0 else pages) * 16
+        assert lay.max_k == k and lay.stride == stride
+        assert lay.attn == 0 and lay.attn_bytes == lib.twl_sparse_attn_workspace_bytes(b, h, stride, 256)
+        parts = [(lay.attn, lay.attn_bytes), (lay.page_scores, b * h * pages * 4 if budget > 0 else 0),
+                 (lay.cand_pages, b * h * k * 4), (lay.cand_npages, b * h * 4 if budget > 0 else 0),
+                 (lay.scores, b * h * stride * 4), (lay.indices, b * h * stride * 4), (lay.budget, b * h * 4),
+                 (lay.threshold, b * h * 8), (lay.weights, b * h * stride * 4 if flags & 1 else 0)]
+        end = 0
+        for off, size in parts:                              # in order, 256-byte aligned, no overlap
+            assert off % 256 == 0 and off >= end
+            end = off + size
+        assert lay.total >= end
+        assert lay.kernels == (5 if budget > 0 else 3) + ((2 if budget > 0 else 1) if flags & 2 else 0)
+    assert lib.twl_step_workspace_bytes(0, 1, 1, 0, 256, 0) == 0
+    # null pointers are refused before anything is launched
+    assert lib.twl_select_prune_attend_step(None, 1, None, None, None, None, None, None, None, 1, 1, 1, 1, 1, 0, 0,
+                                            0.9, None, 0.088, 0, 0, 256, None, None, 0, None, None) == -1
+    assert lib.twl_round_scores(None, 4, 1, 1.0, None) == -1

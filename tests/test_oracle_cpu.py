@@ -200,3 +200,38 @@ def test_topp_oracle_matches_recorded_reference_kernel_masks():
             total_diff += bad.size
             assert k1[r][0]                                  # the sink is always kept
     assert total_diff <= 8
+
+
+# ---- the search instantiated for fp16 / bf16 rows (csrc/src/sampling.cu:22-43) ------------------
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+def test_topp_low_precision_flavour_known_answers(dt):
+    # the paper's example row is exactly representable enough: same kept set as the fp32 search
+    row = torch.tensor([0.5, 0.03, 0.02, 0.15, 0.04, 0.25], dtype=dt)
+    for sums in ("fp32", "dtype"):
+        low, rounds = O.top_p_search_lowp(row, 0.89, sums)
+        assert (row.double() > low).tolist() == [True, False, False, True, False, True]
+        assert 1 <= rounds < O.SEARCH_ITER_CAP
+        assert float(torch.tensor(low, dtype=torch.float64).to(dt)) == low   # low lives in the dtype
+    # sink absent: high = x[0] = 0, one round, nothing pruned
+    row = torch.tensor([0.0, 0.7, 0.2, 0.1], dtype=dt)
+    low, rounds = O.top_p_search_lowp(row, 0.5)
+    assert rounds == 1 and low == 0.0
+
+
+def test_topp_low_precision_flavours_agree_up_to_sum_rounding():
+    g = torch.Generator().manual_seed(5)
+    for dt, tol in ((torch.float16, 5e-3), (torch.bfloat16, 4e-2)):
+        logits = torch.randn(8192, generator=g) * 2.5
+        logits[0] += 8
+        row = torch.softmax(logits, -1).to(dt)
+        la, _, margin = O.top_p_search_lowp(row, 0.9, "fp32", return_margin=True)
+        lb, _ = O.top_p_search_lowp(row, 0.9, "dtype")
+        x = row.double()
+        ma, mb = float(x[x > la].sum()), float(x[x > lb].sum())
+        assert margin >= 0 and abs(ma - mb) <= tol     # kept masses differ by the rounding of the sums only
+        assert ma >= 0.9 - tol and mb >= 0.9 - tol
+
+
+def test_half_block_sum_is_exact_when_nothing_rounds():
+    vals = torch.arange(1024 * 8, dtype=torch.float32).remainder(2).to(torch.float16)  # 0/1 pattern: sums stay exact
+    assert float(O._half_block_sum(vals, 8)) == 4096.0

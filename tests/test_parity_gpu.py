@@ -141,12 +141,24 @@ def test_fused_quest_select_equals_two_step_form(hq, hkv):
             torch.cuda.synchronize()
             assert int(counters.abs().sum()) == 0
             assert torch.equal(a_n, b_n)
+            # groups of four or more query heads are scored on tensor cores in the two-step form and
+            # with FMAs in the fused one: same products, another order of the fp32 additions
+            same_kernel = hq // hkv < 4
             for b in range(len(lens)):
                 npg = (lens[b] + PAGE - 1) // PAGE
-                assert torch.equal(a_scores[b, :, :npg], b_scores[b, :, :npg])
+                if same_kernel:
+                    assert torch.equal(a_scores[b, :, :npg], b_scores[b, :, :npg])
+                else:
+                    assert torch.allclose(a_scores[b, :, :npg], b_scores[b, :, :npg], rtol=2e-6, atol=1e-4)
                 for h in range(hq):
                     k = int(a_n[b, h])
-                    assert torch.equal(a_pages[b, h, :k], b_pages[b, h, :k])
+                    if same_kernel:
+                        assert torch.equal(a_pages[b, h, :k], b_pages[b, h, :k])
+                    else:   # each selection is exact on its own scores; they differ only in near-ties
+                        sc = b_scores[b, h, :npg].cpu().numpy()
+                        must, tie, thr = U.expected_candidates(sc, k)
+                        for pg in set(a_pages[b, h, :k].tolist()) ^ set(b_pages[b, h, :k].tolist()):
+                            assert abs(sc[pg] - thr) <= 1e-4 * max(1.0, abs(thr))
 
 
 def test_quest_selector_mask_interface_matches_reference_fixture(golden):
@@ -231,12 +243,12 @@ def test_gemv_entry_with_the_reference_call_signature():
                                        cache.kv_indptr, cache.kv_last_page_len)
 
 
-def test_corrupt_page_table_is_flagged_not_followed():
+@pytest.mark.parametrize("hq,hkv", [(4, 2), (4, 4), (8, 1)])
+def test_corrupt_page_table_is_flagged_not_followed(hq, hkv):
     """A page-table entry outside the cache must never be dereferenced: the selector scores the
-    page -inf, the estimator leaves its slots alone, both raise FLAG_BAD_INDEX, and every other
-    page comes out as without the corruption."""
+    page -inf, the estimator writes -inf into its sixteen slots (so the pruner keeps none of its
+    tokens), both raise FLAG_BAD_INDEX, and every other page comes out as without the corruption."""
     lens = [700, 300]
-    hq, hkv = 4, 2
     q, cache = make_decode_inputs(len(lens), hq, hkv, lens, dtype=torch.bfloat16, device=DEV, seed=41)
     good_scores = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
                                     max_pages=cache.max_pages).clone()
@@ -253,7 +265,12 @@ def test_corrupt_page_table_is_flagged_not_followed():
                           max_pages=cache.max_pages, scores=scores, status=status)
         assert int(status.item()) & ops.FLAG_BAD_INDEX
         lo, hi = victim * PAGE, (victim + 1) * PAGE
-        assert (scores[0, :, lo:hi] == 777.0).all()                       # untouched
+        assert torch.isinf(scores[0, :, lo:hi]).all() and (scores[0, :, lo:hi] < 0).all()
+        idx, bud = ops.topp_prune(scores, cache.kv_indptr, cache.kv_last_page_len, 2.0)   # keep all with p > 0
+        for h in range(hq):
+            kept = idx[0, h, : int(bud[0, h])]
+            assert not ((kept >= lo) & (kept < hi)).any()
+            assert int(bud[0, h]) == lens[0] - PAGE
         keep = torch.ones(scores.shape[-1], dtype=torch.bool, device=DEV)
         keep[lo:hi] = False
         n1 = ((lens[1] + PAGE - 1) // PAGE) * PAGE     # slots past a sequence's pages are not written
@@ -620,6 +637,135 @@ def test_attention_workspace_and_bad_index_handling():
                                indices, budget, workspace=torch.zeros(16, dtype=torch.uint8, device=DEV))
 
 
+# ---- query-head groups: tensor-core kernels against the per-head kernels -----------------------------------
+@pytest.mark.parametrize("hq,hkv,dt", [(8, 2, torch.bfloat16), (8, 1, torch.bfloat16), (4, 1, torch.float16),
+                                       (16, 2, torch.float16), (4, 2, torch.bfloat16)])
+def test_group_estimator_tensor_core_equals_integer_dot(hq, hkv, dt):
+    """Default estimator for query-head groups (16-bit tensor-core tiles) against the integer-dot
+    group kernel (variant +32) and the fp64 oracle, ragged lengths with odd page counts."""
+    lens = [1, 17, 33, 1000, 2049, 4000, 16 * 129]
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=dt, device=DEV, seed=61,
+                                  recipe="mid", shuffle_pages=True)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kw = dict(max_pages=cache.max_pages, status=status)
+    a = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len, **kw)
+    b_ = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
+                           variant=3 + 32, **kw)
+    assert int(status.item()) == 0
+    g = hq // hkv
+    worst = 0.0
+    for b, n in enumerate(lens):
+        npg = (n + PAGE - 1) // PAGE
+        ra, rb = a[b, :, : npg * PAGE], b_[b, :, : npg * PAGE]
+        assert torch.equal(torch.isinf(ra), torch.isinf(rb))
+        fin = torch.isfinite(ra)
+        scale = max(1.0, float(rb[fin].abs().max()))
+        assert float((ra[fin] - rb[fin]).abs().max()) <= 2e-3 * scale
+        for h in (0, hq - 1):
+            want, _ = U.oracle_scores_row(q, cache, b, h, g)
+            got = ra[h].cpu().numpy()
+            f = np.isfinite(want)
+            assert np.array_equal(np.isfinite(got), f)
+            worst = max(worst, float(np.abs(got[f] - want[f]).max()) / max(1.0, float(np.abs(want[f]).max())))
+    U.record("group_estimator_mma", hq=hq, hkv=hkv, dtype=str(dt), worst_rel=worst)
+    assert worst <= 2e-4     # exact products, fp32 accumulation: tighter than the integer-dot form's 2e-3
+
+
+@pytest.mark.parametrize("hq,hkv,dt", [(8, 1, torch.bfloat16), (8, 2, torch.float16), (32, 4, torch.bfloat16)])
+def test_group_page_scores_tensor_core_vs_oracle(hq, hkv, dt):
+    """Quest page scores of groups of 4 / 8 query heads ([min|max].[min(q,0);max(q,0)] on tensor
+    cores) against the fp32 oracle: products are exact, only the order of the fp32 additions differs."""
+    lens = [16, 100, 4096 + 5, 9000]
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=dt, device=DEV, seed=62,
+                                  recipe="mid", shuffle_pages=True)
+    _, _, ps = ops.quest_select(q, cache.kmeta, cache.kv_indptr, cache.kv_indices, 256, max_pages=cache.max_pages)
+    g = hq // hkv
+    for b, n in enumerate(lens):
+        npg = (n + PAGE - 1) // PAGE
+        for h in range(hq):
+            want = U.oracle_page_scores(q, cache, b, h, g)
+            got = ps[b, h, :npg].cpu().numpy()
+            assert np.allclose(got, want, rtol=2e-5, atol=2e-4), (b, h, np.abs(got - want).max())
+
+
+def test_step_one_call_equals_the_separate_operators():
+    """twl_select_prune_attend_step against the same five launches issued one by one."""
+    lens = [1500, 3000, 40]
+    hq, hkv = 8, 4
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=torch.bfloat16, device=DEV, seed=63,
+                                  recipe="mid", shuffle_pages=True)
+    cfg = SparseConfig(selector="quest", token_budget=1024, weight_pruner="top_p", threshold=0.9)
+    ws = DecodeWorkspace.for_cache(cache, hq, cfg, attn_chunk=256)
+    assert ws.buffer.numel() == _lib.load().twl_step_workspace_bytes(len(lens), hq, cache.max_pages, 1024, 256, 0)
+    out = select_prune_attend_step(q, cache, ws).clone()
+    _status_ok(ws)
+    cp, cn, _ = ops.quest_select(q, cache.kmeta, cache.kv_indptr, cache.kv_indices, 1024, max_pages=cache.max_pages)
+    sc = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
+                           max_pages=cache.max_pages, cand_pages=cp, cand_npages=cn)
+    idx, bud = ops.topp_prune(sc, cache.kv_indptr, cache.kv_last_page_len, 0.9, cand_pages=cp, cand_npages=cn)
+    want = ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices, idx, bud,
+                                  chunk=256)
+    assert torch.equal(ws.cand_npages, cn)
+    valid_pg = torch.arange(cp.shape[-1], device=DEV)[None, None] < cn[:, :, None]
+    assert torch.equal(torch.where(valid_pg, ws.cand_pages, 0), torch.where(valid_pg, cp, 0))
+    assert torch.equal(ws.budget, bud)
+    pos = torch.arange(idx.shape[-1], device=DEV)[None, None] < bud[:, :, None]
+    assert torch.equal(torch.where(pos, ws.indices, 0), torch.where(pos, idx, 0))
+    assert torch.equal(out, want)
+    # a workspace that is too small or misaligned is refused before anything is launched
+    with pytest.raises(_lib.TwilightError, match="workspace"):
+        ops.select_prune_attend_step(q, cache.k_pages, cache.v_pages, cache.k4_pages, cache.kmeta, cache.kv_indptr,
+                                     cache.kv_indices, cache.kv_last_page_len, max_pages=cache.max_pages,
+                                     token_budget=1024, pruner="top_p", pruner_value=0.9, out=ws.out,
+                                     workspace=ws.buffer[:4096])
+
+
+def test_unit_seeded_inputs_do_not_depend_on_the_block_they_are_generated_in():
+    """A (sequence, KV head) unit generated inside a rank's block equals the same unit generated
+    alone: what lets one rank rebuild another rank's unit to check a gathered result."""
+    from twilight_b200.gen import make_unit_inputs
+    lens = {2: 300, 5: 1000, 7: 64}
+    qb, cb = make_unit_inputs([2, 5, 7], [1, 3], 2, [lens[b] for b in (2, 5, 7)], rho=0.02, device=DEV, seed=9,
+                              recipe="mid", shuffle_pages=True)
+    q1, c1 = make_unit_inputs([5], [3], 2, [1000], rho=0.02, device=DEV, seed=9, recipe="mid", shuffle_pages=True)
+    assert torch.equal(qb[1, 2:4], q1[0])
+    for a, c in zip(cb.dense_kv(1, 1), c1.dense_kv(0, 0)):
+        assert torch.equal(a, c)
+    for a, c in zip(cb.dense_k4(1, 1), c1.dense_k4(0, 0)):
+        assert torch.equal(a, c)
+
+
+def test_round_scores_matches_torch_rounding():
+    x = torch.randn(3, 1000, device=DEV) * 20
+    x[0, :5] = float("-inf")
+    for dt in (torch.float16, torch.bfloat16):
+        y = ops.round_scores(x.clone(), dt)
+        assert torch.equal(y, x.to(dt).float())
+        z = ops.round_scores(x.clone(), dt, post_scale=U.SM_SCALE)
+        assert torch.equal(z, (x.to(dt).float() * np.float32(U.SM_SCALE)).to(dt).float())
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("L", [7, 64, 1000, 4096, 32768, 60000])
+def test_top_p_fp16_return_mask_vs_low_precision_oracle(dt, L):
+    """The fp16/bf16 mask operator against the oracle that rounds where
+    csrc/include/sampling.cuh:156-217 instantiated for that dtype rounds (scalars and sums, the sums
+    in the order of the reference's block reduction): equal masks, element for element.  The same
+    oracle flavour is pinned against the reference's own kernel in tests/test_ref_kernel_gpu.py.
+    60000 elements do not fit the kernel's shared-memory row: the global-memory path."""
+    from twilight_b200.kernel import top_p_fp16_return_mask
+    p = 0.95
+    g = torch.Generator().manual_seed(L + (3 if dt == torch.float16 else 4))
+    logits = torch.randn(1, 3, 1, L, generator=g) * 2.0
+    logits[..., 0] += 7.0
+    probs = torch.softmax(logits, -1).to(dt)
+    m = top_p_fp16_return_mask(probs.to(DEV), p).cpu().reshape(3, L).numpy()
+    for r in range(3):
+        x = probs.reshape(3, L)[r]
+        low, _ = O.top_p_search_lowp(x, p, "dtype")
+        assert np.array_equal(m[r], x.double().numpy() > low), r
+
+
 # ---- whole step ------------------------------------------------------------------------------------------------
 def _step_vs_oracle(q, cache, hq, cfg, rows, dtype_faithful_report=False):
     ws = DecodeWorkspace.for_cache(cache, hq, cfg)
@@ -679,36 +825,108 @@ def test_step_config0_fp16_full_candidates(recipe):
         assert float(ws.budget.float().mean()) > 1000
 
 
-def test_step_config0_against_dtype_faithful_pyimpl():
-    """Against the reference's own dtype path (fp16 logits, fp16 fake-quant, dense masked
-    attention).  Its logits are rounded to fp16 several times (dequantised K, matmul output, the
-    division by sqrt(D)): at logits near 10 that is a few 1e-2 in the logit, i.e. a few percent of
-    a token's probability, which for heavy hitters of probability ~0.02 exceeds the absolute 1e-4
-    window.  Kept sets may therefore differ in tokens within 1e-4 OR within 5% (relative) of the
-    reference's threshold; heads whose kept sets agree must give the same output within
-    2e-2 max-abs / 1e-3 mean-abs."""
-    q, cache = make_decode_inputs(1, 32, 32, 4096, rho=0.01, dtype=torch.float16, device=DEV, seed=0, recipe="mid")
-    cfg = SparseConfig(selector="none", weight_pruner="top_p", threshold=0.95)
+def _reference_dtype_step(q, cache, hq, **kw):
+    """The reference's own dtype path (twilight/pyimpl/attention.py:188-306 restated in the model
+    dtype: logits, fake-quantised K, estimate and masked attention all rounded where torch rounds)
+    on the dense tensors of the cache."""
+    g = hq // cache.num_kv_heads
+    outs = []
+    for b in range(cache.batch):
+        kd = torch.stack([cache.dense_kv(b, h // g)[0] for h in range(hq)]).cpu()[None]
+        vd = torch.stack([cache.dense_kv(b, h // g)[1] for h in range(hq)]).cpu()[None]
+        outs.append(O.decode_step(q[b: b + 1].cpu()[:, :, None], kd, vd, quant_group=32, **kw))
+    return outs
+
+
+@pytest.mark.parametrize("case", ["config0", "config1_slice"])
+def test_step_literal_recipe_equals_dtype_faithful_reference_exactly(case):
+    """Literal recipe against the reference's dtype path: the softmax mass sits on the sink, so both
+    sides must keep exactly token 0 for every head, and the outputs are V[0] on both sides."""
+    if case == "config0":   # B=1, 32 = 32 heads, L=4096, fp16, selector none, top-p 0.95
+        q, cache = make_decode_inputs(1, 32, 32, 4096, rho=0.01, dtype=torch.float16, device=DEV, seed=0,
+                                      recipe="literal")
+        cfg = SparseConfig(selector="none", weight_pruner="top_p", threshold=0.95)
+        kw = dict(selector="none", threshold=0.95)
+    else:                   # one sequence of config 1: 32 = 32 heads, L=32768, bf16, Quest 8192, top-p 0.95
+        q, cache = make_decode_inputs(1, 32, 32, 32768, rho=0.005, dtype=torch.bfloat16, device=DEV, seed=3,
+                                      recipe="literal", shuffle_pages=True)
+        cfg = SparseConfig(selector="quest", token_budget=8192, weight_pruner="top_p", threshold=0.95)
+        kw = dict(selector="quest", token_budget=8192, chunk_size=16, threshold=0.95)
     ws = DecodeWorkspace.for_cache(cache, 32, cfg)
     out = select_prune_attend_step(q, cache, ws).float().cpu()
-    kd = torch.stack([cache.dense_kv(0, h)[0] for h in range(32)]).cpu()[None]
-    vd = torch.stack([cache.dense_kv(0, h)[1] for h in range(32)]).cpu()[None]
-    ref = O.decode_step(q.cpu()[:, :, None], kd, vd, selector="none", quant_group=32, threshold=0.95)
+    _status_ok(ws)
+    ref = _reference_dtype_step(q, cache, 32, **kw)[0]
+    assert (ws.budget == 1).all() and (ws.indices[:, :, 0] == 0).all()
+    assert (ref["budget"] == 1).all() and ref["mask"][0, :, 0, 0].all()
+    err = (out[0] - ref["out"][0, :, 0].float()).abs()
+    assert float(err.max()) <= ATOL_MAX and float(err.mean()) <= ATOL_MEAN
+
+
+@pytest.mark.parametrize("rounded", [False, True])
+def test_step_mid_recipe_against_dtype_faithful_reference_measured(rounded):
+    """Config 0 with budgets of tens of tokens against the reference's dtype path.  The reference
+    rounds its logits to fp16 three times (dequantised K, the matmul, the division by sqrt(D)), the
+    library keeps fp32 scores; ``round_to_dtype`` makes the library round its scores to fp16 too
+    (the last two of the three).  What differs is measured and bounded: every token that one side
+    keeps and the other drops has a probability within ``REL`` (relative) or 1e-4 (absolute) of the
+    reference's threshold, at most ``MAX_TOKENS`` such tokens per head, and the heads whose kept
+    sets agree give the same output within 2e-2 max-abs / 1e-3 mean-abs."""
+    # rounded: the strict criterion (1e-4 absolute, no relative allowance); fp32 scores: measured bound
+    REL, MAX_TOKENS, MIN_EQUAL_HEADS = (0.0, 1, 30) if rounded else (0.05, 4, 8)
+    q, cache = make_decode_inputs(1, 32, 32, 4096, rho=0.01, dtype=torch.float16, device=DEV, seed=0, recipe="mid")
+    cfg = SparseConfig(selector="none", weight_pruner="top_p", threshold=0.95, round_to_dtype=rounded)
+    ws = DecodeWorkspace.for_cache(cache, 32, cfg)
+    out = select_prune_attend_step(q, cache, ws).float().cpu()
+    _status_ok(ws)
+    ref = _reference_dtype_step(q, cache, 32, selector="none", threshold=0.95)[0]
     assert ref["out"].dtype == torch.float16
-    same, errs = 0, []
+    same, errs, n_diff, worst_rel = 0, [], [], 0.0
     for h in range(32):
         probs = torch.softmax(ref["est"][0, h, 0].float(), -1).numpy()
         low, _ = O.top_p_search(probs, 0.95)
         want = set(np.nonzero(ref["mask"][0, h, 0].numpy())[0].tolist())
         got = set(ws.indices[0, h, : int(ws.budget[0, h])].cpu().numpy().tolist())
-        for t in want ^ got:
-            assert abs(probs[t] - low) <= max(P_TOL, 0.05 * low), (h, t, probs[t], low)
-        if want == got:
+        diff = want ^ got
+        n_diff.append(len(diff))
+        for t in diff:
+            rel = abs(probs[t] - low) / max(float(low), 1e-30)
+            worst_rel = max(worst_rel, 0.0 if abs(probs[t] - low) <= P_TOL else rel)
+            assert abs(probs[t] - low) <= max(P_TOL, REL * low), (h, t, probs[t], low)
+        if not diff:
             same += 1
             errs.append((out[0, h] - ref["out"][0, h, 0].float()).abs().numpy())
-    assert same >= 8
+    U.record("step_mid_vs_dtype_reference", rounded=rounded, heads_equal=same, tokens_differing=int(sum(n_diff)),
+             max_tokens_per_head=int(max(n_diff)), worst_rel_distance=worst_rel,
+             avg_budget=float(ws.budget.float().mean()))
+    assert max(n_diff) <= MAX_TOKENS and same >= MIN_EQUAL_HEADS
     errs = np.stack(errs)
     assert errs.max() <= ATOL_MAX and errs.mean() <= ATOL_MEAN
+
+
+def test_quest_pages_with_scores_rounded_to_dtype_match_reference_ranking(golden):
+    """With ``round_scores`` to bf16 before the page top-k the library ranks what the reference ranks
+    (its matmul returns bf16, quest.py:76-84): kept pages may differ from the reference fixture
+    only in pages whose ROUNDED score equals the k-th rounded score (true ties, which torch.topk
+    breaks in an unspecified order)."""
+    q = torch.from_numpy(golden["quest_q"]).to(torch.bfloat16).to(DEV)[:, :, 0].contiguous()   # [2,4,128]
+    k = torch.from_numpy(golden["quest_k"]).to(torch.bfloat16).to(DEV)                       # [2,4,100,128]
+    bsz, h, L, _ = k.shape
+    cache = PagedKVCache.from_dense(k, torch.zeros_like(k))
+    for budget in (32, 40, 1000):
+        ref = golden[f"quest_mask_bf16_{budget}"]
+        kk = quest_max_k(budget, cache.max_pages)
+        ps = ops.quest_page_scores(q, cache.kmeta, cache.kv_indptr, cache.kv_indices, max_pages=cache.max_pages)
+        ops.round_scores(ps, torch.bfloat16)
+        cp, cn, _ = ops.quest_topk(ps, cache.kv_indptr, budget, max_pages=cache.max_pages)
+        psn = ps.cpu().numpy()
+        for b in range(bsz):
+            for hh in range(h):
+                ours = set(cp[b, hh, : int(cn[b, hh])].cpu().numpy().tolist())
+                theirs = set((np.nonzero(ref[b, hh, 0])[0] // PAGE).tolist())
+                assert len(ours) == kk == len(theirs)
+                kth = np.sort(psn[b, hh])[::-1][kk - 1]
+                for pg in ours ^ theirs:
+                    assert psn[b, hh, pg] == kth, (budget, b, hh, pg, psn[b, hh, pg], kth)
 
 
 @pytest.mark.parametrize("hq,hkv,sel", [(8, 8, "quest"), (8, 2, "quest"), (8, 2, "none")])

@@ -6,6 +6,7 @@ import torch
 
 from oracle import build_ref
 from oracle import twilight_oracle as O
+from tests import util as U
 
 pytestmark = pytest.mark.gpu
 P_TOL = 1e-4
@@ -54,3 +55,52 @@ def test_reference_kernel_sink_quirks(ref):
     low, rounds = O.top_p_search(probs.cpu().flatten().numpy(), 0.5)
     assert rounds == 1 and k1 == (probs.cpu().flatten() > float(low)).tolist()
     assert k1 == [False, True, True, True, False, False, False, False]
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("L", [64, 1000, 4096, 32768])
+def test_fp16_entry_reference_kernel_vs_library_vs_oracle(ref, dt, L):
+    """``top_p_fp16_return_mask`` (csrc/src/sampling.cu:22-43) on fp16 and bf16 rows: the
+    reference's kernel, this library's operator and the oracle's low-precision flavour (every
+    scalar and every partial sum rounded to the dtype, in the order of the reference's block
+    reduction) must give the same mask on every element."""
+    from twilight_b200.kernel import top_p_fp16_return_mask
+    p = 0.9
+    g = torch.Generator().manual_seed(7 * L + (1 if dt == torch.float16 else 2))
+    logits = torch.randn(2, 2, 1, L, generator=g) * 2.5
+    logits[..., 0] += 8.0
+    probs = torch.softmax(logits, -1).to(dt)
+    dev = probs.cuda().contiguous()
+    ours = top_p_fp16_return_mask(dev, p).cpu().reshape(4, L).numpy()
+    k1m = torch.zeros_like(dev, dtype=torch.bool)
+    ref.top_p_fp16_return_mask(dev, k1m, None, float(p), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    k1 = k1m.cpu().reshape(4, L).numpy()
+    rows = probs.reshape(4, L)
+    for r in range(4):
+        x = rows[r]
+        xf = x.double().numpy()
+        low_d, rounds = O.top_p_search_lowp(x, p, "dtype")
+        low_32, _ = O.top_p_search_lowp(x, p, "fp32")
+        U.record("fp16_entry", dtype=str(dt), L=L, row=r, rounds=rounds, n_ours=int(ours[r].sum()),
+                 n_ref=int(k1[r].sum()), n_oracle_dtype=int((xf > low_d).sum()),
+                 n_oracle_fp32_sums=int((xf > low_32).sum()), diff_ours_ref=int((ours[r] != k1[r]).sum()),
+                 diff_ref_oracle=int((k1[r] != (xf > low_d)).sum()))
+        assert np.array_equal(k1[r], xf > low_d), (r, "oracle vs reference kernel")
+        assert np.array_equal(ours[r], k1[r]), (r, "library vs reference kernel")
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+def test_fp16_entry_per_row_threshold_tensor(ref, dt):
+    """``top_p`` as a per-row fp32 tensor (sampling.cuh:125) through the fp16 entry point."""
+    from twilight_b200.kernel import top_p_fp16_return_mask
+    g = torch.Generator().manual_seed(99)
+    logits = torch.randn(1, 6, 1, 2048, generator=g) * 2.0
+    logits[..., 0] += 6.0
+    probs = torch.softmax(logits, -1).to(dt).cuda().contiguous()
+    arr = torch.tensor([0.5, 0.8, 0.9, 0.95, 0.99, 1.0], dtype=torch.float32, device="cuda")
+    ours = top_p_fp16_return_mask(probs, arr)
+    k1m = torch.zeros_like(probs, dtype=torch.bool)
+    ref.top_p_fp16_return_mask(probs, k1m, arr, 0.0, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert torch.equal(ours, k1m)

@@ -1,5 +1,7 @@
 """Helpers shared by the GPU parity tests: run the oracle on the rows of a paged cache."""
+import json
 import math
+import os
 
 import numpy as np
 import torch
@@ -71,3 +73,13 @@ def expected_candidates(scores, k):
     order = np.sort(scores)[::-1]
     thr = order[k - 1]
     return set(np.nonzero(scores > thr)[0].tolist()), set(np.nonzero(scores == thr)[0].tolist()), thr
+
+
+def record(name, **stats):
+    """Appends measured parity figures (counts of differing tokens, distances to thresholds) as one
+    JSON line to the file named by TWL_PARITY_STATS, when that variable is set; the assertions of
+    a test state the bound, this keeps the measurement behind it."""
+    path = os.environ.get("TWL_PARITY_STATS")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps({"test": name, **stats}, default=float) + "\n")

@@ -839,61 +839,46 @@ estimate_int4_warp_group_kernel(const EstParams p) {
 
 // ---- query-head groups on the tensor cores ---------------------------------------------------------
 // The same warp-private rings, but a staged page (16 tokens) is scored against the whole group with
-// m16n8k16 tiles: A = the page's codes of one 32-channel quantisation group, turned into 16-bit
-// floats in registers, B = the group's queries for those channels (exact: q already has the model
-// dtype), fp32 accumulators; then score += scale * acc + min * sum(q) per (token, group) as in the
-// other kernels.  The work per staged byte no longer grows with the number of query heads.
+// m16n8k16 tiles: A = the page's codes of one 32-channel quantisation group, turned into fp16 in
+// registers, B = the group's queries for those channels, fp32 accumulators; then
+// score += scale * acc + min * sum(q) per (token, group) as in the other kernels.  The work per
+// staged byte no longer grows with the number of query heads.
 //
 // Lane 4*g + t owns tokens g and g+8 of the page and word t of their 16-byte group chunk: eight
-// nibbles, channels 8t..8t+7 of the group.  Two codes at a time (bits 0-3 and 16-19 of the word,
-// after a shift by 0, 4, 8 or 12) are or-ed into the mantissas of a pair of 16-bit floats:
-//   bf16  0x4300 | c = 128 + c (exact); the 128 is not subtracted but folded into the minimum,
-//         scale*(acc - 128*sum q) + min*sum q = scale*acc + (min - 128*scale)*sum q;
-//   fp16  0x6400 | c = 1024 + c and 0x5400 | (c << 4) = 64 + c, brought back to c by one exact
-//         subtraction each.
-// The k-slots of a tile thus hold channels in the order the nibbles come out; B is built once per
-// block in the same order.  Reads of the ring are conflict-free: the eight tokens of a quarter
-// warp's request sit in eight different 16-byte bank groups (the chunk rotation of the copy).
-template <typename T>
-struct CodePairs;
-template <>
-struct CodePairs<__nv_bfloat16> {
-  static constexpr float kOffset = 128.f;
-  // r[j] = codes of channels (j, j+4) of the word's eight, each as 128 + c
-  static __device__ __forceinline__ void unpack(uint32_t w, uint32_t (&r)[4]) {
-    r[0] = (w & 0x000F000Fu) | 0x43004300u;
-    r[1] = ((w >> 4) & 0x000F000Fu) | 0x43004300u;
-    r[2] = ((w >> 8) & 0x000F000Fu) | 0x43004300u;
-    r[3] = ((w >> 12) & 0x000F000Fu) | 0x43004300u;
-  }
-};
-template <>
-struct CodePairs<__half> {
-  static constexpr float kOffset = 0.f;
-  static __device__ __forceinline__ void unpack(uint32_t w, uint32_t (&r)[4]) {
-    const __half2 b1024 = __half2half2(__ushort_as_half(0x6400));
-    const __half2 b64 = __half2half2(__ushort_as_half(0x5400));
-    const uint32_t w8 = w >> 8;
-    uint32_t u0 = (w & 0x000F000Fu) | 0x64006400u, u1 = (w & 0x00F000F0u) | 0x54005400u;
-    uint32_t u2 = (w8 & 0x000F000Fu) | 0x64006400u, u3 = (w8 & 0x00F000F0u) | 0x54005400u;
-    __half2 c0 = __hsub2(*reinterpret_cast<__half2*>(&u0), b1024);
-    __half2 c1 = __hsub2(*reinterpret_cast<__half2*>(&u1), b64);
-    __half2 c2 = __hsub2(*reinterpret_cast<__half2*>(&u2), b1024);
-    __half2 c3 = __hsub2(*reinterpret_cast<__half2*>(&u3), b64);
-    r[0] = *reinterpret_cast<uint32_t*>(&c0);
-    r[1] = *reinterpret_cast<uint32_t*>(&c1);
-    r[2] = *reinterpret_cast<uint32_t*>(&c2);
-    r[3] = *reinterpret_cast<uint32_t*>(&c3);
-  }
-};
+// nibbles, channels 8t..8t+7 of the group.  Two codes at a time are or-ed into the mantissas of a
+// pair of fp16 numbers - bits 0-3 under 0x6400 give 1024 + c, bits 4-7 under 0x5400 give 64 + c, the
+// same again after one shift by 8 - and one exact subtraction each brings them back to c.  (fp16
+// takes a nibble at two bit positions, bf16 only at one; that is one shift per word instead of
+// three, and the logic unit is what bounds this kernel.)  The k-slots of a tile thus hold channels
+// in the order the nibbles come out; B is built once per block in the same order.
+// B is fp16 whatever the model dtype: q is scaled by a power of two that puts the group's largest
+// |q| into [128, 256) - exact, undone together with the softmax scale - so a bf16 q converts to fp16
+// without rounding unless an element is 2^22 times smaller than the largest one.
+// Reads of the ring are conflict-free: the eight tokens of a quarter warp's request sit in eight
+// different 16-byte bank groups (the chunk rotation of the copy).
+__device__ __forceinline__ void unpack_codes_f16(uint32_t w, uint32_t (&r)[4]) {
+  const __half2 b1024 = __half2half2(__ushort_as_half(0x6400));
+  const __half2 b64 = __half2half2(__ushort_as_half(0x5400));
+  const uint32_t w8 = w >> 8;
+  uint32_t u0 = (w & 0x000F000Fu) | 0x64006400u, u1 = (w & 0x00F000F0u) | 0x54005400u;
+  uint32_t u2 = (w8 & 0x000F000Fu) | 0x64006400u, u3 = (w8 & 0x00F000F0u) | 0x54005400u;
+  const __half2 c0 = __hsub2(*reinterpret_cast<__half2*>(&u0), b1024);  // channels (0, 4) of the word's eight
+  const __half2 c1 = __hsub2(*reinterpret_cast<__half2*>(&u1), b64);    // (1, 5)
+  const __half2 c2 = __hsub2(*reinterpret_cast<__half2*>(&u2), b1024);  // (2, 6)
+  const __half2 c3 = __hsub2(*reinterpret_cast<__half2*>(&u3), b64);    // (3, 7)
+  r[0] = *reinterpret_cast<const uint32_t*>(&c0);
+  r[1] = *reinterpret_cast<const uint32_t*>(&c1);
+  r[2] = *reinterpret_cast<const uint32_t*>(&c2);
+  r[3] = *reinterpret_cast<const uint32_t*>(&c3);
+}
 
 template <typename T, int G>
-__global__ void __launch_bounds__(kEstThreads)
+__global__ void __launch_bounds__(kEstThreads, 2)
 estimate_int4_mma_group_kernel(const EstParams p) {
   static_assert(G >= 2 && G <= 8, "one n8 tile holds the group");
   extern __shared__ __align__(128) uint8_t sm_ring[];  // kEstWarps * kRingDepth * kWarpStageBytes
-  __shared__ int sm_phys[kWarpPagesPerBlock];
-  __shared__ int sm_ntok[kWarpPagesPerBlock];
+  __shared__ int sm_phys[kWarpPagesPerBlock + 1];
+  __shared__ int sm_ntok[kWarpPagesPerBlock + 1];
 
   const int row = blockIdx.y;
   const int b = row / p.Hkv, kvh = row % p.Hkv;
@@ -911,7 +896,7 @@ estimate_int4_mma_group_kernel(const EstParams p) {
   const int n_here = min(kWarpPagesPerBlock, n_pages - first);
 
   const int tid = threadIdx.x;
-  if (tid < kWarpPagesPerBlock) {
+  if (tid <= kWarpPagesPerBlock) {  // one entry more than pages: the partner of an odd last page
     int phys = -1, ntok = 0;
     if (tid < n_here) {
       const int seq_page = first + tid;
@@ -921,7 +906,7 @@ estimate_int4_mma_group_kernel(const EstParams p) {
       ntok = (seq_page == n_seq_pages - 1) ? p.last_len[b] : kPage;
     }
     sm_phys[tid] = phys;
-    sm_ntok[tid] = phys < 0 ? 0 : ntok;
+    sm_ntok[tid] = phys < 0 ? 0 : ntok;  // 0 tokens: every slot of the page scores -inf
   }
   __syncthreads();
 
@@ -933,16 +918,16 @@ estimate_int4_mma_group_kernel(const EstParams p) {
   const int my_pairs = (n_pairs > warp) ? (n_pairs - warp + kEstWarps - 1) / kEstWarps : 0;
 
   // Per-lane constants of the five 16-byte copies of a stage: chunk c = c5*32+lane of the pair,
-  // i.e. page c/80 and chunk r = c%80 of its slab (0..63 codes, 64..79 scale/min).
-  uint32_t src16[5], dst_off[5];
-  bool second[5];
+  // i.e. page c/80 and chunk r = c%80 of its slab (0..63 codes, 64..79 scale/min).  Which page a
+  // copy belongs to is fixed for four of the five (chunks 0..63 first page, 96..159 second) and
+  // depends on the lane only for the third.
+  uint32_t src_off[5], dst_off[5];
 #pragma unroll
   for (int c5 = 0; c5 < 5; ++c5) {
     const int c = c5 * 32 + lane;
     const int pgl = c >= 80 ? 1 : 0;
     const int r = c - pgl * 80;
-    second[c5] = pgl != 0;
-    src16[c5] = r;
+    src_off[c5] = r * 16;
     if (r < 64) {
       const int tk = pgl * 16 + (r >> 2), g4 = r & 3;
       dst_off[c5] = tk * 64 + (((g4 + (tk >> 1)) & 3) << 4);
@@ -950,20 +935,24 @@ estimate_int4_mma_group_kernel(const EstParams p) {
       dst_off[c5] = 2048 + (pgl * 16 + (r - 64)) * 16;
     }
   }
-  const uint4* const k4_head16 = reinterpret_cast<const uint4*>(p.k4 + (size_t)kvh * kSlab);
-  const uint32_t page_stride16 = (uint32_t)(p.Hkv * (kSlab / 16));
+  const bool third_is_second = lane >= 16;
+  const uint8_t* const k4_head = p.k4 + (size_t)kvh * kSlab;
+  const size_t page_stride = (size_t)p.Hkv * kSlab;
 
+  // Absent pages (table entry out of range, partner of an odd last page) copy the slab of physical
+  // page 0, which is always mapped; their scores are never used.
   auto issue = [&](int i, int slot) {
     if (i < my_pairs) {
       const int pg0 = (warp + i * kEstWarps) * 2;
       const uint32_t dst0 = ring_u32 + slot * kWarpStageBytes;
-      const int phys0 = sm_phys[pg0], phys1 = sm_phys[pg0 + 1];  // missing pages hold -1
-#pragma unroll
-      for (int c5 = 0; c5 < 5; ++c5) {
-        const int phys = second[c5] ? phys1 : phys0;
-        if (phys >= 0)
-          cp_async16(dst0 + dst_off[c5], k4_head16 + ((size_t)phys * page_stride16 + src16[c5]));
-      }
+      const uint8_t* const s0 = k4_head + (size_t)max(sm_phys[pg0], 0) * page_stride;
+      const uint8_t* const s1 = k4_head + (size_t)max(sm_phys[pg0 + 1], 0) * page_stride;
+      const uint8_t* const s2 = third_is_second ? s1 : s0;
+      cp_async16(dst0 + dst_off[0], s0 + src_off[0]);
+      cp_async16(dst0 + dst_off[1], s0 + src_off[1]);
+      cp_async16(dst0 + dst_off[2], s2 + src_off[2]);
+      cp_async16(dst0 + dst_off[3], s1 + src_off[3]);
+      cp_async16(dst0 + dst_off[4], s1 + src_off[4]);
     }
     cp_async_commit();  // always commit so that group counting stays uniform
   };
@@ -975,20 +964,41 @@ estimate_int4_mma_group_kernel(const EstParams p) {
   // and the channel sums of heads 2t and 2t+1, whose scores this lane ends up owning
   uint32_t bq[4][4];
   float qs0[4], qs1[4];
+  float out_scale;
   {
     const T* qrow = reinterpret_cast<const T*>(p.q) + (size_t)(b * p.Hq + h + (gq < G ? gq : 0)) * kD;
+    float qf[4][8];
+    float amax = 0.f;
 #pragma unroll
     for (int grp = 0; grp < 4; ++grp) {
-      uint4 v = __ldg(reinterpret_cast<const uint4*>(qrow) + 4 * grp + t);
-      if (gq >= G) v = make_uint4(0u, 0u, 0u, 0u);
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(qrow) + 4 * grp + t);
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = Elem<T>::to_f2(u[k]);
+        qf[grp][2 * k] = gq < G ? f.x : 0.f;
+        qf[grp][2 * k + 1] = gq < G ? f.y : 0.f;
+        amax = fmaxf(amax, fmaxf(fabsf(qf[grp][2 * k]), fabsf(qf[grp][2 * k + 1])));
+      }
+    }
+    amax = warp_max(amax);  // over every head and channel of the group
+    int e = (amax > 0.f && amax < INFINITY) ? (7 - ilogbf(amax)) : 0;  // amax * 2^e in [128, 256)
+    e = max(-100, min(100, e));
+    const float up = ldexpf(1.f, e);
+    out_scale = p.sm_scale * ldexpf(1.f, -e);
+#pragma unroll
+    for (int grp = 0; grp < 4; ++grp) {
+      float sum = 0.f;
+      __half hq[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        hq[k] = __float2half_rn(qf[grp][k] * up);
+        sum += __half2float(hq[k]);  // the sum of what the tiles multiply with
+      }
       // elements e0..e7 = channels 8t..8t+7; the tiles want the pairs (e0,e4) (e1,e5) (e2,e6) (e3,e7)
-      bq[grp][0] = __byte_perm(v.x, v.z, 0x5410);
-      bq[grp][1] = __byte_perm(v.x, v.z, 0x7632);
-      bq[grp][2] = __byte_perm(v.y, v.w, 0x5410);
-      bq[grp][3] = __byte_perm(v.y, v.w, 0x7632);
-      const float2 f0 = Elem<T>::to_f2(v.x), f1 = Elem<T>::to_f2(v.y), f2 = Elem<T>::to_f2(v.z),
-                   f3 = Elem<T>::to_f2(v.w);
-      float sum = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        bq[grp][k] = (uint32_t)__half_as_ushort(hq[k]) | ((uint32_t)__half_as_ushort(hq[k + 4]) << 16);
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);  // sum of q over the group's 32 channels, head gq
       qs0[grp] = __shfl_sync(0xffffffffu, sum, (2 * t) * 4);
@@ -996,38 +1006,39 @@ estimate_int4_mma_group_kernel(const EstParams p) {
     }
   }
 
-  float* const out_row = p.scores + (size_t)(b * p.Hq + h + 2 * t) * p.stride + (size_t)first * kPage;
-  constexpr float kOff = CodePairs<T>::kOffset;
-  int use_slot = 0, fill_slot = kRingDepth - 1;
+  // byte offsets, inside a stage, of this lane's code word of token gq for each quantisation group
+  // (tokens gq+8, 16+gq, 24+gq follow at +512, +1024, +1536: the rotation repeats every eight tokens)
+  uint32_t code_off[4];
+#pragma unroll
+  for (int grp = 0; grp < 4; ++grp) code_off[grp] = gq * 64 + (((grp + (gq >> 1)) & 3) << 4) + t * 4;
+  const uint32_t sz_off = 2048 + gq * 16;  // {scale, min} x 4 groups of token gq; +128 per eight tokens
+
+  float* const out0 = p.scores + (size_t)(b * p.Hq + h + 2 * t) * p.stride + (size_t)first * kPage + gq;
+  const bool own0 = 2 * t < G, own1 = 2 * t + 1 < G;
+  const uint8_t* stage = ring;
+  int fill_slot = kRingDepth - 1;
   for (int i = 0; i < my_pairs; ++i) {
     cp_async_wait<kRingDepth - 2>();  // pair i has landed (this thread's copies)
     __syncwarp();                     // ... and every other lane's
-    const int pg0 = (warp + i * kEstWarps) * 2;
-    const uint8_t* stage = ring + use_slot * kWarpStageBytes;
     float res[2][4];
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt) {  // one page = one m16 tile
-      const int ta = mt * 16 + gq, tb = ta + 8;
-      const uint4 sza = *reinterpret_cast<const uint4*>(stage + 2048 + ta * 16);
-      const uint4 szb = *reinterpret_cast<const uint4*>(stage + 2048 + tb * 16);
+      const uint4 sza = *reinterpret_cast<const uint4*>(stage + sz_off + mt * 256);
+      const uint4 szb = *reinterpret_cast<const uint4*>(stage + sz_off + mt * 256 + 128);
       const uint32_t sa[4] = {sza.x, sza.y, sza.z, sza.w}, sb[4] = {szb.x, szb.y, szb.z, szb.w};
       float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
       for (int grp = 0; grp < 4; ++grp) {
-        const uint32_t wa = *reinterpret_cast<const uint32_t*>(stage + ta * 64 + (((grp + (ta >> 1)) & 3) << 4) + t * 4);
-        const uint32_t wb = *reinterpret_cast<const uint32_t*>(stage + tb * 64 + (((grp + (tb >> 1)) & 3) << 4) + t * 4);
+        const uint32_t wa = *reinterpret_cast<const uint32_t*>(stage + code_off[grp] + mt * 1024);
+        const uint32_t wb = *reinterpret_cast<const uint32_t*>(stage + code_off[grp] + mt * 1024 + 512);
         uint32_t ca[4], cb[4];
-        CodePairs<T>::unpack(wa, ca);
-        CodePairs<T>::unpack(wb, cb);
+        unpack_codes_f16(wa, ca);
+        unpack_codes_f16(wb, cb);
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        MmaTile<T>::run(acc, ca[0], cb[0], ca[1], cb[1], bq[grp][0], bq[grp][1]);
-        MmaTile<T>::run(acc, ca[2], cb[2], ca[3], cb[3], bq[grp][2], bq[grp][3]);
-        float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&sa[grp]));  // {scale, min}
-        float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&sb[grp]));
-        if (kOff != 0.f) {
-          fa.y = fmaf(-kOff, fa.x, fa.y);
-          fb.y = fmaf(-kOff, fb.x, fb.y);
-        }
+        MmaTile<__half>::run(acc, ca[0], cb[0], ca[1], cb[1], bq[grp][0], bq[grp][1]);
+        MmaTile<__half>::run(acc, ca[2], cb[2], ca[3], cb[3], bq[grp][2], bq[grp][3]);
+        const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&sa[grp]));  // {scale, min}
+        const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&sb[grp]));
         r0 = fmaf(fa.x, acc[0], fmaf(fa.y, qs0[grp], r0));
         r1 = fmaf(fa.x, acc[1], fmaf(fa.y, qs1[grp], r1));
         r2 = fmaf(fb.x, acc[2], fmaf(fb.y, qs0[grp], r2));
@@ -1037,21 +1048,21 @@ estimate_int4_mma_group_kernel(const EstParams p) {
     }
     __syncwarp();      // all lanes are done reading the slot that the next issue overwrites
     issue(i + kRingDepth - 1, fill_slot);
-    use_slot = (use_slot + 1 == kRingDepth) ? 0 : use_slot + 1;
     fill_slot = (fill_slot + 1 == kRingDepth) ? 0 : fill_slot + 1;
-    if (2 * t < G) {
+    stage = (stage + kWarpStageBytes == ring + kRingDepth * kWarpStageBytes) ? ring : stage + kWarpStageBytes;
+    const int pg0 = (warp + i * kEstWarps) * 2;
+    if (own0) {
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
         const int pg = pg0 + mt;
         if (pg < n_here) {
           const int ntok = sm_ntok[pg];  // 0 for a page whose table entry was out of range
-          float* o0 = out_row + pg * kPage;
-          float* o1 = o0 + p.stride;
-          o0[gq] = gq < ntok ? res[mt][0] * p.sm_scale : -INFINITY;
-          o0[gq + 8] = gq + 8 < ntok ? res[mt][2] * p.sm_scale : -INFINITY;
-          if (2 * t + 1 < G) {
-            o1[gq] = gq < ntok ? res[mt][1] * p.sm_scale : -INFINITY;
-            o1[gq + 8] = gq + 8 < ntok ? res[mt][3] * p.sm_scale : -INFINITY;
+          float* const o0 = out0 + pg * kPage;
+          o0[0] = gq < ntok ? res[mt][0] * out_scale : -INFINITY;
+          o0[8] = gq + 8 < ntok ? res[mt][2] * out_scale : -INFINITY;
+          if (own1) {
+            o0[p.stride] = gq < ntok ? res[mt][1] * out_scale : -INFINITY;
+            o0[p.stride + 8] = gq + 8 < ntok ? res[mt][3] * out_scale : -INFINITY;
           }
         }
       }

@@ -289,16 +289,19 @@ quest_page_scores_kernel(const ScoreParams p) {
 // straight into the A fragments of sixteen m16n8k16 tiles (two per piece) (the channel-to-slot assignment this
 // gives is applied to B as well), accumulates in fp32 and owns the scores of pages g, g+8 for
 // heads 2t, 2t+1.  With four heads the upper four columns of B are zero.
-template <typename T, int G>
-__global__ void __launch_bounds__(kSelThreads, 3)
+// NW warps per block, PPB pages per block: a warp should stream many steps per block it belongs
+// to, because a block's set-up (page table look-ups, a barrier) moves no metadata.
+template <typename T, int G, int NW, int PPB, bool PIPE>
+__global__ void __launch_bounds__(NW * 32, (PIPE ? 256 : 768) / (NW * 32))
 quest_page_scores_mma_kernel(const ScoreParams p) {
   static_assert(G == 4 || G == 8, "one n8 tile holds the group");
+  constexpr int kThreads = NW * 32;
   const int row = blockIdx.x;  // (b, kv head), kv head fastest
   const int b = row / p.Hkv, kvh = row % p.Hkv;
   pdl_wait();  // q and the page table may come from the kernel launched just before
   const int page_base = p.indptr[b];
   const int n_pages = min(p.indptr[b + 1] - page_base, p.max_pages);
-  const int first = blockIdx.y * kSelPagesPerBlock;
+  const int first = blockIdx.y * PPB;
   if (first >= n_pages) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -325,9 +328,9 @@ quest_page_scores_mma_kernel(const ScoreParams p) {
     }
   }
 
-  __shared__ int sm_phys[kSelPagesPerBlock];
-  const int n_here = min(kSelPagesPerBlock, n_pages - first);
-  for (int i = threadIdx.x; i < kSelPagesPerBlock; i += kSelThreads) {
+  __shared__ int sm_phys[PPB];
+  const int n_here = min(PPB, n_pages - first);
+  for (int i = threadIdx.x; i < PPB; i += kThreads) {
     int phys = -1;
     if (i < n_here) {
       phys = p.indices[page_base + first + i];
@@ -342,35 +345,63 @@ quest_page_scores_mma_kernel(const ScoreParams p) {
 
   const uint4* const meta16 = reinterpret_cast<const uint4*>(p.kmeta);
   const size_t slab16 = 2 * kD * sizeof(T) / 16;  // 32 pieces per (page, kv-head) slab
-  for (int l0 = warp * 16; l0 < n_here; l0 += (kSelThreads / 32) * 16) {
-    const int la = l0 + g, lb = l0 + g + 8;
-    const int pa = la < n_here ? sm_phys[la] : -1, pb = lb < n_here ? sm_phys[lb] : -1;
-    // absent pages read the slab of physical page 0 (always mapped); their scores are not used
-    const uint4* sa = meta16 + ((size_t)max(pa, 0) * p.Hkv + kvh) * slab16 + t;
-    const uint4* sb = meta16 + ((size_t)max(pb, 0) * p.Hkv + kvh) * slab16 + t;
+  struct Step {
     uint4 va[8], vb[8];
+    int pa, pb;
+  };
+  auto load_step = [&](Step& s, int l0) {
+    const int la = l0 + g, lb = l0 + g + 8;
+    s.pa = la < n_here ? sm_phys[la] : -1;
+    s.pb = lb < n_here ? sm_phys[lb] : -1;
+    // absent pages read the slab of physical page 0 (always mapped); their scores are not used
+    const uint4* sa = meta16 + ((size_t)max(s.pa, 0) * p.Hkv + kvh) * slab16 + t;
+    const uint4* sb = meta16 + ((size_t)max(s.pb, 0) * p.Hkv + kvh) * slab16 + t;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
-      va[c] = ldg_stream_u4(sa + 4 * c);
-      vb[c] = ldg_stream_u4(sb + 4 * c);
+      s.va[c] = ldg_stream_u4(sa + 4 * c);
+      s.vb[c] = ldg_stream_u4(sb + 4 * c);
     }
+  };
+  auto finish_step = [&](const Step& s, int l0) {
+    const int la = l0 + g, lb = l0 + g + 8;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
-      MmaTile<T>::run(acc, va[c].x, vb[c].x, va[c].y, vb[c].y, bq[c][0], bq[c][1]);
-      MmaTile<T>::run(acc, va[c].z, vb[c].z, va[c].w, vb[c].w, bq[c][2], bq[c][3]);
+      MmaTile<T>::run(acc, s.va[c].x, s.vb[c].x, s.va[c].y, s.vb[c].y, bq[c][0], bq[c][1]);
+      MmaTile<T>::run(acc, s.va[c].z, s.vb[c].z, s.va[c].w, s.vb[c].w, bq[c][2], bq[c][3]);
     }
     if (2 * t < G) {
       float* const o0 = p.page_scores + (size_t)(b * p.Hq + h0 + 2 * t) * p.max_pages + first;
       float* const o1 = o0 + p.max_pages;
       if (la < n_here) {
-        o0[la] = pa >= 0 ? acc[0] : -INFINITY;
-        o1[la] = pa >= 0 ? acc[1] : -INFINITY;
+        o0[la] = s.pa >= 0 ? acc[0] : -INFINITY;
+        o1[la] = s.pa >= 0 ? acc[1] : -INFINITY;
       }
       if (lb < n_here) {
-        o0[lb] = pb >= 0 ? acc[2] : -INFINITY;
-        o1[lb] = pb >= 0 ? acc[3] : -INFINITY;
+        o0[lb] = s.pb >= 0 ? acc[2] : -INFINITY;
+        o1[lb] = s.pb >= 0 ? acc[3] : -INFINITY;
       }
+    }
+  };
+  constexpr int kStride = NW * 16;
+  if constexpr (PIPE) {
+    // two register sets: the loads of the next step are in flight while this one is multiplied
+    Step s0, s1;
+    int l0 = warp * 16;
+    if (l0 < n_here) load_step(s0, l0);
+    while (l0 < n_here) {
+      const int l1 = l0 + kStride, l2 = l1 + kStride;
+      if (l1 < n_here) load_step(s1, l1);
+      finish_step(s0, l0);
+      if (l2 < n_here) load_step(s0, l2);
+      if (l1 < n_here) finish_step(s1, l1);
+      l0 = l2;
+    }
+  } else {
+    for (int l0 = warp * 16; l0 < n_here; l0 += kStride) {
+      Step s0;
+      load_step(s0, l0);
+      finish_step(s0, l0);
     }
   }
 }
@@ -518,14 +549,37 @@ static int launch_scores(const ScoreParams& p, cudaStream_t st) {
   return TWL_OK;
 }
 
-template <typename T, int G>
-static int launch_scores_mma(const ScoreParams& p, cudaStream_t st) {
+template <typename T, int G, int NW, int PPB, bool PIPE>
+static int launch_scores_mma_shape(const ScoreParams& p, cudaStream_t st) {
   const int rows = p.B * p.Hkv;
-  const int chunks = (p.max_pages + kSelPagesPerBlock - 1) / kSelPagesPerBlock;
+  const int chunks = (p.max_pages + PPB - 1) / PPB;
   if (chunks > 65535) return TWL_ERR_TOO_LARGE;
-  TWL_CUDA_TRY(launch_chain(quest_page_scores_mma_kernel<T, G>, dim3(rows, chunks), dim3(kSelThreads), 0, st, p));
+  TWL_CUDA_TRY(launch_chain(quest_page_scores_mma_kernel<T, G, NW, PPB, PIPE>, dim3(rows, chunks), dim3(NW * 32), 0, st, p));
   TWL_CHECK_LAUNCH();
   return TWL_OK;
+}
+
+template <typename T, int G>
+static int launch_scores_mma(const ScoreParams& p, cudaStream_t st) {
+  // Two warps per block, each with two steps (2 x 8 KiB) of loads in flight.  Measured on one KV
+  // head x 128 sequences x 4096 pages (268 MB, pages scattered): 57 us against 58 (8 warps x 256
+  // pages, one step in flight) and 66 (2 warps x 256 pages, one step in flight).  Pages per block:
+  // as many as still leave every SM four blocks, so that small problems spread out.
+  // TWL_SCORES_MMA_SHAPE picks a shape by hand (for measurement).
+  static const int forced = [] {
+    const char* e = getenv("TWL_SCORES_MMA_SHAPE");
+    return e ? atoi(e) : 0;
+  }();
+  switch (forced) {
+    case 1: return launch_scores_mma_shape<T, G, 8, 256, false>(p, st);
+    case 2: return launch_scores_mma_shape<T, G, 2, 256, false>(p, st);
+    case 3: return launch_scores_mma_shape<T, G, 4, 512, true>(p, st);
+    default: break;
+  }
+  const long rows = (long)p.B * p.Hkv, want = 4L * num_sms();
+  if (rows * ((p.max_pages + 511) / 512) >= want) return launch_scores_mma_shape<T, G, 2, 512, true>(p, st);
+  if (rows * ((p.max_pages + 255) / 256) >= want) return launch_scores_mma_shape<T, G, 2, 256, true>(p, st);
+  return launch_scores_mma_shape<T, G, 2, 128, true>(p, st);
 }
 
 template <typename T>

@@ -26,6 +26,9 @@ constexpr float kSearchEps = 1e-5f;
 constexpr int kRowCap = 56 * 1024;
 // rows of the fused pruner also need a working list of a quarter of the row (6 bytes an entry)
 constexpr int kPruneRowCap = 40 * 1024;
+// elements of a row that one warp searches on its own (see topp_search_solo)
+constexpr int kSoloCap = 1024;
+constexpr int kPruneHeaderWords = 352 + kSoloCap;  // reduction scratch, scan scratch, short list
 
 template <typename T>
 struct Prec;  // rounding of the search scalars to the probability type, as the reference does
@@ -107,6 +110,94 @@ __device__ float topp_search(F load, int n, float x0, float p_in, float* red, in
   return low;
 }
 
+// The search for fp16 / bf16 probabilities, reproducing the reference's arithmetic for that type
+// (TopPReturnMaskKernel<..., DType = half or bfloat16>, csrc/include/sampling.cuh:156-217): p, eps,
+// low, high, mid and the stop width live in the type, and so does the mass above the pivot, which
+// the reference adds with a 1024-thread block reduction per chunk of 1024*VEC elements (VEC =
+// gcd(8, d)): every thread adds its VEC consecutive items (two-wide: the items at even and at odd
+// positions in order, side by side, then the two sums; in order when there are fewer than four),
+// every warp combines its lanes with a shuffle-down tree (offsets 1, 2, 4, 8, 16), thread 0 adds
+// the 32 warp totals in order, and the chunk totals are accumulated in order - each addition
+// rounded to the type.  That is the order the block reduction of the CUDA 12.9 toolkit's CUB
+// produces for 16-bit floats; it is used here too, so the masks are those of the reference's kernel
+// built with that toolkit, bit for bit (checked against it on a GPU).  Needs THREADS == 1024.
+// red: 192 floats of shared scratch.
+template <int THREADS, typename PT, typename F>
+__device__ float topp_search_lowp(F load, int d, float x0, float p_in, float* red, int32_t* status) {
+  static_assert(THREADS == 1024, "the order of the additions is that of a 1024-thread block");
+  const int tx = threadIdx.x, lane = tx & 31, warp = tx >> 5;
+  const int vec = (d & 7) == 0 ? 8 : ((d & 3) == 0 ? 4 : ((d & 1) == 0 ? 2 : 1));  // gcd(16 / sizeof, d)
+  const int n_chunks = (d + THREADS * vec - 1) / (THREADS * vec);
+  float* const wtot = red + 96;  // 32 warp totals, then the running total
+  const float p = Prec<PT>::rnd(p_in);
+  const float eps = Prec<PT>::rnd(kSearchEps);
+  float low = 0.f, high = x0;
+  int round = 0;
+  while (true) {
+    const float mid = Prec<PT>::rnd(Prec<PT>::rnd(low + high) * 0.5f);
+    float a = high, b = low;
+    float total = 0.f;  // meaningful in thread 0
+    for (int c = 0; c < n_chunks; ++c) {
+      const int base = (c * THREADS + tx) * vec;
+      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (base < d) {  // d is a multiple of vec: whole groups
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (j < vec) {
+            const float x = load(base + j);
+            a = (x > low) ? fminf(a, x) : a;
+            b = (x <= high) ? fmaxf(b, x) : b;
+            v[j] = (x > mid) ? x : 0.f;
+          }
+        }
+      }
+      // a thread's items: even and odd positions are added up side by side (two-wide additions),
+      // then the two sums are added; with fewer than four items, in order
+      float ts;
+      if (vec == 8) {
+        const float ev = Prec<PT>::rnd(Prec<PT>::rnd(Prec<PT>::rnd(v[0] + v[2]) + v[4]) + v[6]);
+        const float od = Prec<PT>::rnd(Prec<PT>::rnd(Prec<PT>::rnd(v[1] + v[3]) + v[5]) + v[7]);
+        ts = Prec<PT>::rnd(ev + od);
+      } else if (vec == 4) {
+        ts = Prec<PT>::rnd(Prec<PT>::rnd(v[0] + v[2]) + Prec<PT>::rnd(v[1] + v[3]));
+      } else if (vec == 2) {
+        ts = Prec<PT>::rnd(v[0] + v[1]);
+      } else {
+        ts = v[0];
+      }
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float other = __shfl_down_sync(0xffffffffu, ts, o);
+        if (lane + o < 32) ts = Prec<PT>::rnd(ts + other);
+      }
+      if (lane == 0) wtot[warp] = ts;
+      __syncthreads();
+      if (tx == 0) {
+        float agg = wtot[0];
+        for (int w = 1; w < THREADS / 32; ++w) agg = Prec<PT>::rnd(agg + wtot[w]);
+        total = Prec<PT>::rnd(total + agg);
+      }
+      __syncthreads();  // the warp totals are rewritten by the next chunk
+    }
+    if (tx == 0) wtot[32] = total;
+    const Red3 r = block_red3<THREADS>(0.f, a, b, red);  // its barrier also publishes the total
+    const float s = wtot[32];
+    if (s >= p) {
+      low = mid;
+    } else {
+      high = fminf(mid, r.b);
+    }
+    ++round;
+    __syncthreads();  // everybody has read the reductions before the next round overwrites them
+    if (!(Prec<PT>::rnd(r.b - r.a) > eps)) break;
+    if (round >= kSearchRoundCap) {
+      if (tx == 0) raise_flag(status, TWL_FLAG_ITER_CAP);
+      break;
+    }
+  }
+  return low;
+}
+
 // Warp-wide inclusive prefix sum of one int per lane.
 __device__ __forceinline__ int warp_incl_scan(int v) {
   const int lane = threadIdx.x & 31;
@@ -170,13 +261,13 @@ struct SearchResult {
 // the search goes on over the old set.  Ordering inside a segment is fixed by lane order, so
 // results do not depend on scheduling.
 //
-// The caller has already made the first round's pass (mid = x0/2) while it produced the row:
-// `first` holds its three reductions and `first_cnt` the number of elements above x0/2 that
-// this warp wrote (or would have written, had they fitted) to its segment.
+// The search starts from the state (low, high, round) the caller hands over (0, x0, 0 for a fresh
+// search; the state at which the short-list search below gave up otherwise), with the whole row as
+// the working set.
 //   x: n floats (n % 4 == 0); red: 256 words; p, eps in the units of x.
 template <int THREADS>
-__device__ SearchResult topp_search_narrowing(const float* x, int n, SearchList L, int* seg_cnt, float x0,
-                                              float p, float eps, Red3 first, int first_cnt, float* red,
+__device__ SearchResult topp_search_narrowing(const float* x, int n, SearchList L, int* seg_cnt, float low,
+                                              float high, int round, float p, float eps, float* red,
                                               int32_t* status) {
   constexpr int NW = THREADS / 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -190,37 +281,31 @@ __device__ SearchResult topp_search_narrowing(const float* x, int n, SearchList 
   bool in_list = false;
   int my_cnt = 0;    // elements in this warp's segment (valid when in_list)
   int total = n;     // size of the working set
-  float low = 0.f, high = x0;
-  int round = 0;
+  int flip = 0;      // the two reduction buffers alternate
   while (true) {
     const float mid = (low + high) * 0.5f;
-    Red3 r;
-    if (round == 0) {
-      r = first;
-    } else {
-      float s = 0.f, a = high, b = low;
-      if (!in_list) {
-        for (int i = threadIdx.x; i < n4; i += THREADS) {
-          const float4 v = x4[i];
-          const float e[4] = {v.x, v.y, v.z, v.w};
+    float s = 0.f, a = high, b = low;
+    if (!in_list) {
+      for (int i = threadIdx.x; i < n4; i += THREADS) {
+        const float4 v = x4[i];
+        const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            s += (e[k] > mid) ? e[k] : 0.f;
-            a = (e[k] > low) ? fminf(a, e[k]) : a;
-            b = (e[k] <= high) ? fmaxf(b, e[k]) : b;
-          }
-        }
-      } else {
-        for (int i = lane; i < my_cnt; i += 32) {
-          const float e = my_val[i];
-          s += (e > mid) ? e : 0.f;
-          a = (e > low) ? fminf(a, e) : a;
-          b = (e <= high) ? fmaxf(b, e) : b;
+        for (int k = 0; k < 4; ++k) {
+          s += (e[k] > mid) ? e[k] : 0.f;
+          a = (e[k] > low) ? fminf(a, e[k]) : a;
+          b = (e[k] <= high) ? fmaxf(b, e[k]) : b;
         }
       }
-      // never the buffer of the reduction before: the caller's last one used red + 96
-      r = block_red3<THREADS>(s, a, b, red + ((round + 1) & 1) * 96);
+    } else {
+      for (int i = lane; i < my_cnt; i += 32) {
+        const float e = my_val[i];
+        s += (e > mid) ? e : 0.f;
+        a = (e > low) ? fminf(a, e) : a;
+        b = (e <= high) ? fmaxf(b, e) : b;
+      }
     }
+    const Red3 r = block_red3<THREADS>(s, a, b, red + flip * 96);
+    flip ^= 1;
     bool rose = false;
     if (r.s >= p) {
       low = mid;
@@ -236,9 +321,7 @@ __device__ SearchResult topp_search_narrowing(const float* x, int n, SearchList 
     }
     if (rose && total > 32) {
       int cnt = 0;
-      if (round == 1) {
-        cnt = first_cnt;  // collected by the caller against the same mid
-      } else if (!in_list) {
+      if (!in_list) {
         const int begin = warp * slice, end = min(n, begin + slice);
         for (int i0 = begin; i0 < end; i0 += 128) {
           const int i = i0 + lane * 4;
@@ -304,6 +387,65 @@ __device__ SearchResult topp_search_narrowing(const float* x, int n, SearchList 
   return res;
 }
 
+// The search on a short list, run by ONE warp without any block-wide barrier.
+//
+// While the row is turned into exponentials, every element above cut = x0 / 256 is collected.  As
+// long as low is 0 and the pivot stays at or above the cut, and for good once low has risen to a
+// pivot >= cut, a round needs nothing else from the row: S sums elements above the pivot; the
+// smallest element above low is the row's smallest positive element (low = 0) or a listed one; the
+// largest element not above high is a listed one, or the largest unlisted element `b_rest` while
+// low is 0 (afterwards unlisted elements lie below low and cannot win).  Rows whose mass sits in a
+// few hundred tokens - the case the pruner exists for - are searched entirely here, at a fraction
+// of a microsecond per round instead of a block-wide pass.  When the pivot would drop below the
+// cut with low still 0 the warp stops and hands its state (low = 0, high, round) to the block.
+// Returns true when the search is finished.  solo: n_solo values; lane-strided sums, fixed order.
+struct SoloState {
+  float low, high;
+  int round, done;
+};
+__device__ __forceinline__ SoloState topp_search_solo(const float* solo, int n_solo, float x0, float cut,
+                                                      float a_pos, float b_rest, float p, float eps,
+                                                      int32_t* status) {
+  const int lane = threadIdx.x & 31;
+  SoloState st;
+  st.low = 0.f; st.high = x0; st.round = 0; st.done = 0;
+  while (true) {
+    const float low = st.low, high = st.high;
+    const float mid = (low + high) * 0.5f;
+    if (low == 0.f && mid < cut) break;  // the block takes over from this state
+    float s = 0.f, a = high, b = low;
+    for (int i = lane; i < n_solo; i += 32) {
+      const float e = solo[i];
+      s += (e > mid) ? e : 0.f;
+      a = (e > low) ? fminf(a, e) : a;
+      b = (e <= high) ? fmaxf(b, e) : b;
+    }
+    s = warp_sum(s);
+    a = warp_min(a);
+    b = warp_max(b);
+    if (low == 0.f) {
+      a = fminf(a, a_pos);   // smallest positive element of the whole row (a_pos <= high always)
+      b = fmaxf(b, b_rest);  // largest unlisted element: b_rest <= cut <= mid < high
+    }
+    if (s >= p) {
+      st.low = mid;
+    } else {
+      st.high = fminf(mid, b);
+    }
+    ++st.round;
+    if (!(b - a > eps)) {
+      st.done = 1;
+      break;
+    }
+    if (st.round >= kSearchRoundCap) {
+      if (lane == 0) raise_flag(status, TWL_FLAG_ITER_CAP);
+      st.done = 1;
+      break;
+    }
+  }
+  return st;
+}
+
 // ---- dense mask form ------------------------------------------------------------------------
 template <int THREADS, typename T, bool IN_SMEM>
 __global__ void __launch_bounds__(THREADS)
@@ -322,7 +464,13 @@ top_p_mask_kernel(const T* __restrict__ probs, uint8_t* __restrict__ mask,
   }
   const float x0 = IN_SMEM ? row[0] : Prec<T>::load(src, 0);
   float low;
-  if (IN_SMEM) {
+  if constexpr (sizeof(T) == 2) {
+    if (IN_SMEM) {
+      low = topp_search_lowp<THREADS, T>([&](int i) { return row[i]; }, (int)d, x0, p, red, status);
+    } else {
+      low = topp_search_lowp<THREADS, T>([&](int i) { return Prec<T>::load(src, i); }, (int)d, x0, p, red, status);
+    }
+  } else if (IN_SMEM) {
     low = topp_search<THREADS, T>([&](int i) { return row[i]; }, (int)d, x0, p, red, status);
   } else {
     low = topp_search<THREADS, T>([&](int i) { return Prec<T>::load(src, i); }, (int)d, x0, p, red, status);
@@ -389,7 +537,8 @@ topp_prune_kernel(const PruneParams p) {
   constexpr int NW = THREADS / 32;
   float* red = smem;                                  // 256 words
   int* wsum = reinterpret_cast<int*>(smem + 256);     // 96 ints: 33 of scan scratch, 32 segment counts
-  float* row = smem + 352;                            // the row when IN_SMEM, then the working list
+  float* solo = smem + 352;                           // kSoloCap values: the short list one warp searches
+  float* row = smem + kPruneHeaderWords;              // the row when IN_SMEM, then the working list
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   pdl_release();  // the attention kernel's blocks may move in while this small grid works
   const int r = blockIdx.x;
@@ -463,13 +612,13 @@ topp_prune_kernel(const PruneParams p) {
     low = sink_present ? x0 - top_p : -INFINITY;
   } else if (IN_SMEM) {
     // pass 2: exponentials in place and their sum.  The search runs on the un-normalised values
-    // (p and the stop width scaled by the sum instead of every element divided by it), so this
-    // pass already is the search's first round: low = 0, high = x0, mid = x0/2 need only the
-    // maximum.  Elements above x0/2 - the working set if that round raises low - go to the list.
+    // (p and the stop width scaled by the sum instead of every element divided by it).  The same
+    // pass collects every element above x0/256 into the working list, with the smallest positive
+    // element and the largest element that was not collected: what the short-list search needs.
     x0 = sink_present ? fexp(row[0]) : 0.f;
     __syncthreads();  // row[0] is read by everyone before its owner overwrites it
-    const float mid1 = x0 * 0.5f;
-    float z = 0.f, s1 = 0.f, a1 = x0, b1 = 0.f;
+    const float cut = x0 * (1.f / 256.f);
+    float z = 0.f, a1 = x0, b1 = 0.f;
     int first_cnt = 0;
     float* const my_val = L.vals + warp * L.seg_cap;
     uint16_t* const my_rel = L.rel + warp * L.seg_cap;
@@ -484,17 +633,16 @@ topp_prune_kernel(const PruneParams p) {
       int c = 0;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        s1 += (e[k] > mid1) ? e[k] : 0.f;
         a1 = (e[k] > 0.f) ? fminf(a1, e[k]) : a1;
-        b1 = (e[k] <= x0) ? fmaxf(b1, e[k]) : b1;
-        c += e[k] > mid1 ? 1 : 0;
+        b1 = (e[k] <= cut) ? fmaxf(b1, e[k]) : b1;
+        c += e[k] > cut ? 1 : 0;
       }
       if (__ballot_sync(0xffffffffu, c > 0) == 0) continue;
       const int inc = warp_incl_scan(c);
       int pos = first_cnt + inc - c;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        if (e[k] > mid1) {
+        if (e[k] > cut) {
           if (pos < L.seg_cap) {
             my_val[pos] = e[k];
             my_rel[pos] = (uint16_t)(i - s_begin + k);
@@ -504,19 +652,60 @@ topp_prune_kernel(const PruneParams p) {
       }
       first_cnt += __shfl_sync(0xffffffffu, inc, 31);
     }
-    const Red4 r2 = block_red4<THREADS>(z, s1, a1, b1, red + 96);
+    const Red4 r2 = block_red4<THREADS>(z, 0.f, a1, b1, red + 96);  // sum, -, smallest positive, largest uncollected
     inv_z = 1.f / r2.z;
     if (top_p > 1.f) {
       low = 0.f;  // no pruning asked for: keep every candidate with non-zero probability
     } else {
-      Red3 first;
-      first.s = r2.s; first.a = r2.a; first.b = r2.b;
-      const SearchResult res = topp_search_narrowing<THREADS>(row, n, L, wsum + 40, x0, top_p * r2.z,
-                                                              kSearchEps * r2.z, first, first_cnt, red,
-                                                              p.status);
-      low = res.low;
-      from_list = res.in_list;
-      list_cnt = res.my_cnt;
+      const float p_z = top_p * r2.z, eps_z = kSearchEps * r2.z;
+      int* const seg_cnt = wsum + 40;
+      if (lane == 0) seg_cnt[warp] = first_cnt;
+      __syncthreads();
+      bool fits = true;
+      int total = 0, my_off = 0;
+#pragma unroll 1
+      for (int w = 0; w < NW; ++w) {
+        const int cw = seg_cnt[w];
+        fits = fits && (cw <= L.seg_cap);
+        my_off += w < warp ? cw : 0;
+        total += cw;
+      }
+      float lo0 = 0.f, hi0 = x0;
+      int round0 = 0;
+      bool done = false;
+      if (fits && total <= kSoloCap) {
+        // the collected elements side by side, then one warp runs the rounds on them alone
+        for (int i = lane; i < first_cnt; i += 32) solo[my_off + i] = my_val[i];
+        __syncthreads();
+        if (warp == 0) {
+          const SoloState st = topp_search_solo(solo, total, x0, cut, r2.a, r2.b, p_z, eps_z, p.status);
+          if (lane == 0) {
+            red[0] = st.low;
+            red[1] = st.high;
+            red[2] = __int_as_float(st.round);
+            red[3] = __int_as_float(st.done);
+          }
+        }
+        __syncthreads();
+        lo0 = red[0];
+        hi0 = red[1];
+        round0 = __float_as_int(red[2]);
+        done = __float_as_int(red[3]) != 0;
+      }
+      __syncthreads();  // seg_cnt and red are reused by the block-wide search
+      if (done) {
+        // every element above low (>= the collection cut, or 0 with everything positive collected)
+        // is in the list, each warp's segment in row order
+        low = lo0;
+        from_list = true;
+        list_cnt = first_cnt;
+      } else {
+        const SearchResult res = topp_search_narrowing<THREADS>(row, n, L, seg_cnt, lo0, hi0, round0, p_z, eps_z,
+                                                                red, p.status);
+        low = res.low;
+        from_list = res.in_list;
+        list_cnt = res.my_cnt;
+      }
     }
   } else {
     float z = 0.f;
@@ -645,13 +834,13 @@ static int launch_prune(const PruneParams& p, int rows, int n_max, cudaStream_t 
     PruneParams q = p;
     q.row_cap = (n_max + 3) & ~3;
     q.list_cap = std::max(q.row_cap / 4, 32 * (THREADS / 32));  // entries: a float and a uint16 each
-    const size_t smem = (((352 + (size_t)q.row_cap + q.list_cap) * sizeof(float) + (size_t)q.list_cap * 2) + 15) & ~(size_t)15;
+    const size_t smem = (((kPruneHeaderWords + (size_t)q.row_cap + q.list_cap) * sizeof(float) + (size_t)q.list_cap * 2) + 15) & ~(size_t)15;
     auto kern = topp_prune_kernel<THREADS, true>;
     TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     TWL_CUDA_TRY(launch_chain(kern, dim3(rows), dim3(THREADS), smem, st, static_cast<const PruneParams&>(q)));
   } else {
     auto kern = topp_prune_kernel<THREADS, false>;
-    TWL_CUDA_TRY(launch_chain(kern, dim3(rows), dim3(THREADS), 352 * sizeof(float), st, p));
+    TWL_CUDA_TRY(launch_chain(kern, dim3(rows), dim3(THREADS), kPruneHeaderWords * sizeof(float), st, p));
   }
   TWL_CHECK_LAUNCH();
   return TWL_OK;

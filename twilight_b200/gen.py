@@ -96,3 +96,53 @@ def ragged_lengths(batch: int, lo: int, hi: int, seed: int = 0) -> List[int]:
     """``batch`` context lengths uniform in ``[lo, hi]``."""
     g = torch.Generator().manual_seed(seed)
     return torch.randint(lo, hi + 1, (batch,), generator=g).tolist()
+
+
+def make_unit_inputs(batch_ids: Sequence[int], kv_head_ids: Sequence[int], group: int,
+                     seq_lens: Sequence[int], *, rho: Union[float, Tuple[float, float]] = 0.01,
+                     dtype: torch.dtype = torch.bfloat16, device="cuda", seed: int = 0, recipe: str = "literal",
+                     heavy_logit: float = 10.0, sink_logit: float = 12.0, shuffle_pages: bool = False
+                     ) -> Tuple[torch.Tensor, PagedKVCache]:
+    """The same kind of inputs for a rectangular block of (sequence, KV head) units of a larger
+    problem, every unit generated from its own seed ``(seed, global sequence id, global KV head
+    id)``: whichever rank owns a unit produces the same q, K and V for it, so any rank can rebuild
+    a unit of another one to check a gathered result.  ``seq_lens`` holds the lengths of the
+    sequences in ``batch_ids`` (in that order); ``group`` = query heads per KV head.
+    Returns ``(q [B_local, H_kv_local*group, 128], cache)`` for the block."""
+    dev = torch.device(device)
+    lens = [int(x) for x in seq_lens]
+    nb, nh = len(batch_ids), len(kv_head_ids)
+    assert len(lens) == nb
+    indptr, indices, last, total = PagedKVCache.page_table(lens, dev, seed + 1 if shuffle_pages else None)
+    q = torch.empty(nb, nh * group, HEAD_DIM, dtype=dtype, device=dev)
+    k_pages = torch.zeros(total, nh, PAGE, HEAD_DIM, dtype=dtype, device=dev)
+    v_pages = torch.zeros_like(k_pages)
+    idx_host, ptr_host = indices.cpu().long(), indptr.cpu().long()
+    for bi, b in enumerate(batch_ids):
+        n = lens[bi]
+        npg = (n + PAGE - 1) // PAGE
+        phys = idx_host[ptr_host[bi]: ptr_host[bi + 1]].to(dev)
+        for hi, h in enumerate(kv_head_ids):
+            gen = torch.Generator(device=dev).manual_seed((seed * 1000003 + int(b) * 4099 + int(h)) & 0x7FFFFFFF)
+            q32 = torch.randn(group, HEAD_DIM, generator=gen, device=dev)
+            k = torch.randn(npg * PAGE, HEAD_DIM, generator=gen, device=dev)
+            v = torch.randn(npg * PAGE, HEAD_DIM, generator=gen, device=dev)
+            qnorm = q32[0].norm()
+            c_h, c_s = _coeffs(recipe, qnorm.reshape(1), heavy_logit, sink_logit)
+            qhat = q32[0] / qnorm
+            r = rho[0] + (rho[1] - rho[0]) * float(torch.rand(1, generator=gen, device=dev)) \
+                if isinstance(rho, tuple) else rho
+            n_heavy = int(math.floor(r * n))
+            if n_heavy > 0:
+                pos = torch.randperm(n, generator=gen, device=dev)[:n_heavy]
+                noise = 0.1 * torch.randn(n_heavy, HEAD_DIM, generator=gen, device=dev)
+                k[pos] = c_h * qhat * math.sqrt(HEAD_DIM) + noise
+            k[0] = c_s * qhat * math.sqrt(HEAD_DIM)
+            k[n:] = 0
+            v[n:] = 0
+            q[bi, hi * group: (hi + 1) * group] = q32.to(dtype)
+            k_pages[phys, hi] = k.to(dtype).view(npg, PAGE, HEAD_DIM)
+            v_pages[phys, hi] = v.to(dtype).view(npg, PAGE, HEAD_DIM)
+    cache = PagedKVCache(k_pages, v_pages, None, None, indptr, indices, last, lens)
+    cache.build_aux()
+    return q, cache
