@@ -130,7 +130,9 @@ TWL_API int twl_quest_select(const void* q, int dtype, const void* kmeta, const 
  * variant: arithmetic 0 = library default (3), 1 = fp32 FMA, 2 = packed-half FMA (about 1e-2
  * off in the logit), 3 = integer dot product; add 16 for the kernel that uses direct 128-bit
  * global loads, add 128 for the block-wide bulk-copy (TMA) ring even when a row has a single
- * query head (by default such rows use warp-private 16-byte async copies), add 32 for the
+ * query head (by default such rows use warp-private 16-byte async copies), add 64 for warp-private
+ * rings fed by bulk copies (two 1280-byte cp.async.bulk per stage on the warp's own mbarrier: the
+ * default's block shape and bytes in flight, the copy engine instead of per-lane copies), add 32 for the
  * integer-dot kernel on query-head groups (by default groups of 2, 4 or 8 heads that share a KV
  * head's pages are scored with 16-bit tensor-core tiles: codes and q are exact in the model dtype,
  * accumulation is fp32).  The non-default variants exist for measurement. */

@@ -183,7 +183,7 @@ def test_quest_selector_mask_interface_matches_reference_fixture(golden):
 
 
 # ---- estimator -------------------------------------------------------------------------------------
-@pytest.mark.parametrize("variant,tol", [(1, 2e-4), (2, 6e-2), (3, 2e-3), (17, 2e-4), (19, 2e-3)])
+@pytest.mark.parametrize("variant,tol", [(1, 2e-4), (2, 6e-2), (3, 2e-3), (17, 2e-4), (19, 2e-3), (67, 2e-3)])
 @pytest.mark.parametrize("hq,hkv,dt", [(4, 4, torch.float16), (8, 2, torch.bfloat16), (8, 1, torch.bfloat16),
                                        (4, 2, torch.float16)])
 def test_estimator_full_context(variant, tol, hq, hkv, dt):
@@ -207,7 +207,7 @@ def test_estimator_full_context(variant, tol, hq, hkv, dt):
             assert np.abs(got[fin] - want[fin]).max() <= tol * scale, (variant, b, h)
 
 
-@pytest.mark.parametrize("variant,tol", [(1, 2e-4), (3, 2e-3), (19, 2e-3)])
+@pytest.mark.parametrize("variant,tol", [(1, 2e-4), (3, 2e-3), (19, 2e-3), (67, 2e-3)])
 def test_estimator_candidate_lists(variant, tol):
     lens = [300, 2000, 17]
     hq, hkv = 8, 2
@@ -227,6 +227,41 @@ def test_estimator_candidate_lists(variant, tol):
             assert np.array_equal(np.isinf(got), np.isinf(want))
             fin = np.isfinite(want)
             assert np.abs(got[fin] - want[fin]).max() <= tol * max(1.0, float(np.abs(want[fin]).max()))
+
+
+def test_estimator_bulk_copy_rings_equal_the_default():
+    """Variant +64 (warp-private rings fed by cp.async.bulk on per-warp mbarriers) moves the same
+    bytes as the default's 16-byte cp.async copies and does the same integer arithmetic per
+    (token, group); only the order in which the four groups' fp32 terms are added differs (a chain in
+    one lane against two shuffles across four lanes): scores equal to a few ulp, with and without
+    candidate lists, odd page counts included."""
+    lens = [16, 17, 33, 1000, 4097, 8000]
+    hq = hkv = 4
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=torch.bfloat16, device=DEV, seed=64,
+                                  recipe="mid", shuffle_pages=True)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kw = dict(max_pages=cache.max_pages, status=status)
+    a = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len, **kw)
+    b_ = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
+                           variant=3 + 64, **kw)
+    def close(x, y):
+        assert torch.equal(torch.isinf(x), torch.isinf(y))
+        fin = torch.isfinite(x)
+        assert float((x[fin] - y[fin]).abs().max()) <= 1e-5 * max(1.0, float(x[fin].abs().max()))
+
+    for b, n in enumerate(lens):
+        npg = (n + PAGE - 1) // PAGE
+        close(a[b, :, : npg * PAGE], b_[b, :, : npg * PAGE])
+    cp, cn, _ = ops.quest_select(q, cache.kmeta, cache.kv_indptr, cache.kv_indices, 1000, max_pages=cache.max_pages)
+    a = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
+                          cand_pages=cp, cand_npages=cn, **kw)
+    b_ = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
+                           cand_pages=cp, cand_npages=cn, variant=3 + 64, **kw)
+    for b in range(len(lens)):
+        for h in range(hq):
+            k = int(cn[b, h]) * PAGE
+            close(a[b, h, :k], b_[b, h, :k])
+    assert int(status.item()) == 0
 
 
 def test_gemv_entry_with_the_reference_call_signature():

@@ -36,7 +36,7 @@ struct EstParams {
   const int32_t* cand_npages;
   float* scores;
   int32_t* status;
-  int max_k, B, Hq, Hkv, num_pages_total, stride, pages_per_block, force_ring, simt_group;
+  int max_k, B, Hq, Hkv, num_pages_total, stride, pages_per_block, force_ring, simt_group, bulk_warp;
   float sm_scale;
 };
 
@@ -332,7 +332,7 @@ constexpr int kStages = 4;                           // 40 KiB ring per block
 constexpr int kTmaMaxPagesPerBlock = 512;            // capacity of the per-block page list
 constexpr int kTmaPagesPerBlockDefault = 128;        // 160 KiB of INT4 cache per block
 constexpr int kTmaThreads = kEstThreads + 32;        // 8 consumer warps + 1 producer warp
-constexpr uint32_t kWaitLimit = 1u << 20;
+constexpr uint32_t kWaitLimit = 1u << 16;  // about a second of bounded waiting, then the error flag
 constexpr uint32_t kSuspendHintNs = 20000;  // a waiting thread may sleep this long per try
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -667,6 +667,148 @@ estimate_int4_warp_kernel(const EstParams p) {
     if (pg0 + pgl < n_here) out_row[(pg0 + pgl) * kPage + tl] = (present && tl < ntok) ? acc * p.sm_scale : -INFINITY;
   }
   cp_async_wait<0>();
+}
+
+// ---- warp-private rings fed by bulk asynchronous copies (TMA) -------------------------------------
+// The scheme of the kernel above with the copy engine doing the moving: a stage is two whole slabs
+// (2 x 1280 bytes, each one contiguous in HBM and 16-byte aligned), fetched by two cp.async.bulk
+// instructions that lane 0 issues and that complete on the stage's own mbarrier (transaction
+// bytes); the warp's lanes wait on that barrier (bounded), consume the stage, meet at __syncwarp and
+// lane 0 re-arms the barrier and refills the slot.  No block-wide barrier, no producer warp, the
+// same bytes in flight per SM as with 16-byte cp.async copies (rings of the same depth and size).
+// A bulk copy lands the slab as it lies in HBM, so a lane cannot own a token (the four 16-byte
+// chunks of a token would sit in the same banks for every other lane); four lanes share a token
+// instead, lane (token, group) reads the group's 16 code bytes and its {scale, min}, and two
+// shuffles add the groups up.  Only local HBM is read; no multicast.
+template <typename T, int VARIANT, int NW, int DEPTH, int PPB>
+__global__ void __launch_bounds__(NW * 32, (220 * 1024) / (NW * DEPTH * kWarpStageBytes + 2048))
+estimate_int4_bulk_warp_kernel(const EstParams p) {
+  extern __shared__ __align__(128) uint8_t sm_ring[];  // NW * DEPTH * kWarpStageBytes
+  __shared__ __align__(8) uint64_t sm_bar[NW][DEPTH];
+  __shared__ int sm_phys[PPB + 1];
+  __shared__ int sm_ntok[PPB + 1];
+  __shared__ QRegs<VARIANT> sm_q[4];
+
+  const int row = blockIdx.y;
+  const bool has_cand = p.cand_pages != nullptr;
+  int b, kvh, h;
+  if (has_cand) {
+    b = row / p.Hq;
+    h = row % p.Hq;
+    kvh = h / (p.Hq / p.Hkv);
+  } else {  // one query head per KV head
+    b = row / p.Hkv;
+    kvh = row % p.Hkv;
+    h = kvh;
+  }
+  pdl_wait();  // candidate lists (and maybe q, the page table) come from the kernel before; nothing is read earlier
+  const int page_base = p.indptr[b];
+  const int n_seq_pages = p.indptr[b + 1] - page_base;
+  int n_pages = has_cand ? min(p.cand_npages[b * p.Hq + h], p.max_k) : n_seq_pages;
+  if (n_pages > p.stride / kPage) {
+    n_pages = p.stride / kPage;
+    if (threadIdx.x == 0 && blockIdx.x == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+  }
+  const int first = blockIdx.x * PPB;
+  if (first >= n_pages) return;
+  const int n_here = min(PPB, n_pages - first);
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  if (tid <= PPB) {
+    int phys = -1, ntok = 0;
+    if (tid < n_here) {
+      const int seq_page = has_cand ? p.cand_pages[(size_t)(b * p.Hq + h) * p.max_k + first + tid] : first + tid;
+      if (seq_page >= 0 && seq_page < n_seq_pages) {
+        phys = p.indices[page_base + seq_page];
+        if (phys < 0 || phys >= p.num_pages_total) phys = -1;
+      }
+      if (phys < 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+      ntok = (seq_page == n_seq_pages - 1) ? p.last_len[b] : kPage;
+    }
+    sm_phys[tid] = phys;
+    sm_ntok[tid] = phys < 0 ? 0 : ntok;
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) mbar_init(&sm_bar[warp][d], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (tid >= NW * 32 - 4) {
+    float qf[32];
+    load_q_group<T>(reinterpret_cast<const T*>(p.q) + ((size_t)(b * p.Hq + h)) * kD +
+                        (tid - (NW * 32 - 4)) * kGroup, qf);
+    sm_q[tid - (NW * 32 - 4)].init(qf);
+  }
+  __syncthreads();
+
+  uint8_t* const ring = sm_ring + (size_t)warp * DEPTH * kWarpStageBytes;
+  const int n_pairs = (n_here + 1) >> 1;
+  const int my_pairs = (n_pairs > warp) ? (n_pairs - warp + NW - 1) / NW : 0;
+  const uint8_t* const k4_head = p.k4 + (size_t)kvh * kSlab;
+  const size_t page_stride = (size_t)p.Hkv * kSlab;
+
+  // lane 0: arm the slot's barrier with the bytes that will arrive, then start the copies
+  uint32_t armed = 0;  // bit d: slot d has been armed and not yet consumed (the same in every lane)
+  auto issue = [&](int i, int slot) {
+    if (i < my_pairs) {
+      armed |= 1u << slot;
+      if (lane == 0) {
+        const int pg0 = (warp + i * NW) * 2;
+        const int phys0 = sm_phys[pg0], phys1 = sm_phys[pg0 + 1];  // missing pages hold -1
+        uint8_t* const dst = ring + slot * kWarpStageBytes;
+        mbar_arrive_expect_tx(&sm_bar[warp][slot], (phys0 >= 0 ? kSlab : 0) + (phys1 >= 0 ? kSlab : 0));
+        if (phys0 >= 0) bulk_copy_g2s(dst, k4_head + (size_t)phys0 * page_stride, kSlab, &sm_bar[warp][slot]);
+        if (phys1 >= 0) bulk_copy_g2s(dst + kSlab, k4_head + (size_t)phys1 * page_stride, kSlab, &sm_bar[warp][slot]);
+      }
+    }
+  };
+#pragma unroll
+  for (int i = 0; i < DEPTH - 1; ++i) issue(i, i);
+
+  const int grp = lane & 3, tok8 = lane >> 2;
+  const QRegs<VARIANT> qr = sm_q[grp];
+  float* const out_row = p.scores + (size_t)(b * p.Hq + h) * p.stride + (size_t)first * kPage + tok8;
+  int use_slot = 0, fill_slot = DEPTH - 1;
+  uint32_t phase = 0;  // bit d: parity of the phase of slot d that is waited for next
+  bool alive = true;
+  for (int i = 0; i < my_pairs && alive; ++i) {
+    // the whole warp goes on or gives up together
+    if (!__all_sync(0xffffffffu, mbar_wait(&sm_bar[warp][use_slot], (phase >> use_slot) & 1u))) {
+      if (lane == 0) raise_flag(p.status, TWL_FLAG_WAIT_LIMIT);
+      alive = false;  // give up on this warp's pages; the drain below still waits for what is in flight
+      break;
+    }
+    phase ^= 1u << use_slot;
+    armed &= ~(1u << use_slot);
+    const int pg0 = (warp + i * NW) * 2;
+    const uint8_t* stage = ring + use_slot * kWarpStageBytes;
+#pragma unroll
+    for (int s4 = 0; s4 < 4; ++s4) {  // half a page (8 tokens) per step
+      const int pgl = s4 >> 1, half = s4 & 1;
+      const int pg = pg0 + pgl;
+      const uint8_t* slab = stage + pgl * kSlab;
+      const uint4 w = *reinterpret_cast<const uint4*>(slab + half * 512 + lane * 16);
+      const uint32_t sz = *reinterpret_cast<const uint32_t*>(slab + kSlabCodes + half * 128 + lane * 4);
+      const float2 szf = __half22float2(*reinterpret_cast<const __half2*>(&sz));
+      float part = fmaf(szf.x, qr.dot(w), szf.y * qr.qsum);
+      part += __shfl_xor_sync(0xffffffffu, part, 1);
+      part += __shfl_xor_sync(0xffffffffu, part, 2);
+      if (grp == 0 && pg < n_here) {
+        const int tk = half * 8 + tok8;
+        out_row[pg * kPage + half * 8] = (tk < sm_ntok[pg]) ? part * p.sm_scale : -INFINITY;
+      }
+    }
+    __syncwarp();  // every lane is done reading the slot that the next issue overwrites
+    issue(i + DEPTH - 1, fill_slot);
+    use_slot = (use_slot + 1 == DEPTH) ? 0 : use_slot + 1;
+    fill_slot = (fill_slot + 1 == DEPTH) ? 0 : fill_slot + 1;
+  }
+  if (!alive && lane == 0) {
+    // copies may still be writing into the ring: wait (bounded) for every slot that was armed and not consumed
+    for (int d = 0; d < DEPTH; ++d)
+      if (armed & (1u << d)) mbar_wait(&sm_bar[warp][d], (phase >> d) & 1u);
+  }
 }
 
 // The same streaming scheme for a KV head shared by G query heads (every page is a candidate).
@@ -1089,6 +1231,14 @@ static int launch_one(const EstParams& p, int rows, int max_row_pages, bool ldg,
     TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
     dim3 grid((max_row_pages + kWarpPagesPerBlock - 1) / kWarpPagesPerBlock, rows);
     TWL_CUDA_TRY(launch_chain(kern, grid, dim3(kEstThreads), kBytes, st, p));
+  } else if (G == 1 && p.bulk_warp) {
+    // warp-private rings fed by bulk copies: the same block shape and bytes in flight as the default
+    constexpr int kWarps = 2, kPages = 32;
+    constexpr int kBytes = kWarps * kRingDepth * kWarpStageBytes;
+    dim3 grid((max_row_pages + kPages - 1) / kPages, rows);
+    auto kern = estimate_int4_bulk_warp_kernel<T, VARIANT, kWarps, kRingDepth, kPages>;
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+    TWL_CUDA_TRY(launch_chain(kern, grid, dim3(kWarps * 32), kBytes, st, p));
   } else if (G == 1 && !p.force_ring) {
     // Small blocks: 16 warps and the same bytes in flight per SM whatever the block size, but the
     // blocks' set-up phases spread out more.  Per step of config 1: 8 warps x 128 pages 5.45 ms,
@@ -1130,6 +1280,7 @@ static int launch_dtype(const EstParams& p, bool has_cand, int max_row_pages, in
   // +16: direct global loads; +128: the block-wide bulk-copy ring even for a single query head
   const_cast<EstParams&>(p).force_ring = (variant & 128) != 0;
   const_cast<EstParams&>(p).simt_group = (variant & 32) != 0;  // +32: integer-dot kernel for query-head groups
+  const_cast<EstParams&>(p).bulk_warp = (variant & 64) != 0;   // +64: warp-private rings fed by bulk copies
   const bool ldg = (variant & 16) != 0;
   switch (variant & 15) {
     case VAR_F32: return launch_variant<T, VAR_F32>(p, has_cand, max_row_pages, ldg, st);

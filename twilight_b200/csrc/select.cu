@@ -562,20 +562,18 @@ static int launch_scores_mma_shape(const ScoreParams& p, cudaStream_t st) {
 template <typename T, int G>
 static int launch_scores_mma(const ScoreParams& p, cudaStream_t st) {
   // Two warps per block, each with two steps (2 x 8 KiB) of loads in flight.  Measured on one KV
-  // head x 128 sequences x 4096 pages (268 MB, pages scattered): 57 us against 58 (8 warps x 256
-  // pages, one step in flight) and 66 (2 warps x 256 pages, one step in flight).  Pages per block:
-  // as many as still leave every SM four blocks, so that small problems spread out.
-  // TWL_SCORES_MMA_SHAPE picks a shape by hand (for measurement).
+  // head x 128 sequences x 4096 pages (268 MB of metadata, 17 MB of scores written): 56-57 us, the
+  // same within 2 us for 1 or 2 warps x 128..512 pages with two steps in flight and for 8 warps x
+  // 256 pages with one; 2 warps x 256 pages with one step in flight: 66 us.  Staging the slabs
+  // through a shared-memory ring (whole-slab cp.async copies, ldmatrix fragments) was slower (60-68
+  // us) and is not kept.  Pages per block: as many as still leave every SM four blocks, so that
+  // small problems spread out.  TWL_SCORES_MMA_SHAPE=1 selects 8 warps x 256 pages, one step in
+  // flight (for measurement).
   static const int forced = [] {
     const char* e = getenv("TWL_SCORES_MMA_SHAPE");
     return e ? atoi(e) : 0;
   }();
-  switch (forced) {
-    case 1: return launch_scores_mma_shape<T, G, 8, 256, false>(p, st);
-    case 2: return launch_scores_mma_shape<T, G, 2, 256, false>(p, st);
-    case 3: return launch_scores_mma_shape<T, G, 4, 512, true>(p, st);
-    default: break;
-  }
+  if (forced == 1) return launch_scores_mma_shape<T, G, 8, 256, false>(p, st);
   const long rows = (long)p.B * p.Hkv, want = 4L * num_sms();
   if (rows * ((p.max_pages + 511) / 512) >= want) return launch_scores_mma_shape<T, G, 2, 512, true>(p, st);
   if (rows * ((p.max_pages + 255) / 256) >= want) return launch_scores_mma_shape<T, G, 2, 256, true>(p, st);
