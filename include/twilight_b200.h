@@ -178,6 +178,11 @@ TWL_API int twl_threshold_prune(const float* scores, int32_t score_stride, const
  * (row, chunk) work items are dealt, long ones first, to a grid that fills the GPU once, so
  * heads with large budgets do not serialise.  The block that finishes a row's last chunk merges
  * the partial (max, sum, acc) triples; no block waits for another.
+ * indices[row][0..budget) must be ascending (twl_topp_prune writes them so).  With 2, 4 or 8 query
+ * heads per KV head, a (sequence, KV head) row whose heads keep, together, at least as many tokens
+ * as the sequence has is served by a second kernel that reads every K/V page once for the whole
+ * group and computes all its heads on tensor cores (softmax weights rounded to the model dtype
+ * before P.V, as attention.py:302-304 does); the choice is made per row on the device.
  * Limit: batch*num_q_heads <= 65536 (TWL_ERR_TOO_LARGE above).
  * workspace: twl_sparse_attn_workspace_bytes(...) bytes, 16-byte aligned; its first
  * batch*num_q_heads int32 words are arrival counters that must be zero on entry and are

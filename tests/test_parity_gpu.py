@@ -658,6 +658,56 @@ def test_sparse_attention_every_small_budget():
             assert err.max() <= ATOL_MAX, (chunk, r + 1, float(err.max()))
 
 
+@pytest.mark.parametrize("hq,hkv,dt", [(8, 2, torch.bfloat16), (8, 1, torch.float16), (4, 2, torch.bfloat16),
+                                       (16, 2, torch.bfloat16)])
+def test_group_attention_of_dense_heads(hq, hkv, dt):
+    """Query-head groups whose heads keep, together, at least the sequence's length in tokens are
+    served by the tensor-core group kernel (K/V pages read once per KV head); sparser groups stay
+    on the per-head kernel.  Both kinds in one call, ragged lengths, partial last pages: against
+    the per-head kernel on the same K/V expanded to one KV head per query head, and against the
+    fp64 oracle on sampled rows."""
+    lens = [16, 700, 1031, 2048, 5000, 9000]
+    g = hq // hkv
+    q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=dt, device=DEV, seed=77,
+                                  recipe="calibrated", shuffle_pages=True)
+    stride = cache.max_pages * PAGE
+    gen = torch.Generator().manual_seed(78)
+    indices = torch.zeros(len(lens), hq, stride, dtype=torch.int32)
+    budget = torch.zeros(len(lens), hq, dtype=torch.int32)
+    for b, n in enumerate(lens):
+        for h in range(hq):
+            # densities per (sequence, KV head): even KV heads dense (group kernel), odd ones sparse
+            dense = ((b + h // g) % 2 == 0)
+            frac = [1.0, 0.9, 0.6, 0.3][h % g % 4] if dense else [0.02, 0.1, 0.0, 0.05][h % g % 4]
+            nb = min(n, int(round(frac * n)))
+            budget[b, h] = nb
+            indices[b, h, :nb] = torch.sort(torch.randperm(n, generator=gen)[:nb])[0].int()
+    indices, budget = indices.to(DEV), budget.to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices, indices,
+                                 budget, chunk=256, status=status).clone()
+    again = ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices, indices,
+                                   budget, chunk=256, status=status)
+    assert int(status.item()) == 0
+    assert torch.equal(out, again)                       # the workspace comes back clean, results repeat
+    kx = cache.k_pages.repeat_interleave(g, dim=1).contiguous()
+    vx = cache.v_pages.repeat_interleave(g, dim=1).contiguous()
+    per_head = ops.sparse_decode_attn(q, kx, vx, cache.kv_indptr, cache.kv_indices, indices, budget, chunk=256)
+    err = (out.float() - per_head.float()).abs()
+    assert torch.isfinite(out.float()).all()
+    assert float(err.max()) <= ATOL_MAX and float(err.mean()) <= ATOL_MEAN
+    assert (out[budget == 0].float() == 0).all()         # rows without kept tokens give zeros
+    errs = []
+    for (b, h) in [(1, 0), (3, hq - 1), (4, 1), (5, g - 1), (5, hq - 1), (2, 0)]:
+        kd, vd = cache.dense_kv(b, h // g)
+        idx = indices[b, h, : int(budget[b, h])].cpu().numpy().astype(np.int64)
+        want = O.sparse_attention_fp32(q[b, h].float().cpu().numpy(), kd.float().cpu().numpy(),
+                                       vd.float().cpu().numpy(), idx, U.SM_SCALE)
+        errs.append(np.abs(out[b, h].float().cpu().numpy() - want))
+    errs = np.stack(errs)
+    assert errs.max() <= ATOL_MAX and errs.mean() <= ATOL_MEAN
+
+
 def test_attention_workspace_and_bad_index_handling():
     q, cache = make_decode_inputs(1, 2, 2, [64], dtype=torch.bfloat16, device=DEV, seed=14)
     indices = torch.tensor([[[0, 5, 9999] + [0] * 61, [1, 2, 3] + [0] * 61]], dtype=torch.int32, device=DEV)

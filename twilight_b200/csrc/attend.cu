@@ -27,6 +27,7 @@
 // Warps merge through shared memory; chunks of a row merge through the caller's workspace, and
 // the block that finishes a row's last chunk (an atomic ticket, nobody waits) writes the output.
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -57,6 +58,7 @@ struct AttParams {
   float* part_o;      // [rows][kMaxChunksPerRow][128]
   int32_t* status;
   const float* weights;  // [rows][index_stride] softmax weights of the kept tokens, or nullptr
+  int32_t* group_flags;  // [batch*Hkv] 1 = the (sequence, KV head) row is served by the group kernel; or nullptr
   int index_stride, rows, Hq, Hkv, num_pages_total, chunk;
   float sm_scale;
 };
@@ -104,10 +106,11 @@ sparse_decode_attn_kernel(const AttParams p) {
       for (int j = 0; j < kPer; ++j) {
         const int r = r0 + tid * kPer + j;
         if (r < p.rows) {
-          const int bud = min(max(p.budget[r], 0), p.index_stride);
+          const bool grouped = p.group_flags != nullptr && p.group_flags[r / (p.Hq / p.Hkv)] != 0;
+          const int bud = grouped ? 0 : min(max(p.budget[r], 0), p.index_stride);
           const int len = row_chunk_len(bud, p.chunk);
           const int n = (bud + len - 1) / len;
-          sm_cnt[r] = (uint8_t)n;
+          sm_cnt[r] = grouped ? (uint8_t)255 : (uint8_t)n;  // 255: not this kernel's row (row counts stop at 32)
           s_lead += max(n - 1, 0);
           s_last += n > 0 ? 1 : 0;
         }
@@ -160,7 +163,8 @@ sparse_decode_attn_kernel(const AttParams p) {
     }
     const int rem = pos - pref[lo];
     const int cand_row = lo * 32 + lane;
-    const int n_mine = cand_row < p.rows ? (int)sm_cnt[cand_row] : 0;
+    const int n_raw = cand_row < p.rows ? (int)sm_cnt[cand_row] : 0;
+    const int n_mine = n_raw == 255 ? 0 : n_raw;
     const int mine = leading ? max(n_mine - 1, 0) : (n_mine > 0 ? 1 : 0);
     int inc = mine;
 #pragma unroll
@@ -456,6 +460,336 @@ sparse_decode_attn_kernel(const AttParams p) {
   }
 }
 
+// ---- query-head groups: the K/V pages of a KV head are read once for all of its query heads ----
+//
+// When the query heads of a KV head keep, between them, at least as many tokens as the sequence
+// has (what dense-ish heads do), fetching every head's tokens separately reads the same K/V rows
+// several times.  This kernel serves such (sequence, KV head) rows instead: it walks the pages of a
+// chunk of the sequence in which any head of the group kept a token, stages each page once (K and
+// V: 8 KiB) in a warp-private ring, and computes all the group's heads on tensor cores:
+//   S^T[head][token] = Q K^T      m16n8k16 tiles, A = Q (heads as rows, padded to 16), B = the K page
+//   masked per head by the page's kept-token bits, online softmax per head in the accumulator
+//   layout, O[head][dim] += P V   A = P rounded to the model dtype (attention.py:302-304), B = the
+//   V page read transposed.
+// The per-head kept-token bits come from the index lists themselves: they are ascending (the
+// pruner writes them so), so a head's tokens inside the chunk are one run of its list, found by a
+// 32-way search; every lane turns a piece of the run into page bit masks.  Partial results go
+// through the same workspace slots and arrival counters as the per-head kernel's chunks, so the
+// merge and the output are the same.  Whether a row is served here is decided on the device from
+// the budgets (the host never sees them) and published in group_flags for the per-head kernel,
+// which runs afterwards and skips those rows.
+constexpr int kGrpWarps = 2;
+constexpr int kGrpThreads = kGrpWarps * 32;
+constexpr int kGrpStages = 3;
+constexpr int kGrpStageBytes = 2 * kPage * kD * 2;                       // K page, then V page: 8 KiB
+constexpr int kGrpRingBytes = kGrpWarps * kGrpStages * kGrpStageBytes;   // 48 KiB per block
+constexpr int kGrpMaxChunkPages = 256;                                   // pages of one work item
+constexpr int kGrpMinChunkPages = 64;
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// First position of the ascending list idx[0..n) whose value is >= key; the warp probes 32 places
+// per step, so three dependent loads settle a list of 32768 entries.
+__device__ __forceinline__ int warp_lower_bound(const int32_t* idx, int n, int key, int lane) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    const int step = (hi - lo + 31) >> 5;
+    const int q = lo + lane * step;
+    const bool less = q < hi && idx[q] < key;
+    const int cnt = __popc(__ballot_sync(0xffffffffu, less));  // the probes below key are a prefix
+    if (cnt == 0) {
+      hi = lo;
+    } else {
+      const int nlo = lo + (cnt - 1) * step + 1;
+      hi = min(hi, lo + cnt * step);
+      lo = nlo;
+    }
+  }
+  return lo;
+}
+
+template <typename T, int G>
+__global__ void __launch_bounds__(kGrpThreads)
+group_decode_attn_kernel(const AttParams p) {
+  static_assert(G == 2 || G == 4 || G == 8, "the group sits in the upper rows of one m16 tile");
+  extern __shared__ __align__(128) unsigned char sm_dyn[];  // the rings; later the warps' results
+  __shared__ uint32_t sm_mask[G][kGrpMaxChunkPages / 2];    // kept-token bits, two pages a word
+  __shared__ uint16_t sm_upage[kGrpMaxChunkPages];          // pages of the chunk with any kept token
+  __shared__ int sm_uphys[kGrpMaxChunkPages];
+  __shared__ int sm_nunion;
+  __shared__ int sm_ticket[G];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int c = blockIdx.x, rkv = blockIdx.y;
+  const int b = rkv / p.Hkv, kvh = rkv % p.Hkv;
+  const int row0 = b * p.Hq + kvh * G;  // first (batch, query head) row of the group
+  pdl_wait();  // budgets and index lists come from the pruner launched before
+  const int page_base = p.indptr[b];
+  const int pages_b = p.indptr[b + 1] - page_base;
+  // served here when the group's heads keep at least one token per token of the sequence
+  int bud_l = 0;
+  if (lane < G) bud_l = min(max(p.budget[row0 + lane], 0), p.index_stride);
+  const int bud_sum = warp_sum_i(bud_l);
+  const bool mine = pages_b > 0 && pages_b <= kMaxChunksPerRow * kGrpMaxChunkPages &&
+                    (long long)bud_sum >= (long long)pages_b * kPage;
+  if (c == 0 && tid == 0) p.group_flags[rkv] = mine ? 1 : 0;
+  if (!mine) return;
+  int cp = kGrpMinChunkPages;  // pages per chunk: at most kMaxChunksPerRow chunks per row
+  while (cp * kMaxChunksPerRow < pages_b) cp *= 2;
+  const int n_chunks = (pages_b + cp - 1) / cp;
+  if (c >= n_chunks) return;
+  const int p0 = c * cp, p1 = min(pages_b, p0 + cp), npg = p1 - p0;
+
+  // ---- kept-token bits of every head for the pages of this chunk ----
+  for (int i = tid; i < G * (kGrpMaxChunkPages / 2); i += kGrpThreads) (&sm_mask[0][0])[i] = 0u;
+  __syncthreads();
+  bool bad = false;
+  for (int hh = warp; hh < G; hh += kGrpWarps) {
+    const int32_t* idx = p.idx + (size_t)(row0 + hh) * p.index_stride;
+    const int n = __shfl_sync(0xffffffffu, bud_l, hh);
+    const int s0 = warp_lower_bound(idx, n, p0 * kPage, lane);
+    const int s1 = warp_lower_bound(idx, n, p1 * kPage, lane);
+    if (c == n_chunks - 1 && s1 < n) bad = true;  // tokens past the last page of the sequence
+    const int per = (s1 - s0 + 31) >> 5;
+    const int a = s0 + lane * per, e = min(s1, a + per);
+    int cur = -1;
+    uint32_t bits = 0;
+    for (int i = a; i < e; ++i) {
+      const int tok = idx[i];
+      const int pg = (tok >> 4) - p0;
+      if (pg != cur) {
+        if (cur >= 0 && cur < npg) atomicOr(&sm_mask[hh][cur >> 1], bits << ((cur & 1) * 16));
+        cur = pg;
+        bits = 0;
+      }
+      bits |= 1u << (tok & 15);
+    }
+    if (cur >= 0 && cur < npg) atomicOr(&sm_mask[hh][cur >> 1], bits << ((cur & 1) * 16));
+  }
+  __syncthreads();
+  // ---- pages with any kept token, and where they lie ----
+  if (warp == 0) {
+    int n_u = 0;
+    for (int j0 = 0; j0 < npg; j0 += 32) {
+      const int j = j0 + lane;
+      uint32_t u = 0;
+      if (j < npg) {
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) u |= (sm_mask[hh][j >> 1] >> ((j & 1) * 16)) & 0xFFFFu;
+      }
+      int phys = -1;
+      if (u != 0) {
+        phys = p.indices[page_base + p0 + j];
+        if (phys < 0 || phys >= p.num_pages_total) {
+          phys = -1;
+          bad = true;
+        }
+      }
+      const unsigned m = __ballot_sync(0xffffffffu, phys >= 0);
+      if (phys >= 0) {
+        const int pos = n_u + __popc(m & ((1u << lane) - 1));
+        sm_upage[pos] = (uint16_t)j;
+        sm_uphys[pos] = phys;
+      }
+      n_u += __popc(m);
+    }
+    if (lane == 0) sm_nunion = n_u;
+  }
+  __syncthreads();
+  if (__any_sync(0xffffffffu, bad) && lane == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+  const int n_union = sm_nunion;
+
+  // ---- Q as the A operand: row g = head g (rows from G on are zero), eight k-steps of 16 channels ----
+  const int g = lane >> 2, t = lane & 3;
+  uint32_t qa[8][2];
+  {
+    const uint32_t* qrow = reinterpret_cast<const uint32_t*>(reinterpret_cast<const T*>(p.q) +
+                                                             (size_t)(row0 + (g < G ? g : 0)) * kD);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      qa[ks][0] = g < G ? __ldg(qrow + 8 * ks + t) : 0u;      // channels 16ks + 2t, +1
+      qa[ks][1] = g < G ? __ldg(qrow + 8 * ks + 4 + t) : 0u;  // channels 16ks + 8 + 2t, +1
+    }
+  }
+
+  unsigned char* const my_ring = sm_dyn + warp * (kGrpStages * kGrpStageBytes);
+  const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
+  const int my_n = (n_union > warp) ? (n_union - warp + kGrpWarps - 1) / kGrpWarps : 0;
+  const T* const kbase = reinterpret_cast<const T*>(p.k);
+  const T* const vbase = reinterpret_cast<const T*>(p.v);
+  // a page is 16 token rows of 256 bytes; chunk ch of token row r goes to position ch ^ (r & 7), which
+  // keeps the copies and the 8-row matrix reads below free of bank conflicts
+  auto issue = [&](int i, int slot) {
+    if (i < my_n) {
+      const int phys = sm_uphys[warp + i * kGrpWarps];
+      const size_t off = ((size_t)phys * p.Hkv + kvh) * (kPage * kD);
+      const unsigned char* ksrc = reinterpret_cast<const unsigned char*>(kbase + off) + lane * 16;
+      const unsigned char* vsrc = reinterpret_cast<const unsigned char*>(vbase + off) + lane * 16;
+      const uint32_t dst = ring_s + slot * kGrpStageBytes;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int r = 2 * j + (lane >> 4), ch = lane & 15;
+        const uint32_t d = r * 256 + ((ch ^ (r & 7)) << 4);
+        cp_async16(dst + d, ksrc + j * 512);
+        cp_async16(dst + kPage * kD * 2 + d, vsrc + j * 512);
+      }
+    }
+    cp_async_commit();  // always commit so that group counting stays uniform
+  };
+#pragma unroll
+  for (int i = 0; i < kGrpStages - 1; ++i) issue(i, i);
+
+  // ldmatrix lane addressing: matrix mi = lane >> 3, row r8 = lane & 7 of it
+  const int mi = lane >> 3, r8 = lane & 7;
+  // K: matrices (tokens 0-7, chunk 2ks) (tokens 0-7, 2ks+1) (tokens 8-15, 2ks) (tokens 8-15, 2ks+1)
+  const int k_tok = r8 + (mi >> 1) * 8, k_sub = mi & 1;
+  // V, transposed: (tokens 0-7, chunk 2jj) (tokens 8-15, 2jj) (tokens 0-7, 2jj+1) (tokens 8-15, 2jj+1)
+  const int v_tok = r8 + (mi & 1) * 8, v_sub = mi >> 1;
+
+  float o[16][4];
+#pragma unroll
+  for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+  float m_run = kNegBig, l_run = 0.f;  // of head g, over this lane's tokens (columns 2t, 2t+1, 8+2t, 9+2t)
+  int slot = 0, fill = kGrpStages - 1;
+  for (int i = 0; i < my_n; ++i) {
+    cp_async_wait<kGrpStages - 2>();
+    __syncwarp();
+    const uint32_t st = ring_s + slot * kGrpStageBytes;
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t b0, b1, b2, b3;
+      const uint32_t addr = st + k_tok * 256 + ((((2 * ks + k_sub)) ^ (k_tok & 7)) << 4);
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                   : "r"(addr));
+      MmaTile<T>::run(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);  // tokens 0-7
+      MmaTile<T>::run(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);  // tokens 8-15
+    }
+    const int pg = sm_upage[warp + i * kGrpWarps];
+    const uint32_t bits = g < G ? (sm_mask[g < G ? g : 0][pg >> 1] >> ((pg & 1) * 16)) & 0xFFFFu : 0u;
+    float x[4];
+    x[0] = (bits >> (2 * t)) & 1u ? s0[0] * p.sm_scale : -INFINITY;
+    x[1] = (bits >> (2 * t + 1)) & 1u ? s0[1] * p.sm_scale : -INFINITY;
+    x[2] = (bits >> (8 + 2 * t)) & 1u ? s1[0] * p.sm_scale : -INFINITY;
+    x[3] = (bits >> (9 + 2 * t)) & 1u ? s1[1] * p.sm_scale : -INFINITY;
+    float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float alpha = __expf(m_run - m_new);
+    float pw[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) pw[k] = __expf(x[k] - m_new);
+    l_run = l_run * alpha + (pw[0] + pw[1]) + (pw[2] + pw[3]);
+    m_run = m_new;
+    if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt) {
+        o[nt][0] *= alpha;
+        o[nt][1] *= alpha;
+      }
+    }
+    const uint32_t pa0 = pack_pair<T>(pw[0], pw[1]), pa2 = pack_pair<T>(pw[2], pw[3]);
+    const uint32_t sv = st + kPage * kD * 2;
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      uint32_t b0, b1, b2, b3;
+      const uint32_t addr = sv + v_tok * 256 + ((((2 * jj + v_sub)) ^ (v_tok & 7)) << 4);
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                   : "r"(addr));
+      MmaTile<T>::run(o[2 * jj], pa0, 0u, pa2, 0u, b0, b1);      // channels 16jj .. 16jj+7
+      MmaTile<T>::run(o[2 * jj + 1], pa0, 0u, pa2, 0u, b2, b3);  // channels 16jj+8 .. 16jj+15
+    }
+    __syncwarp();  // every lane is done with the slot before it is refilled
+    issue(i + kGrpStages - 1, fill);
+    slot = (slot + 1 == kGrpStages) ? 0 : slot + 1;
+    fill = (fill + 1 == kGrpStages) ? 0 : fill + 1;
+  }
+  cp_async_wait<0>();
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  __syncthreads();  // the rings are idle from here on: they take the warps' results
+
+  // ---- merge the warps: per head (max, sum, 128 channels) ----
+  float* const res = reinterpret_cast<float*>(sm_dyn);  // [warp][G][130]
+  if (g < G) {
+    float* mine_o = res + ((size_t)warp * G + g) * 130;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      mine_o[8 * nt + 2 * t] = o[nt][0];
+      mine_o[8 * nt + 2 * t + 1] = o[nt][1];
+    }
+    if (t == 0) {
+      mine_o[128] = m_run;
+      mine_o[129] = l_run;
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < G * kD; e += kGrpThreads) {
+    const int hh = e / kD, d = e % kD;
+    float gm = kNegBig;
+#pragma unroll
+    for (int w = 0; w < kGrpWarps; ++w) gm = fmaxf(gm, res[((size_t)w * G + hh) * 130 + 128]);
+    float gl = 0.f, go = 0.f;
+#pragma unroll
+    for (int w = 0; w < kGrpWarps; ++w) {
+      const float* r = res + ((size_t)w * G + hh) * 130;
+      const float f = __expf(r[128] - gm);
+      gl += f * r[129];
+      go += f * r[d];
+    }
+    const int row = row0 + hh;
+    if (n_chunks == 1) {
+      reinterpret_cast<T*>(p.out)[(size_t)row * kD + d] = Elem<T>::from_f(gl > 0.f ? go / gl : 0.f);
+    } else {
+      const size_t ps = (size_t)row * kMaxChunksPerRow + c;
+      p.part_o[ps * kD + d] = go;
+      if (d == 0) {
+        p.part_ml[ps * 2] = gm;
+        p.part_ml[ps * 2 + 1] = gl;
+      }
+    }
+  }
+  if (n_chunks == 1) return;
+  // publish, then one ticket per head; whoever holds the last ticket of a row merges its chunks
+  __threadfence();
+  __syncthreads();
+  if (tid < G) sm_ticket[tid] = atomicAdd(&p.counters[row0 + tid], 1);
+  __syncthreads();
+  for (int hh = 0; hh < G; ++hh) {
+    if (sm_ticket[hh] != n_chunks - 1) continue;  // the same for the whole block
+    __threadfence();
+    const int row = row0 + hh;
+    float gm = kNegBig;
+    for (int cc = 0; cc < n_chunks; ++cc)
+      gm = fmaxf(gm, __ldcg(&p.part_ml[((size_t)row * kMaxChunksPerRow + cc) * 2]));
+    for (int d = tid; d < kD; d += kGrpThreads) {
+      float gl = 0.f, go = 0.f;
+      for (int cc = 0; cc < n_chunks; ++cc) {
+        const size_t s2 = (size_t)row * kMaxChunksPerRow + cc;
+        const float f = __expf(__ldcg(&p.part_ml[s2 * 2]) - gm);
+        gl += f * __ldcg(&p.part_ml[s2 * 2 + 1]);
+        go += f * __ldcg(&p.part_o[s2 * kD + d]);
+      }
+      reinterpret_cast<T*>(p.out)[(size_t)row * kD + d] = Elem<T>::from_f(gl > 0.f ? go / gl : 0.f);
+    }
+    if (tid == 0) p.counters[row] = 0;  // leave the workspace ready for the next call
+  }
+}
+
 // Launch shared by the entry points.  `chain`: launch with programmatic stream serialization so
 // that the kernel's prologue overlaps the tail of the kernel before it.
 static int launch_attn(const AttParams& p, int dtype, size_t rows, int32_t index_stride, int32_t chunk,
@@ -466,6 +800,32 @@ static int launch_attn(const AttParams& p, int dtype, size_t rows, int32_t index
       rows * std::min<size_t>(kMaxChunksPerRow, ((size_t)index_stride + chunk - 1) / chunk);
   const size_t n_groups = (rows + 31) / 32;
   const size_t smem = (kAttRingBytes + 2 * (n_groups + 1) * sizeof(int) + rows + 15) & ~(size_t)15;
+  // query-head groups whose heads keep, together, at least the sequence's length in tokens are served
+  // by the group kernel (it decides per row on the device and leaves flags for the kernel below)
+  if (p.group_flags != nullptr) {
+    const int g = p.Hq / p.Hkv;
+    const dim3 grid(kMaxChunksPerRow, (unsigned)(rows / g));
+    if (grid.y > 65535) return TWL_ERR_TOO_LARGE;
+#define TWL_LAUNCH_GRP(TYPE, GG)                                                                   \
+  do {                                                                                             \
+    auto kern = group_decode_attn_kernel<TYPE, GG>;                                                \
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGrpRingBytes)); \
+    if (chain) {                                                                                   \
+      TWL_CUDA_TRY(launch_chain(kern, grid, dim3(kGrpThreads), kGrpRingBytes, st, p));             \
+    } else {                                                                                       \
+      kern<<<grid, kGrpThreads, kGrpRingBytes, st>>>(p);                                           \
+    }                                                                                              \
+  } while (0)
+    if (dtype == TWL_F16) {
+      if (g == 2) TWL_LAUNCH_GRP(__half, 2); else if (g == 4) TWL_LAUNCH_GRP(__half, 4); else TWL_LAUNCH_GRP(__half, 8);
+    } else if (dtype == TWL_BF16) {
+      if (g == 2) TWL_LAUNCH_GRP(__nv_bfloat16, 2); else if (g == 4) TWL_LAUNCH_GRP(__nv_bfloat16, 4); else TWL_LAUNCH_GRP(__nv_bfloat16, 8);
+    } else {
+      return TWL_ERR_UNSUPPORTED;
+    }
+#undef TWL_LAUNCH_GRP
+    TWL_CHECK_LAUNCH();
+  }
 #define TWL_LAUNCH_ATT(TYPE, W)                                                                    \
   do {                                                                                             \
     auto kern = sparse_decode_attn_kernel<TYPE, W>;                                                \
@@ -494,13 +854,24 @@ static int launch_attn(const AttParams& p, int dtype, size_t rows, int32_t index
 
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// Groups of 2, 4 or 8 query heads per KV head may be served by the group kernel; TWL_ATTN_GROUP=0
+// in the environment keeps everything on the per-head kernel (for measurement).
+static bool group_path_enabled(int num_q_heads, int num_kv_heads) {
+  static const bool on = [] {
+    const char* e = getenv("TWL_ATTN_GROUP");
+    return !(e && e[0] == '0');
+  }();
+  const int g = num_q_heads / num_kv_heads;
+  return on && (g == 2 || g == 4 || g == 8);
+}
+
 }  // namespace twl
 
 extern "C" size_t twl_sparse_attn_workspace_bytes(int32_t batch, int32_t num_q_heads,
                                                   int32_t index_stride, int32_t chunk) {
   if (batch <= 0 || num_q_heads <= 0 || index_stride <= 0 || chunk <= 0) return 0;
   const size_t rows = (size_t)batch * num_q_heads;
-  size_t bytes = twl::align_up(rows * sizeof(int32_t), 256);
+  size_t bytes = twl::align_up(2 * rows * sizeof(int32_t), 256);  // arrival counters, then group flags
   bytes += twl::align_up(rows * twl::kMaxChunksPerRow * 2 * sizeof(float), 256);
   bytes += rows * twl::kMaxChunksPerRow * twl::kD * sizeof(float);
   return bytes;
@@ -534,7 +905,8 @@ static int attn_entry(const void* q, int dtype, const void* k_pages, const void*
   p.idx = indices; p.budget = budget; p.out = out; p.status = status; p.weights = weights;
   char* ws = static_cast<char*>(workspace);
   p.counters = reinterpret_cast<int32_t*>(ws);
-  ws += align_up(rows * sizeof(int32_t), 256);
+  p.group_flags = (weights == nullptr && group_path_enabled(num_q_heads, num_kv_heads)) ? p.counters + rows : nullptr;
+  ws += align_up(2 * rows * sizeof(int32_t), 256);
   p.part_ml = reinterpret_cast<float*>(ws);
   ws += align_up(rows * kMaxChunksPerRow * 2 * sizeof(float), 256);
   p.part_o = reinterpret_cast<float*>(ws);
@@ -580,7 +952,7 @@ extern "C" int twl_sparse_decode_attn_weighted(const void* q, int dtype, const v
 namespace twl {
 
 constexpr size_t kStaticRows = TWL_STATIC_ATTN_MAX_ROWS;
-constexpr size_t kStaticCounterBytes = (kStaticRows * sizeof(int32_t) + 255) / 256 * 256;
+constexpr size_t kStaticCounterBytes = (2 * kStaticRows * sizeof(int32_t) + 255) / 256 * 256;  // counters, group flags
 constexpr size_t kStaticMlBytes = (kStaticRows * kMaxChunksPerRow * 2 * sizeof(float) + 255) / 256 * 256;
 constexpr size_t kStaticScratchBytes =
     kStaticCounterBytes + kStaticMlBytes + kStaticRows * kMaxChunksPerRow * kD * sizeof(float);
@@ -641,6 +1013,7 @@ extern "C" int twl_sparse_decode_attn_static(const void* q, int dtype, const voi
   p.idx = indices; p.budget = budget; p.out = out; p.status = status; p.weights = nullptr;
   char* ws = static_cast<char*>(scratch);
   p.counters = reinterpret_cast<int32_t*>(ws);
+  p.group_flags = group_path_enabled(num_q_heads, num_kv_heads) ? p.counters + rows : nullptr;
   p.part_ml = reinterpret_cast<float*>(ws + kStaticCounterBytes);
   p.part_o = reinterpret_cast<float*>(ws + kStaticCounterBytes + kStaticMlBytes);
   p.index_stride = index_stride; p.rows = (int)rows; p.Hq = num_q_heads; p.Hkv = num_kv_heads;

@@ -679,7 +679,7 @@ estimate_int4_warp_kernel(const EstParams p) {
 // A bulk copy lands the slab as it lies in HBM, so a lane cannot own a token (the four 16-byte
 // chunks of a token would sit in the same banks for every other lane); four lanes share a token
 // instead, lane (token, group) reads the group's 16 code bytes and its {scale, min}, and two
-// shuffles add the groups up.  Only local HBM is read; no multicast.
+// shuffles add the groups up.  Only this GPU's own HBM is read, by plain (single-destination) bulk copies.
 template <typename T, int VARIANT, int NW, int DEPTH, int PPB>
 __global__ void __launch_bounds__(NW * 32, (220 * 1024) / (NW * DEPTH * kWarpStageBytes + 2048))
 estimate_int4_bulk_warp_kernel(const EstParams p) {
