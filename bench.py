@@ -685,7 +685,7 @@ def topp_vs_reference(dev):
 # ---------------------------------------------------------------------------------------------
 # strong scaling through the shard plan
 # ---------------------------------------------------------------------------------------------
-def strong_leg(name, w, args, dev, dist, world, rank, steps, repeats):
+def strong_leg(name, w, args, dev, dist, world, rank, steps, repeats, prefer="batch"):
     """The GLOBAL problem ``w`` partitioned over the ranks by (sequence, KV head) units
     (``twilight_b200.dist.shard_units``); every rank holds only its units' caches, the outputs are
     gathered with one NCCL all-gather per decoded token.  With ``check``, rank 0 rebuilds two units
@@ -695,7 +695,7 @@ def strong_leg(name, w, args, dev, dist, world, rank, steps, repeats):
     from twilight_b200.gen import ragged_lengths
     g = w["heads"] // w["kv_heads"]
     lens = [w["ctx"]] * w["batch"] if isinstance(w["ctx"], int) else ragged_lengths(w["batch"], *w["ctx"], seed=2)
-    plan = shard_units(w["batch"], w["kv_heads"], world, lens)
+    plan = shard_units(w["batch"], w["kv_heads"], world, lens, prefer=prefer)
     bids, hids = plan.batch_ids[rank], plan.kv_head_ids[rank]
     h = Harness(w, dev, resident_layers=2, attn_chunk=args.attn_chunk, variant=args.variant, seed_base=9000,
                 units=(bids, hids, [lens[b] for b in bids]), dist=dist, world=world, use_graph=not args.no_graph)
@@ -932,9 +932,9 @@ def main():
         strong = {}
         try:
             strong["config1"] = strong_leg("config1", dict(PRESETS["config1"]), args, dev, dist, world, rank, 10, 5)
-            if world == 8:
+            if 8 % world == 0:   # the 8 KV heads of config 4 over the ranks: one per GPU at N=8
                 w4 = dict(PRESETS["config4_shard"], title="Llama-3-70B-class decode attention", heads=64, kv_heads=8)
-                strong["config4"] = strong_leg("config4", w4, args, dev, dist, world, rank, 1, 3)
+                strong["config4"] = strong_leg("config4", w4, args, dev, dist, world, rank, 1, 3, prefer="heads")
         except Exception as e:
             strong["error"] = f"{type(e).__name__}: {e}"
         extra["strong"] = strong

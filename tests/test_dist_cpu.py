@@ -25,6 +25,13 @@ def test_plans_tile_the_grid_exactly_once():
     assert all(len(plan.kv_head_ids[r]) == 1 and plan.batch_ids[r] == [0, 1, 2] for r in range(8))
     with pytest.raises(ValueError):
         shard_units(3, 5, 4)
+    # both split: sequences by default, KV heads on request (config 4: B=128, 8 KV heads, 8 GPUs)
+    by_batch, by_heads = shard_units(128, 8, 8), shard_units(128, 8, 8, prefer="heads")
+    assert all(len(by_batch.batch_ids[r]) == 16 and len(by_batch.kv_head_ids[r]) == 8 for r in range(8))
+    assert all(by_heads.kv_head_ids[r] == [r] and len(by_heads.batch_ids[r]) == 128 for r in range(8))
+    assert shard_units(128, 8, 2, prefer="heads").kv_head_ids == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    with pytest.raises(ValueError):
+        shard_units(4, 4, 2, prefer="rows")
 
 
 def test_ragged_lengths_are_balanced():

@@ -714,6 +714,8 @@ group_decode_attn_kernel(const AttParams p) {
       MmaTile<T>::run(o[2 * jj + 1], pa0, 0u, pa2, 0u, b2, b3);  // channels 16jj+8 .. 16jj+15
     }
     __syncwarp();  // every lane is done with the slot before it is refilled
+    // (a four-stage ring refilled before the page is worked on - three pages in flight per warp all
+    // the time, but three blocks per SM instead of four - was slower: 1077 against 1001 us on config 2)
     issue(i + kGrpStages - 1, fill);
     slot = (slot + 1 == kGrpStages) ? 0 : slot + 1;
     fill = (fill + 1 == kGrpStages) ? 0 : fill + 1;

@@ -33,17 +33,21 @@ class ShardPlan:
 
 
 def shard_units(batch: int, num_kv_heads: int, world_size: int,
-                seq_lens: Optional[Sequence[int]] = None) -> ShardPlan:
+                seq_lens: Optional[Sequence[int]] = None, prefer: str = "batch") -> ShardPlan:
     """Splits the grid into ``world_size`` equal rectangles: over sequences when the batch divides
     (balanced by context length when ``seq_lens`` is given), otherwise over KV heads, otherwise
-    over both (``world = wb * wh``).  Raises when no rectangular tiling exists."""
+    over both (``world = wb * wh``).  ``prefer="heads"`` tries the KV heads first (one KV head per
+    GPU for an 8-KV-head model on 8 GPUs).  Raises when no rectangular tiling exists."""
     if world_size <= 0:
         raise ValueError("world_size must be positive")
+    if prefer not in ("batch", "heads"):
+        raise ValueError("prefer must be 'batch' or 'heads'")
     wb = wh = None
-    if batch % world_size == 0:
-        wb, wh = world_size, 1
-    elif num_kv_heads % world_size == 0:
+    by_batch, by_heads = batch % world_size == 0, num_kv_heads % world_size == 0
+    if by_heads and (prefer == "heads" or not by_batch):
         wb, wh = 1, world_size
+    elif by_batch:
+        wb, wh = world_size, 1
     else:
         for cand in range(world_size, 0, -1):
             if world_size % cand == 0 and batch % cand == 0 and num_kv_heads % (world_size // cand) == 0:
