@@ -679,6 +679,8 @@ def test_group_attention_of_dense_heads(hq, hkv, dt):
             # densities per (sequence, KV head): even KV heads dense (group kernel), odd ones sparse
             dense = ((b + h // g) % 2 == 0)
             frac = [1.0, 0.9, 0.6, 0.3][h % g % 4] if dense else [0.02, 0.1, 0.0, 0.05][h % g % 4]
+            if dense and b == 3 and h % g == 1:
+                frac = 0.0                        # a head without kept tokens inside a group that is served together
             nb = min(n, int(round(frac * n)))
             budget[b, h] = nb
             indices[b, h, :nb] = torch.sort(torch.randperm(n, generator=gen)[:nb])[0].int()
@@ -706,6 +708,27 @@ def test_group_attention_of_dense_heads(hq, hkv, dt):
         errs.append(np.abs(out[b, h].float().cpu().numpy() - want))
     errs = np.stack(errs)
     assert errs.max() <= ATOL_MAX and errs.mean() <= ATOL_MEAN
+
+
+def test_group_attention_flags_tokens_past_the_sequence():
+    """An index past the last page of the sequence in a row served by the group kernel is skipped
+    and flagged, like in the per-head kernel."""
+    n, hq, hkv = 1000, 4, 1
+    q, cache = make_decode_inputs(1, hq, hkv, [n], dtype=torch.bfloat16, device=DEV, seed=79, recipe="calibrated")
+    stride = cache.max_pages * PAGE + 64
+    indices = torch.zeros(1, hq, stride, dtype=torch.int32)
+    budget = torch.full((1, hq), n, dtype=torch.int32)
+    for h in range(hq):
+        indices[0, h, :n] = torch.arange(n, dtype=torch.int32)
+    good = ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices,
+                                  indices.to(DEV), budget.to(DEV), chunk=256).clone()
+    indices[0, 2, n] = 5000                      # one more "kept token", far past the sequence
+    budget[0, 2] = n + 1
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices,
+                                 indices.to(DEV), budget.to(DEV), chunk=256, status=status)
+    assert int(status.item()) & ops.FLAG_BAD_INDEX
+    assert torch.equal(out, good)                # the stray index changes nothing else
 
 
 def test_attention_workspace_and_bad_index_handling():

@@ -667,15 +667,22 @@ group_decode_attn_kernel(const AttParams p) {
     __syncwarp();
     const uint32_t st = ring_s + slot * kGrpStageBytes;
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      // all fragment loads of the page first, then the tiles: the loads' latencies overlap instead
+      // of each one being waited for by the tile that follows it
+      uint32_t kb[8][4];
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      uint32_t b0, b1, b2, b3;
-      const uint32_t addr = st + k_tok * 256 + ((((2 * ks + k_sub)) ^ (k_tok & 7)) << 4);
-      asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
-                   : "r"(addr));
-      MmaTile<T>::run(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);  // tokens 0-7
-      MmaTile<T>::run(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);  // tokens 8-15
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t addr = st + k_tok * 256 + ((((2 * ks + k_sub)) ^ (k_tok & 7)) << 4);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(kb[ks][0]), "=r"(kb[ks][1]), "=r"(kb[ks][2]), "=r"(kb[ks][3])
+                     : "r"(addr));
+      }
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        MmaTile<T>::run(s0, qa[ks][0], 0u, qa[ks][1], 0u, kb[ks][0], kb[ks][1]);  // tokens 0-7
+        MmaTile<T>::run(s1, qa[ks][0], 0u, qa[ks][1], 0u, kb[ks][2], kb[ks][3]);  // tokens 8-15
+      }
     }
     const int pg = sm_upage[warp + i * kGrpWarps];
     const uint32_t bits = g < G ? (sm_mask[g < G ? g : 0][pg >> 1] >> ((pg & 1) * 16)) & 0xFFFFu : 0u;
@@ -703,15 +710,20 @@ group_decode_attn_kernel(const AttParams p) {
     }
     const uint32_t pa0 = pack_pair<T>(pw[0], pw[1]), pa2 = pack_pair<T>(pw[2], pw[3]);
     const uint32_t sv = st + kPage * kD * 2;
+    {
+      uint32_t vb[8][4];
 #pragma unroll
-    for (int jj = 0; jj < 8; ++jj) {
-      uint32_t b0, b1, b2, b3;
-      const uint32_t addr = sv + v_tok * 256 + ((((2 * jj + v_sub)) ^ (v_tok & 7)) << 4);
-      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
-                   : "r"(addr));
-      MmaTile<T>::run(o[2 * jj], pa0, 0u, pa2, 0u, b0, b1);      // channels 16jj .. 16jj+7
-      MmaTile<T>::run(o[2 * jj + 1], pa0, 0u, pa2, 0u, b2, b3);  // channels 16jj+8 .. 16jj+15
+      for (int jj = 0; jj < 8; ++jj) {
+        const uint32_t addr = sv + v_tok * 256 + ((((2 * jj + v_sub)) ^ (v_tok & 7)) << 4);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(vb[jj][0]), "=r"(vb[jj][1]), "=r"(vb[jj][2]), "=r"(vb[jj][3])
+                     : "r"(addr));
+      }
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        MmaTile<T>::run(o[2 * jj], pa0, 0u, pa2, 0u, vb[jj][0], vb[jj][1]);      // channels 16jj .. 16jj+7
+        MmaTile<T>::run(o[2 * jj + 1], pa0, 0u, pa2, 0u, vb[jj][2], vb[jj][3]);  // channels 16jj+8 .. 16jj+15
+      }
     }
     __syncwarp();  // every lane is done with the slot before it is refilled
     // (a four-stage ring refilled before the page is worked on - three pages in flight per warp all

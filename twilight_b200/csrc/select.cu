@@ -566,7 +566,8 @@ static int launch_scores_mma(const ScoreParams& p, cudaStream_t st) {
   // same within 2 us for 1 or 2 warps x 128..512 pages with two steps in flight and for 8 warps x
   // 256 pages with one; 2 warps x 256 pages with one step in flight: 66 us.  Staging the slabs
   // through a shared-memory ring (whole-slab cp.async copies, ldmatrix fragments) was slower (60-68
-  // us) and is not kept.  Pages per block: as many as still leave every SM four blocks, so that
+  // us) and is not kept; neither is a one-wave grid whose blocks walk the (row, page run) items
+  // (58.9 us with runs of 128 pages, 59.9 us with 256).  Pages per block: as many as still leave every SM four blocks, so that
   // small problems spread out.  TWL_SCORES_MMA_SHAPE=1 selects 8 warps x 256 pages, one step in
   // flight (for measurement).
   static const int forced = [] {

@@ -15,6 +15,7 @@
 // the three reductions of a round are fused into one pass, and a round limit replaces the
 // open-ended loop.
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -236,7 +237,7 @@ __device__ __forceinline__ Red4 block_red4(float z, float s, float a, float b, f
   return r;
 }
 
-// Working list of the narrowing search: one private segment per warp, holding values and their
+// The cut list of the fused pruner: one private segment per warp, holding values and their
 // offsets inside the owning warp's slice of the row (so that the kept tokens can be written
 // from the list, in row order, without another pass over the row).
 struct SearchList {
@@ -245,71 +246,140 @@ struct SearchList {
   int seg_cap;
 };
 
-struct SearchResult {
-  float low;
-  bool in_list;  // every element above `low` is in the list
-  int my_cnt;    // entries in this warp's segment (valid when in_list)
-};
+// Walks the entries col[0], col[32], ... col[32 * (cnt - 1)] of a lane's column, `BATCH` loads at a
+// time ahead of the calls of f (which may store to entries already read), so that the loads of a
+// batch do not wait for one another.  Missing entries of the last batch read as -1, a value outside
+// every window of non-negative numbers.
+template <int BATCH, typename F>
+__device__ __forceinline__ void walk_column(const float* col, int cnt, F f) {
+  for (int j0 = 0; j0 < cnt; j0 += BATCH) {
+    float e[BATCH];
+#pragma unroll
+    for (int k = 0; k < BATCH; ++k) e[k] = (j0 + k < cnt) ? col[32 * (j0 + k)] : -1.f;
+#pragma unroll
+    for (int k = 0; k < BATCH; ++k) f(e[k]);
+  }
+}
+
+// Block-wide (sum, min, max) of non-negative values in one barrier, three warp-reduce instructions
+// a level.  The minimum and the maximum are taken on the bit patterns, which order like the values.
+// The sum is taken in fixed point: every lane's partial sum (fp32) is rounded to a multiple of
+// total * 2^-30, `total` being the sum of the whole row (no sum of parts exceeds it), and the
+// integers are added - exact, so the result does not depend on the order, at a resolution finer
+// than the rounding of an fp32 sum of that many terms.  scale = 2^30 / total, inv_scale = 1 / scale.
+// `buf` holds 3*32 words and must not be the buffer used by the previous call.
+__device__ __forceinline__ unsigned fix_from(float s, float scale) { return __float2uint_rn(s * scale); }
+__device__ __forceinline__ float warp_sum_fix(float s, float scale, float inv_scale) {
+  return (float)__reduce_add_sync(0xffffffffu, fix_from(s, scale)) * inv_scale;
+}
+template <int THREADS>
+__device__ __forceinline__ Red3 block_red3_pos(float s, float a, float b, float scale, float inv_scale, float* buf) {
+  constexpr int NW = THREADS / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned* ubuf = reinterpret_cast<unsigned*>(buf);
+  const unsigned us = __reduce_add_sync(0xffffffffu, fix_from(s, scale));
+  const unsigned ua = __reduce_min_sync(0xffffffffu, __float_as_uint(a));
+  const unsigned ub = __reduce_max_sync(0xffffffffu, __float_as_uint(b));
+  if (lane == 0) {
+    ubuf[warp] = us;
+    ubuf[32 + warp] = ua;
+    ubuf[64 + warp] = ub;
+  }
+  __syncthreads();
+  Red3 r;
+  r.s = (float)__reduce_add_sync(0xffffffffu, lane < NW ? ubuf[lane] : 0u) * inv_scale;
+  r.a = __uint_as_float(__reduce_min_sync(0xffffffffu, lane < NW ? ubuf[32 + lane] : 0x7f800000u));
+  r.b = __uint_as_float(__reduce_max_sync(0xffffffffu, lane < NW ? ubuf[64 + lane] : 0u));
+  return r;
+}
 
 // The same search with the row in shared memory and a shrinking working set.
 //
-// Once `low` has risen, elements <= low can no longer change any of the three reductions of a
-// round: S sums x > mid > low, a = min{x > low}, and b = max({x <= high} U {low}) is at least low
-// anyway.  So whenever a round raises low, every warp squeezes its share of the current working
-// set (its slice of the row, later its own segment of the list) into its segment of the list
-// and the following rounds walk the list only; a squeeze whose survivors do not fit is dropped and
-// the search goes on over the old set.  Ordering inside a segment is fixed by lane order, so
-// results do not depend on scheduling.
+// A round needs only the elements of the window (low, high]: S sums x > mid, and every x > high is
+// above all later pivots too, so its value can be added once and for all to a running sum; a =
+// min{x > low} starts at high and b = max{x <= high} starts at low, so elements outside the window
+// never move them.  The window halves with every round.  So each lane copies the window elements
+// among the ones it reads (four consecutive slots of every 128 of its warp's slice of the row)
+// into a column of its own in the warp's part of `region`, adds what lies above the window to its
+// share of the running sum, and from then on walks - and keeps squeezing, in place - that column
+// instead of the row.  A warp in which some lane's column overflows stays on the row for this
+// round and tries again in the next.  Nothing depends on scheduling: every lane's order is fixed.
+// The row itself is left as it is (the compaction reads it afterwards).
 //
-// The search starts from the state (low, high, round) the caller hands over (0, x0, 0 for a fresh
-// search; the state at which the short-list search below gave up otherwise), with the whole row as
-// the working set.
-//   x: n floats (n % 4 == 0); red: 256 words; p, eps in the units of x.
+// Starts from the state (low, high, round) the caller hands over (0, x0, 0 for a fresh search; the
+// state at which the short-list search below gave up otherwise).
+//   x: n non-negative floats (n % 4 == 0); region: NW * seg_floats floats (seg_floats % 32 == 0);
+//   red: 192 words; p, eps in the units of x; total = the sum of x.  Returns low.
 template <int THREADS>
-__device__ SearchResult topp_search_narrowing(const float* x, int n, SearchList L, int* seg_cnt, float low,
-                                              float high, int round, float p, float eps, float* red,
-                                              int32_t* status) {
+__device__ float topp_search_window(const float* x, int n, float* region, int seg_floats, float low, float high,
+                                    int round, float p, float eps, float total, float* red, int32_t* status) {
+  const float scale = 1073741824.f / total, inv_scale = total * (1.f / 1073741824.f);
   constexpr int NW = THREADS / 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const float4* x4 = reinterpret_cast<const float4*>(x);
-  const int n4 = n >> 2;
-  // slice of the row owned by this warp when the row is squeezed (whole float4 groups per lane)
   const int slice = ((n + NW - 1) / NW + 127) & ~127;
-  const int seg_cap = L.seg_cap;
-  float* const my_val = L.vals + warp * seg_cap;
-  uint16_t* const my_rel = L.rel + warp * seg_cap;
-  bool in_list = false;
-  int my_cnt = 0;    // elements in this warp's segment (valid when in_list)
-  int total = n;     // size of the working set
-  int flip = 0;      // the two reduction buffers alternate
+  const int begin = warp * slice, end = min(n, begin + slice);
+  float* const col = region + warp * seg_floats + lane;  // entry j of this lane: col[32 * j]
+  const int lane_cap = seg_floats >> 5;
+  bool on_list = false;  // warp-uniform
+  int cnt = 0;           // entries in this lane's column
+  float s_drop = 0.f;    // this lane's share of the sum of everything dropped above the window
+  bool first = round == 0;  // the window of a fresh search's first round is (0, x0]: nearly the whole row
+  int flip = 0;          // the two reduction buffers alternate
   while (true) {
     const float mid = (low + high) * 0.5f;
-    float s = 0.f, a = high, b = low;
-    if (!in_list) {
-      for (int i = threadIdx.x; i < n4; i += THREADS) {
-        const float4 v = x4[i];
+    float s, a = high, b = low;
+    if (!on_list) {
+      s = 0.f;
+      float sd = 0.f;
+      int w = 0;
+      const bool attempt = !first && lane_cap > 0;
+      for (int i0 = begin; i0 < end; i0 += 128) {
+        const int i = i0 + lane * 4;
+        if (i >= end) continue;
+        const float4 v = *reinterpret_cast<const float4*>(x + i);  // n % 4 == 0: whole groups
         const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
+          const bool gh = e[k] > high;
+          const bool keep = (e[k] > low) && !gh;
           s += (e[k] > mid) ? e[k] : 0.f;
-          a = (e[k] > low) ? fminf(a, e[k]) : a;
-          b = (e[k] <= high) ? fmaxf(b, e[k]) : b;
+          a = keep ? fminf(a, e[k]) : a;
+          b = keep ? fmaxf(b, e[k]) : b;
+          if (attempt) {
+            sd += gh ? e[k] : 0.f;
+            if (keep) {
+              if (w < lane_cap) col[32 * w] = e[k];
+              ++w;
+            }
+          }
         }
       }
-    } else {
-      for (int i = lane; i < my_cnt; i += 32) {
-        const float e = my_val[i];
-        s += (e > mid) ? e : 0.f;
-        a = (e > low) ? fminf(a, e) : a;
-        b = (e <= high) ? fmaxf(b, e) : b;
+      if (attempt && !__any_sync(0xffffffffu, w > lane_cap)) {
+        on_list = true;
+        cnt = w;
+        s_drop = sd;
       }
+    } else {
+      s = s_drop;
+      float sd = s_drop;
+      int w = 0;
+      walk_column<4>(col, cnt, [&](float e) {
+        const bool gh = e > high;
+        const bool keep = (e > low) && !gh;
+        s += (e > mid) ? e : 0.f;
+        sd += gh ? e : 0.f;
+        a = keep ? fminf(a, e) : a;
+        b = keep ? fmaxf(b, e) : b;
+        if (keep) col[32 * w++] = e;  // w never passes the entries already read
+      });
+      cnt = w;
+      s_drop = sd;
     }
-    const Red3 r = block_red3<THREADS>(s, a, b, red + flip * 96);
+    first = false;
+    const Red3 r = block_red3_pos<THREADS>(s, a, b, scale, inv_scale, red + flip * 96);
     flip ^= 1;
-    bool rose = false;
     if (r.s >= p) {
       low = mid;
-      rose = true;
     } else {
       high = fminf(mid, r.b);
     }
@@ -319,72 +389,8 @@ __device__ SearchResult topp_search_narrowing(const float* x, int n, SearchList 
       if (threadIdx.x == 0) raise_flag(status, TWL_FLAG_ITER_CAP);
       break;
     }
-    if (rose && total > 32) {
-      int cnt = 0;
-      if (!in_list) {
-        const int begin = warp * slice, end = min(n, begin + slice);
-        for (int i0 = begin; i0 < end; i0 += 128) {
-          const int i = i0 + lane * 4;
-          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (i < end) v = *reinterpret_cast<const float4*>(x + i);  // n % 4 == 0: whole groups
-          const float e[4] = {v.x, v.y, v.z, v.w};
-          int c = 0;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) c += e[k] > low ? 1 : 0;
-          if (__ballot_sync(0xffffffffu, c > 0) == 0) continue;
-          const int inc = warp_incl_scan(c);
-          int pos = cnt + inc - c;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            if (e[k] > low) {
-              if (pos < seg_cap) {
-                my_val[pos] = e[k];
-                my_rel[pos] = (uint16_t)(i - begin + k);
-              }
-              ++pos;
-            }
-          }
-          cnt += __shfl_sync(0xffffffffu, inc, 31);
-        }
-      } else {
-        for (int i0 = 0; i0 < my_cnt; i0 += 32) {
-          const bool in = i0 + lane < my_cnt;
-          const float e = in ? my_val[i0 + lane] : 0.f;
-          const uint16_t rl = in ? my_rel[i0 + lane] : (uint16_t)0;
-          const bool keep = e > low;
-          const unsigned m = __ballot_sync(0xffffffffu, keep);
-          const int pos = cnt + __popc(m & ((1u << lane) - 1));
-          __syncwarp();  // every lane has read its element before the front is overwritten
-          if (keep) {
-            my_val[pos] = e;
-            my_rel[pos] = rl;
-          }
-          cnt += __popc(m);
-        }
-      }
-      if (lane == 0) seg_cnt[warp] = cnt;
-      __syncthreads();
-      bool fits = true;
-      int sum = 0;
-#pragma unroll 1
-      for (int w = 0; w < NW; ++w) {
-        const int cw = seg_cnt[w];
-        fits = fits && (cw <= seg_cap);
-        sum += cw;
-      }
-      __syncthreads();  // seg_cnt is rewritten by the next squeeze
-      if (fits) {       // (a list-to-list squeeze always fits)
-        in_list = true;
-        my_cnt = cnt;
-        total = sum;
-      }
-    }
   }
-  SearchResult res;
-  res.low = low;
-  res.in_list = in_list;
-  res.my_cnt = my_cnt;
-  return res;
+  return low;
 }
 
 // The search on a short list, run by ONE warp without any block-wide barrier.
@@ -398,15 +404,18 @@ __device__ SearchResult topp_search_narrowing(const float* x, int n, SearchList 
 // few hundred tokens - the case the pruner exists for - are searched entirely here, at a fraction
 // of a microsecond per round instead of a block-wide pass.  When the pivot would drop below the
 // cut with low still 0 the warp stops and hands its state (low = 0, high, round) to the block.
-// Returns true when the search is finished.  solo: n_solo values; lane-strided sums, fixed order.
+// Lane-strided sums in a fixed order.  (Squeezing the list to the window (low, high] as the rounds
+// go, as the block-wide search does, made this search slower: its lists shrink only in the last
+// rounds, and the bookkeeping doubles the work per element before that.)
 struct SoloState {
   float low, high;
   int round, done;
 };
 __device__ __forceinline__ SoloState topp_search_solo(const float* solo, int n_solo, float x0, float cut,
                                                       float a_pos, float b_rest, float p, float eps,
-                                                      int32_t* status) {
+                                                      float total, int32_t* status) {
   const int lane = threadIdx.x & 31;
+  const float scale = 1073741824.f / total, inv_scale = total * (1.f / 1073741824.f);
   SoloState st;
   st.low = 0.f; st.high = x0; st.round = 0; st.done = 0;
   while (true) {
@@ -420,9 +429,9 @@ __device__ __forceinline__ SoloState topp_search_solo(const float* solo, int n_s
       a = (e > low) ? fminf(a, e) : a;
       b = (e <= high) ? fmaxf(b, e) : b;
     }
-    s = warp_sum(s);
-    a = warp_min(a);
-    b = warp_max(b);
+    s = warp_sum_fix(s, scale, inv_scale);  // fixed point, as in block_red3_pos
+    a = __uint_as_float(__reduce_min_sync(0xffffffffu, __float_as_uint(a)));  // non-negative values
+    b = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(b)));
     if (low == 0.f) {
       a = fminf(a, a_pos);   // smallest positive element of the whole row (a_pos <= high always)
       b = fmaxf(b, b_rest);  // largest unlisted element: b_rest <= cut <= mid < high
@@ -439,6 +448,55 @@ __device__ __forceinline__ SoloState topp_search_solo(const float* solo, int n_s
     }
     if (st.round >= kSearchRoundCap) {
       if (lane == 0) raise_flag(status, TWL_FLAG_ITER_CAP);
+      st.done = 1;
+      break;
+    }
+  }
+  return st;
+}
+
+// The same short-list search run by the whole block: every warp walks its own segment of the cut
+// list where it lies (`my_val`, `my_cnt` entries; the list stays as it is, the compaction reads it)
+// and a round costs one block-wide reduction.  For blocks that have an SM to themselves - there
+// one warp searching alone would leave the other schedulers idle - and for lists of any length.
+template <int THREADS>
+__device__ SoloState topp_search_cut_list(const float* my_val, int my_cnt, float x0, float cut, float a_pos,
+                                          float b_rest, float p, float eps, float total, float* red,
+                                          int32_t* status) {
+  const int lane = threadIdx.x & 31;
+  const float scale = 1073741824.f / total, inv_scale = total * (1.f / 1073741824.f);
+  SoloState st;
+  st.low = 0.f; st.high = x0; st.round = 0; st.done = 0;
+  int flip = 0;
+  while (true) {
+    const float low = st.low, high = st.high;
+    const float mid = (low + high) * 0.5f;
+    if (low == 0.f && mid < cut) break;  // the search over the whole row takes over from this state
+    float s = 0.f, a = high, b = low;
+    for (int i = lane; i < my_cnt; i += 32) {
+      const float e = my_val[i];
+      s += (e > mid) ? e : 0.f;
+      a = (e > low) ? fminf(a, e) : a;
+      b = (e <= high) ? fmaxf(b, e) : b;
+    }
+    Red3 r = block_red3_pos<THREADS>(s, a, b, scale, inv_scale, red + flip * 96);
+    flip ^= 1;
+    if (low == 0.f) {
+      r.a = fminf(r.a, a_pos);
+      r.b = fmaxf(r.b, b_rest);
+    }
+    if (r.s >= p) {
+      st.low = mid;
+    } else {
+      st.high = fminf(mid, r.b);
+    }
+    ++st.round;
+    if (!(r.b - r.a > eps)) {
+      st.done = 1;
+      break;
+    }
+    if (st.round >= kSearchRoundCap) {
+      if (threadIdx.x == 0) raise_flag(status, TWL_FLAG_ITER_CAP);
       st.done = 1;
       break;
     }
@@ -525,13 +583,13 @@ struct PruneParams {
   float* out_threshold;
   float* out_weights;  // [rows][index_stride] un-normalised softmax weight of each kept token, or nullptr
   int32_t* status;
-  int stride, max_k, B, Hq, index_stride, row_cap, list_cap;
+  int stride, max_k, B, Hq, index_stride, row_cap, list_cap, seg_floats;
   int mode;  // 0: softmax + top-p search; 1: keep scores above (score of token 0) - top_p_val
   float top_p_val;
 };
 
 template <int THREADS, bool IN_SMEM>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, THREADS == 1024 ? 1 : THREADS == 512 ? 3 : 5)
 topp_prune_kernel(const PruneParams p) {
   extern __shared__ __align__(16) float smem[];
   constexpr int NW = THREADS / 32;
@@ -569,11 +627,22 @@ topp_prune_kernel(const PruneParams p) {
   {
     const float4* s4 = reinterpret_cast<const float4*>(src);  // stride and n are multiples of 16
     float4* r4 = reinterpret_cast<float4*>(row);
-#pragma unroll 4
-    for (int i = threadIdx.x; i < n / 4; i += THREADS) {
-      const float4 v = s4[i];
-      if (IN_SMEM) r4[i] = v;
-      m = fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+    // all loads of a row in shared memory are issued before the first is used: a block that has
+    // its SM to itself has nothing else to hide their latency behind
+    constexpr int kLd = !IN_SMEM ? 4 : THREADS == 1024 ? 10 : 4;
+    const int n4 = n / 4;
+    for (int i0 = threadIdx.x; i0 < n4; i0 += kLd * THREADS) {
+      float4 v[kLd];
+#pragma unroll
+      for (int k = 0; k < kLd; ++k)
+        if (i0 + k * THREADS < n4) v[k] = s4[i0 + k * THREADS];
+#pragma unroll
+      for (int k = 0; k < kLd; ++k) {
+        if (i0 + k * THREADS < n4) {
+          if (IN_SMEM) r4[i0 + k * THREADS] = v[k];
+          m = fmaxf(fmaxf(m, fmaxf(v[k].x, v[k].y)), fmaxf(v[k].z, v[k].w));
+        }
+      }
     }
   }
   Red3 r1 = block_red3<THREADS>(0.f, 0.f, m, red);
@@ -630,6 +699,7 @@ topp_prune_kernel(const PruneParams p) {
       if (i < s_end) *reinterpret_cast<float4*>(row + i) = v;
       const float e[4] = {v.x, v.y, v.z, v.w};
       z += (v.x + v.y) + (v.z + v.w);
+      if (first_cnt > L.seg_cap) continue;  // the list has overflowed: this row goes to the block-wide search
       int c = 0;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -673,12 +743,21 @@ topp_prune_kernel(const PruneParams p) {
       float lo0 = 0.f, hi0 = x0;
       int round0 = 0;
       bool done = false;
-      if (fits && total <= kSoloCap) {
+      if (THREADS == 1024 && fits) {
+        // this block has its SM to itself: all warps run the rounds, each on its own segment
+        __syncthreads();  // seg_cnt has been read by everyone; red is free
+        const SoloState st = topp_search_cut_list<THREADS>(my_val, first_cnt, x0, cut, r2.a, r2.b, p_z, eps_z, r2.z,
+                                                           red, p.status);
+        lo0 = st.low;
+        hi0 = st.high;
+        round0 = st.round;
+        done = st.done != 0;
+      } else if (fits && total <= kSoloCap) {
         // the collected elements side by side, then one warp runs the rounds on them alone
         for (int i = lane; i < first_cnt; i += 32) solo[my_off + i] = my_val[i];
         __syncthreads();
         if (warp == 0) {
-          const SoloState st = topp_search_solo(solo, total, x0, cut, r2.a, r2.b, p_z, eps_z, p.status);
+          const SoloState st = topp_search_solo(solo, total, x0, cut, r2.a, r2.b, p_z, eps_z, r2.z, p.status);
           if (lane == 0) {
             red[0] = st.low;
             red[1] = st.high;
@@ -700,11 +779,9 @@ topp_prune_kernel(const PruneParams p) {
         from_list = true;
         list_cnt = first_cnt;
       } else {
-        const SearchResult res = topp_search_narrowing<THREADS>(row, n, L, seg_cnt, lo0, hi0, round0, p_z, eps_z,
-                                                                red, p.status);
-        low = res.low;
-        from_list = res.in_list;
-        list_cnt = res.my_cnt;
+        // the cut list is dead from here on: its memory is the working area of the block-wide search
+        low = topp_search_window<THREADS>(row, n, L.vals, p.seg_floats, lo0, hi0, round0, p_z, eps_z, r2.z, red,
+                                          p.status);
       }
     }
   } else {
@@ -767,32 +844,30 @@ topp_prune_kernel(const PruneParams p) {
     const int inc_w = warp_incl_scan(lane < NW ? wsum[lane] : 0);
     base = __shfl_sync(0xffffffffu, inc_w, NW - 1);                // kept tokens of the row
     int off = __shfl_sync(0xffffffffu, inc_w, warp) - my_cnt;      // exclusive prefix of this warp
+    // a run of 128 slots is first looked at four slots per lane; where it holds kept tokens it is
+    // walked again one slot per lane, so that a warp's stores go to consecutive addresses
+    const unsigned lt_mask = (1u << lane) - 1u;
     for (int i0 = s_begin; i0 < s_end; i0 += 128) {
       const int i = i0 + lane * 4;
       float4 v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);  // never above any cut
       if (i < s_end) v = *reinterpret_cast<const float4*>(row + i);
-      const float e[4] = {v.x, v.y, v.z, v.w};
-      int c = 0;
+      const bool any = (v.x > low) || (v.y > low) || (v.z > low) || (v.w > low);
+      if (__ballot_sync(0xffffffffu, any) == 0) continue;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) c += e[k] > low ? 1 : 0;
-      if (__ballot_sync(0xffffffffu, c > 0) == 0) continue;
-      const int inc = warp_incl_scan(c);
-      if (c) {
-        const int page = has_cand ? cand[i / kPage] : (i / kPage);  // i % 4 == 0: one page
-        const int tok0 = page * kPage + (i % kPage);
-        int pos = off + inc - c;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          if (e[k] > low) {
-            if (pos < p.index_stride) {
-              out[pos] = tok0 + k;
-              if (out_w) out_w[pos] = thresh_mode ? fexp(e[k]) : e[k] * out_scale;
-            }
-            ++pos;
-          }
+      for (int sub = 0; sub < 4; ++sub) {
+        const int j = i0 + sub * 32 + lane;
+        const float e = j < s_end ? row[j] : -INFINITY;
+        const bool keep = e > low;
+        const unsigned mk = __ballot_sync(0xffffffffu, keep);
+        if (mk == 0) continue;
+        const int pos = off + __popc(mk & lt_mask);
+        if (keep && pos < p.index_stride) {
+          const int page = has_cand ? cand[j / kPage] : (j / kPage);
+          out[pos] = page * kPage + (j % kPage);
+          if (out_w) out_w[pos] = thresh_mode ? fexp(e) : e * out_scale;
         }
+        off += __popc(mk);
       }
-      off += __shfl_sync(0xffffffffu, inc, 31);
     }
   } else {
     int my_cnt = 0;
@@ -831,16 +906,30 @@ topp_prune_kernel(const PruneParams p) {
 template <int THREADS>
 static int launch_prune(const PruneParams& p, int rows, int n_max, cudaStream_t st) {
   if (n_max <= kPruneRowCap) {
+    constexpr int NW = THREADS / 32;
+    constexpr size_t kSmemMax = 227 * 1024, kPerBlockReserve = 1024;
     PruneParams q = p;
     q.row_cap = (n_max + 3) & ~3;
-    q.list_cap = std::max(q.row_cap / 4, 32 * (THREADS / 32));  // entries: a float and a uint16 each
-    const size_t smem = (((kPruneHeaderWords + (size_t)q.row_cap + q.list_cap) * sizeof(float) + (size_t)q.list_cap * 2) + 15) & ~(size_t)15;
+    q.list_cap = (std::max(q.row_cap / 4, 32 * NW) + 63) & ~63;  // entries: a float and a uint16 each
+    const size_t fixed = (kPruneHeaderWords + (size_t)q.row_cap) * sizeof(float);
+    const size_t list_bytes = (size_t)q.list_cap * 6;
+    // The block-wide search works in the cut list's memory; a block that has its SM to itself
+    // anyway gets what is left of the SM's shared memory for it, up to one float per slot of the row.
+    const int per_sm = (int)std::min<size_t>(2048 / THREADS, kSmemMax / (fixed + list_bytes + kPerBlockReserve));
+    if (per_sm < 1) return TWL_ERR_TOO_LARGE;
+    const size_t room = per_sm == 1 ? kSmemMax - kPerBlockReserve - fixed : list_bytes;
+    const size_t region = std::max(list_bytes, std::min(room, (size_t)q.row_cap * sizeof(float)));
+    q.seg_floats = (int)(region / sizeof(float) / NW) & ~31;
+    const size_t smem = (fixed + region + 15) & ~(size_t)15;
     auto kern = topp_prune_kernel<THREADS, true>;
     TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     TWL_CUDA_TRY(launch_chain(kern, dim3(rows), dim3(THREADS), smem, st, static_cast<const PruneParams&>(q)));
   } else {
+    PruneParams q = p;
+    q.seg_floats = 0;
     auto kern = topp_prune_kernel<THREADS, false>;
-    TWL_CUDA_TRY(launch_chain(kern, dim3(rows), dim3(THREADS), kPruneHeaderWords * sizeof(float), st, p));
+    TWL_CUDA_TRY(launch_chain(kern, dim3(rows), dim3(THREADS), kPruneHeaderWords * sizeof(float), st,
+                              static_cast<const PruneParams&>(q)));
   }
   TWL_CHECK_LAUNCH();
   return TWL_OK;
