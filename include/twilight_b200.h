@@ -133,9 +133,12 @@ TWL_API int twl_quest_select(const void* q, int dtype, const void* kmeta, const 
  * query head (by default such rows use warp-private 16-byte async copies), add 64 for warp-private
  * rings fed by bulk copies (two 1280-byte cp.async.bulk per stage on the warp's own mbarrier: the
  * default's block shape and bytes in flight, the copy engine instead of per-lane copies), add 32 for the
- * integer-dot kernel on query-head groups (by default groups of 2, 4 or 8 heads that share a KV
- * head's pages are scored with 16-bit tensor-core tiles: codes and q are exact in the model dtype,
- * accumulation is fp32).  The non-default variants exist for measurement. */
+ * integer-dot kernel on query-head groups, add 256 for 16-bit float tensor-core tiles on them (codes
+ * and q exact in fp16, fp32 accumulation).  By default groups of 2, 4 or 8 heads that share a KV
+ * head's pages are scored with 8-bit integer tensor-core tiles: one m16n8k32 tile per page and
+ * 32-channel quantisation group against the high and one against the low bytes of q as 13-bit
+ * block-scaled integers (the integer dot product is exact; q is rounded to 2^-13 of the head's
+ * largest element, as in the single-head kernel).  The non-default variants exist for measurement. */
 TWL_API int twl_estimate_int4(const void* q, int dtype, const uint8_t* k4_pages,
                       const int32_t* kv_indptr, const int32_t* kv_indices,
                       const int32_t* kv_last_page_len, const int32_t* cand_pages,

@@ -749,34 +749,40 @@ def test_attention_workspace_and_bad_index_handling():
 @pytest.mark.parametrize("hq,hkv,dt", [(8, 2, torch.bfloat16), (8, 1, torch.bfloat16), (4, 1, torch.float16),
                                        (16, 2, torch.float16), (4, 2, torch.bfloat16)])
 def test_group_estimator_tensor_core_equals_integer_dot(hq, hkv, dt):
-    """Default estimator for query-head groups (16-bit tensor-core tiles) against the integer-dot
-    group kernel (variant +32) and the fp64 oracle, ragged lengths with odd page counts."""
+    """Default estimator for query-head groups (8-bit integer tensor-core tiles, q as 13-bit
+    block-scaled integers like the single-head kernel) and its 16-bit float tile form (variant +256)
+    against the integer-dot group kernel (variant +32) and the fp64 oracle, ragged lengths with odd
+    page counts."""
     lens = [1, 17, 33, 1000, 2049, 4000, 16 * 129]
     q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=dt, device=DEV, seed=61,
                                   recipe="mid", shuffle_pages=True)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     kw = dict(max_pages=cache.max_pages, status=status)
-    a = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len, **kw)
     b_ = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
                            variant=3 + 32, **kw)
-    assert int(status.item()) == 0
     g = hq // hkv
-    worst = 0.0
-    for b, n in enumerate(lens):
-        npg = (n + PAGE - 1) // PAGE
-        ra, rb = a[b, :, : npg * PAGE], b_[b, :, : npg * PAGE]
-        assert torch.equal(torch.isinf(ra), torch.isinf(rb))
-        fin = torch.isfinite(ra)
-        scale = max(1.0, float(rb[fin].abs().max()))
-        assert float((ra[fin] - rb[fin]).abs().max()) <= 2e-3 * scale
-        for h in (0, hq - 1):
-            want, _ = U.oracle_scores_row(q, cache, b, h, g)
-            got = ra[h].cpu().numpy()
-            f = np.isfinite(want)
-            assert np.array_equal(np.isfinite(got), f)
-            worst = max(worst, float(np.abs(got[f] - want[f]).max()) / max(1.0, float(np.abs(want[f]).max())))
-    U.record("group_estimator_mma", hq=hq, hkv=hkv, dtype=str(dt), worst_rel=worst)
-    assert worst <= 2e-4     # exact products, fp32 accumulation: tighter than the integer-dot form's 2e-3
+    # (variant, bound on the error relative to the row's largest |logit|): the float tiles multiply
+    # exact values and accumulate in fp32; the integer tiles round q to 13 bits first
+    for variant, bound in ((0, 2e-4), (3 + 256, 2e-4)):
+        a = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
+                              variant=variant, **kw)
+        assert int(status.item()) == 0
+        worst = 0.0
+        for b, n in enumerate(lens):
+            npg = (n + PAGE - 1) // PAGE
+            ra, rb = a[b, :, : npg * PAGE], b_[b, :, : npg * PAGE]
+            assert torch.equal(torch.isinf(ra), torch.isinf(rb))
+            fin = torch.isfinite(ra)
+            scale = max(1.0, float(rb[fin].abs().max()))
+            assert float((ra[fin] - rb[fin]).abs().max()) <= 2e-3 * scale
+            for h in (0, hq - 1):
+                want, _ = U.oracle_scores_row(q, cache, b, h, g)
+                got = ra[h].cpu().numpy()
+                f = np.isfinite(want)
+                assert np.array_equal(np.isfinite(got), f)
+                worst = max(worst, float(np.abs(got[f] - want[f]).max()) / max(1.0, float(np.abs(want[f]).max())))
+        U.record("group_estimator_mma", variant=variant, hq=hq, hkv=hkv, dtype=str(dt), worst_rel=worst)
+        assert worst <= bound, (variant, worst)
 
 
 @pytest.mark.parametrize("hq,hkv,dt", [(8, 1, torch.bfloat16), (8, 2, torch.float16), (32, 4, torch.bfloat16)])

@@ -60,6 +60,9 @@ struct AttParams {
   const float* weights;  // [rows][index_stride] softmax weights of the kept tokens, or nullptr
   int32_t* group_flags;  // [batch*Hkv] 1 = the (sequence, KV head) row is served by the group kernel; or nullptr
   int index_stride, rows, Hq, Hkv, num_pages_total, chunk;
+  int group_skip_rows;  // group kernel: do not fetch token rows that no head of the group keeps
+  int group_chunk_pages;  // group kernel: pages of the longest chunk of a sequence of max_seq_pages pages
+  int max_seq_pages;      // upper bound of a sequence's page count (the physical page count if nothing better is known)
   float sm_scale;
 };
 
@@ -480,9 +483,8 @@ sparse_decode_attn_kernel(const AttParams p) {
 // which runs afterwards and skips those rows.
 constexpr int kGrpWarps = 2;
 constexpr int kGrpThreads = kGrpWarps * 32;
-constexpr int kGrpStages = 3;
 constexpr int kGrpStageBytes = 2 * kPage * kD * 2;                       // K page, then V page: 8 KiB
-constexpr int kGrpRingBytes = kGrpWarps * kGrpStages * kGrpStageBytes;   // 48 KiB per block
+__host__ __device__ constexpr int grp_ring_bytes(int stages) { return kGrpWarps * stages * kGrpStageBytes; }  // 16 KiB a stage
 constexpr int kGrpMaxChunkPages = 256;                                   // pages of one work item
 constexpr int kGrpMinChunkPages = 64;
 
@@ -519,14 +521,17 @@ __device__ __forceinline__ int warp_lower_bound(const int32_t* idx, int n, int k
   return lo;
 }
 
-template <typename T, int G>
+template <typename T, int G, int kGrpStages>
 __global__ void __launch_bounds__(kGrpThreads)
 group_decode_attn_kernel(const AttParams p) {
   static_assert(G == 2 || G == 4 || G == 8, "the group sits in the upper rows of one m16 tile");
   extern __shared__ __align__(128) unsigned char sm_dyn[];  // the rings; later the warps' results
-  __shared__ uint32_t sm_mask[G][kGrpMaxChunkPages / 2];    // kept-token bits, two pages a word
-  __shared__ uint16_t sm_upage[kGrpMaxChunkPages];          // pages of the chunk with any kept token
-  __shared__ int sm_uphys[kGrpMaxChunkPages];
+  // behind the rings, sized by the launch for the longest chunk any row can have (cpm pages):
+  const int cpm = p.group_chunk_pages;
+  int* const sm_uphys = reinterpret_cast<int*>(sm_dyn + grp_ring_bytes(kGrpStages));  // [cpm] where the pages lie
+  uint32_t* const sm_mask = reinterpret_cast<uint32_t*>(sm_uphys + cpm);   // [G][cpm / 2] kept-token bits, two pages a word
+  uint16_t* const sm_upage = reinterpret_cast<uint16_t*>(sm_mask + G * (cpm / 2));  // [cpm] pages with any kept token
+  uint16_t* const sm_ubits = sm_upage + cpm;                               // [cpm] which of their tokens any head keeps
   __shared__ int sm_nunion;
   __shared__ int sm_ticket[G];
 
@@ -541,7 +546,7 @@ group_decode_attn_kernel(const AttParams p) {
   int bud_l = 0;
   if (lane < G) bud_l = min(max(p.budget[row0 + lane], 0), p.index_stride);
   const int bud_sum = warp_sum_i(bud_l);
-  const bool mine = pages_b > 0 && pages_b <= kMaxChunksPerRow * kGrpMaxChunkPages &&
+  const bool mine = pages_b > 0 && pages_b <= kMaxChunksPerRow * cpm &&
                     (long long)bud_sum >= (long long)pages_b * kPage;
   if (c == 0 && tid == 0) p.group_flags[rkv] = mine ? 1 : 0;
   if (!mine) return;
@@ -552,7 +557,7 @@ group_decode_attn_kernel(const AttParams p) {
   const int p0 = c * cp, p1 = min(pages_b, p0 + cp), npg = p1 - p0;
 
   // ---- kept-token bits of every head for the pages of this chunk ----
-  for (int i = tid; i < G * (kGrpMaxChunkPages / 2); i += kGrpThreads) (&sm_mask[0][0])[i] = 0u;
+  for (int i = tid; i < G * (cpm / 2); i += kGrpThreads) sm_mask[i] = 0u;
   __syncthreads();
   bool bad = false;
   for (int hh = warp; hh < G; hh += kGrpWarps) {
@@ -569,13 +574,13 @@ group_decode_attn_kernel(const AttParams p) {
       const int tok = idx[i];
       const int pg = (tok >> 4) - p0;
       if (pg != cur) {
-        if (cur >= 0 && cur < npg) atomicOr(&sm_mask[hh][cur >> 1], bits << ((cur & 1) * 16));
+        if (cur >= 0 && cur < npg) atomicOr(&sm_mask[hh * (cpm / 2) + (cur >> 1)], bits << ((cur & 1) * 16));
         cur = pg;
         bits = 0;
       }
       bits |= 1u << (tok & 15);
     }
-    if (cur >= 0 && cur < npg) atomicOr(&sm_mask[hh][cur >> 1], bits << ((cur & 1) * 16));
+    if (cur >= 0 && cur < npg) atomicOr(&sm_mask[hh * (cpm / 2) + (cur >> 1)], bits << ((cur & 1) * 16));
   }
   __syncthreads();
   // ---- pages with any kept token, and where they lie ----
@@ -586,7 +591,7 @@ group_decode_attn_kernel(const AttParams p) {
       uint32_t u = 0;
       if (j < npg) {
 #pragma unroll
-        for (int hh = 0; hh < G; ++hh) u |= (sm_mask[hh][j >> 1] >> ((j & 1) * 16)) & 0xFFFFu;
+        for (int hh = 0; hh < G; ++hh) u |= (sm_mask[hh * (cpm / 2) + (j >> 1)] >> ((j & 1) * 16)) & 0xFFFFu;
       }
       int phys = -1;
       if (u != 0) {
@@ -600,6 +605,7 @@ group_decode_attn_kernel(const AttParams p) {
       if (phys >= 0) {
         const int pos = n_u + __popc(m & ((1u << lane) - 1));
         sm_upage[pos] = (uint16_t)j;
+        sm_ubits[pos] = (uint16_t)(p.group_skip_rows ? u : 0xFFFFu);
         sm_uphys[pos] = phys;
       }
       n_u += __popc(m);
@@ -630,9 +636,12 @@ group_decode_attn_kernel(const AttParams p) {
   const T* const vbase = reinterpret_cast<const T*>(p.v);
   // a page is 16 token rows of 256 bytes; chunk ch of token row r goes to position ch ^ (r & 7), which
   // keeps the copies and the 8-row matrix reads below free of bank conflicts
+  // Token rows that no head keeps are not fetched: their slots keep what an earlier page left there
+  // (zeros at first), finite values that the masked softmax multiplies by zero.
   auto issue = [&](int i, int slot) {
     if (i < my_n) {
       const int phys = sm_uphys[warp + i * kGrpWarps];
+      const uint32_t ub = sm_ubits[warp + i * kGrpWarps];
       const size_t off = ((size_t)phys * p.Hkv + kvh) * (kPage * kD);
       const unsigned char* ksrc = reinterpret_cast<const unsigned char*>(kbase + off) + lane * 16;
       const unsigned char* vsrc = reinterpret_cast<const unsigned char*>(vbase + off) + lane * 16;
@@ -641,12 +650,19 @@ group_decode_attn_kernel(const AttParams p) {
       for (int j = 0; j < 8; ++j) {
         const int r = 2 * j + (lane >> 4), ch = lane & 15;
         const uint32_t d = r * 256 + ((ch ^ (r & 7)) << 4);
-        cp_async16(dst + d, ksrc + j * 512);
-        cp_async16(dst + kPage * kD * 2 + d, vsrc + j * 512);
+        if ((ub >> r) & 1u) {
+          cp_async16(dst + d, ksrc + j * 512);
+          cp_async16(dst + kPage * kD * 2 + d, vsrc + j * 512);
+        }
       }
     }
     cp_async_commit();  // always commit so that group counting stays uniform
   };
+  {
+    uint4* z = reinterpret_cast<uint4*>(my_ring);
+    for (int i = lane; i < kGrpStages * kGrpStageBytes / 16; i += 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncwarp();
+  }
 #pragma unroll
   for (int i = 0; i < kGrpStages - 1; ++i) issue(i, i);
 
@@ -665,6 +681,9 @@ group_decode_attn_kernel(const AttParams p) {
   for (int i = 0; i < my_n; ++i) {
     cp_async_wait<kGrpStages - 2>();
     __syncwarp();
+    // the slot of the page worked on in the last iteration is refilled before this page is worked
+    // on: kGrpStages - 1 pages of the warp are in flight all the time
+    issue(i + kGrpStages - 1, fill);
     const uint32_t st = ring_s + slot * kGrpStageBytes;
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
     {
@@ -685,7 +704,7 @@ group_decode_attn_kernel(const AttParams p) {
       }
     }
     const int pg = sm_upage[warp + i * kGrpWarps];
-    const uint32_t bits = g < G ? (sm_mask[g < G ? g : 0][pg >> 1] >> ((pg & 1) * 16)) & 0xFFFFu : 0u;
+    const uint32_t bits = g < G ? (sm_mask[g * (cpm / 2) + (pg >> 1)] >> ((pg & 1) * 16)) & 0xFFFFu : 0u;
     float x[4];
     x[0] = (bits >> (2 * t)) & 1u ? s0[0] * p.sm_scale : -INFINITY;
     x[1] = (bits >> (2 * t + 1)) & 1u ? s0[1] * p.sm_scale : -INFINITY;
@@ -725,10 +744,7 @@ group_decode_attn_kernel(const AttParams p) {
         MmaTile<T>::run(o[2 * jj + 1], pa0, 0u, pa2, 0u, vb[jj][2], vb[jj][3]);  // channels 16jj+8 .. 16jj+15
       }
     }
-    __syncwarp();  // every lane is done with the slot before it is refilled
-    // (a four-stage ring refilled before the page is worked on - three pages in flight per warp all
-    // the time, but three blocks per SM instead of four - was slower: 1077 against 1001 us on config 2)
-    issue(i + kGrpStages - 1, fill);
+    __syncwarp();  // every lane is done with the slot before the next iteration refills it
     slot = (slot + 1 == kGrpStages) ? 0 : slot + 1;
     fill = (fill + 1 == kGrpStages) ? 0 : fill + 1;
   }
@@ -806,8 +822,26 @@ group_decode_attn_kernel(const AttParams p) {
 
 // Launch shared by the entry points.  `chain`: launch with programmatic stream serialization so
 // that the kernel's prologue overlaps the tail of the kernel before it.
-static int launch_attn(const AttParams& p, int dtype, size_t rows, int32_t index_stride, int32_t chunk,
+static int launch_attn(const AttParams& p_in, int dtype, size_t rows, int32_t index_stride, int32_t chunk,
                        bool chain, cudaStream_t st) {
+  // TWL_ATTN_FETCH_ALL=1: the group kernel fetches whole pages (for measurement)
+  static const bool fetch_all = [] {
+    const char* e = getenv("TWL_ATTN_FETCH_ALL");
+    return e && e[0] == '1';
+  }();
+  // TWL_ATTN_GROUP_STAGES=3: three pages per warp in the group kernel's rings instead of two
+  static const int grp_stages = [] {
+    const char* e = getenv("TWL_ATTN_GROUP_STAGES");
+    return (e && e[0] == '3') ? 3 : 2;
+  }();
+  AttParams p = p_in;
+  p.group_skip_rows = fetch_all ? 0 : 1;
+  // chunks are 64 * 2^k pages, at most kMaxChunksPerRow a row: the tables behind the rings are sized
+  // for the longest sequence the caller announces (sequences longer than that, or than 256 pages a
+  // chunk allow, stay with the per-head kernel)
+  p.group_chunk_pages = kGrpMinChunkPages;
+  while (p.group_chunk_pages < kGrpMaxChunkPages && p.group_chunk_pages * kMaxChunksPerRow < p.max_seq_pages)
+    p.group_chunk_pages *= 2;
   // enough blocks to give every row its own block when budgets are small, never more than the
   // machine holds at once (the schedule tables grow with the row count and may cost a block)
   const size_t max_items =
@@ -820,15 +854,20 @@ static int launch_attn(const AttParams& p, int dtype, size_t rows, int32_t index
     const int g = p.Hq / p.Hkv;
     const dim3 grid(kMaxChunksPerRow, (unsigned)(rows / g));
     if (grid.y > 65535) return TWL_ERR_TOO_LARGE;
+#define TWL_LAUNCH_GRP_S(TYPE, GG, SS)                                                             \
+  do {                                                                                             \
+    auto kern = group_decode_attn_kernel<TYPE, GG, SS>;                                            \
+    const int bytes = grp_ring_bytes(SS) + p.group_chunk_pages * (8 + 2 * GG);                     \
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));  \
+    if (chain) {                                                                                   \
+      TWL_CUDA_TRY(launch_chain(kern, grid, dim3(kGrpThreads), bytes, st, p));                     \
+    } else {                                                                                       \
+      kern<<<grid, kGrpThreads, bytes, st>>>(p);                                                   \
+    }                                                                                              \
+  } while (0)
 #define TWL_LAUNCH_GRP(TYPE, GG)                                                                   \
   do {                                                                                             \
-    auto kern = group_decode_attn_kernel<TYPE, GG>;                                                \
-    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGrpRingBytes)); \
-    if (chain) {                                                                                   \
-      TWL_CUDA_TRY(launch_chain(kern, grid, dim3(kGrpThreads), kGrpRingBytes, st, p));             \
-    } else {                                                                                       \
-      kern<<<grid, kGrpThreads, kGrpRingBytes, st>>>(p);                                           \
-    }                                                                                              \
+    if (grp_stages == 3) TWL_LAUNCH_GRP_S(TYPE, GG, 3); else TWL_LAUNCH_GRP_S(TYPE, GG, 2);        \
   } while (0)
     if (dtype == TWL_F16) {
       if (g == 2) TWL_LAUNCH_GRP(__half, 2); else if (g == 4) TWL_LAUNCH_GRP(__half, 4); else TWL_LAUNCH_GRP(__half, 8);
@@ -837,6 +876,7 @@ static int launch_attn(const AttParams& p, int dtype, size_t rows, int32_t index
     } else {
       return TWL_ERR_UNSUPPORTED;
     }
+#undef TWL_LAUNCH_GRP_S
 #undef TWL_LAUNCH_GRP
     TWL_CHECK_LAUNCH();
   }
@@ -896,7 +936,7 @@ static int attn_entry(const void* q, int dtype, const void* k_pages, const void*
                       int32_t index_stride, const int32_t* budget, const float* weights, int32_t batch,
                       int32_t num_q_heads, int32_t num_kv_heads, int32_t num_pages_total,
                       float sm_scale, void* out, void* workspace, size_t workspace_bytes,
-                      int32_t chunk, int32_t* status, void* stream) {
+                      int32_t chunk, int32_t* status, void* stream, int32_t max_seq_pages = 0) {
   using namespace twl;
   if (!q || !k_pages || !v_pages || !kv_indptr || !kv_indices || !indices || !budget || !out)
     return TWL_ERR_BAD_ARG;
@@ -926,8 +966,23 @@ static int attn_entry(const void* q, int dtype, const void* k_pages, const void*
   p.part_o = reinterpret_cast<float*>(ws);
   p.index_stride = index_stride; p.rows = (int)rows; p.Hq = num_q_heads; p.Hkv = num_kv_heads;
   p.num_pages_total = num_pages_total; p.chunk = chunk; p.sm_scale = sm_scale;
+  p.max_seq_pages = max_seq_pages > 0 ? std::min(max_seq_pages, num_pages_total) : num_pages_total;
   return launch_attn(p, dtype, rows, index_stride, chunk, true, reinterpret_cast<cudaStream_t>(stream));
 }
+
+// For the one-call step, which knows the longest sequence's page count.
+namespace twl {
+int sparse_decode_attn_bounded(const void* q, int dtype, const void* k_pages, const void* v_pages,
+                               const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* indices,
+                               int32_t index_stride, const int32_t* budget, const float* weights, int32_t batch,
+                               int32_t num_q_heads, int32_t num_kv_heads, int32_t num_pages_total, float sm_scale,
+                               void* out, void* workspace, size_t workspace_bytes, int32_t chunk, int32_t* status,
+                               void* stream, int32_t max_seq_pages) {
+  return attn_entry(q, dtype, k_pages, v_pages, kv_indptr, kv_indices, indices, index_stride, budget, weights,
+                    batch, num_q_heads, num_kv_heads, num_pages_total, sm_scale, out, workspace, workspace_bytes,
+                    chunk, status, stream, max_seq_pages);
+}
+}  // namespace twl
 
 extern "C" int twl_sparse_decode_attn(const void* q, int dtype, const void* k_pages,
                                       const void* v_pages, const int32_t* kv_indptr,
@@ -1032,5 +1087,6 @@ extern "C" int twl_sparse_decode_attn_static(const void* q, int dtype, const voi
   p.part_o = reinterpret_cast<float*>(ws + kStaticCounterBytes + kStaticMlBytes);
   p.index_stride = index_stride; p.rows = (int)rows; p.Hq = num_q_heads; p.Hkv = num_kv_heads;
   p.num_pages_total = num_pages_total; p.chunk = chunk; p.sm_scale = sm_scale;
+  p.max_seq_pages = num_pages_total;
   return launch_attn(p, dtype, rows, index_stride, chunk, false, st);
 }

@@ -260,4 +260,13 @@ struct MmaTile<__nv_bfloat16> {
   }
 };
 
+// twl_sparse_decode_attn for a caller that knows an upper bound of the sequences' page counts
+// (attend.cu; the group kernel sizes its shared-memory tables by it).
+int sparse_decode_attn_bounded(const void* q, int dtype, const void* k_pages, const void* v_pages,
+                               const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* indices,
+                               int32_t index_stride, const int32_t* budget, const float* weights, int32_t batch,
+                               int32_t num_q_heads, int32_t num_kv_heads, int32_t num_pages_total, float sm_scale,
+                               void* out, void* workspace, size_t workspace_bytes, int32_t chunk, int32_t* status,
+                               void* stream, int32_t max_seq_pages);
+
 }  // namespace twl

@@ -36,7 +36,7 @@ struct EstParams {
   const int32_t* cand_npages;
   float* scores;
   int32_t* status;
-  int max_k, B, Hq, Hkv, num_pages_total, stride, pages_per_block, force_ring, simt_group, bulk_warp;
+  int max_k, B, Hq, Hkv, num_pages_total, stride, pages_per_block, force_ring, simt_group, bulk_warp, f16_tiles;
   float sm_scale;
 };
 
@@ -1213,12 +1213,249 @@ estimate_int4_mma_group_kernel(const EstParams p) {
   cp_async_wait<0>();
 }
 
+// ---- the same on the integer tensor-core path --------------------------------------------------
+// m16n8k32 tiles of 8-bit integers: one tile spans exactly one 32-channel quantisation group, and a
+// code word turns into two operand registers with two masks and one shift (the 16-bit tiles above
+// spend nine instructions on it, and the logic unit is what bounds that kernel).  q is what the
+// single-head kernel uses: per head, q_d ~= (256*hi_d + lo_d) * 2^-e with |256*hi + lo| < 2^13, hi a
+// signed and lo an unsigned byte - two tiles per (page, group), one against the hi bytes and one
+// against the lo bytes, both exact in 32-bit integers.  The lo tile starts from the bit pattern of
+// 1.5 * 2^23, so that hi*256 + lo, read as a float, is 12582912 + the integer dot product (exact
+// below 2^22), and one exact subtraction leaves the dot product.
+//
+// Lane 4*g + t owns tokens g and g+8 of the page and word t of their 16-byte group chunk, as above:
+// the low nibbles of the word (channels 8t, 8t+2, 8t+4, 8t+6) fill the k-slots 4t..4t+3, the high
+// nibbles (the odd channels) the k-slots 16+4t..16+4t+3; B holds head g's bytes in the same order.
+struct ImmaTile {
+  // d = a (u8, 16x32) * b (8-bit, 32x8) + c, 32-bit integers
+  static __device__ __forceinline__ void run_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                uint32_t b0, uint32_t b1, int c) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
+  }
+  static __device__ __forceinline__ void run_u8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                uint32_t b0, uint32_t b1, int c) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
+  }
+};
+
+template <typename T, int G>
+__global__ void __launch_bounds__(kEstThreads, 2)
+estimate_int4_imma_group_kernel(const EstParams p) {
+  static_assert(G >= 2 && G <= 8, "one n8 tile holds the group");
+  extern __shared__ __align__(128) uint8_t sm_ring[];  // kEstWarps * kRingDepth * kWarpStageBytes
+  __shared__ int sm_phys[kWarpPagesPerBlock + 1];
+  __shared__ int sm_ntok[kWarpPagesPerBlock + 1];
+
+  const int row = blockIdx.y;
+  const int b = row / p.Hkv, kvh = row % p.Hkv;
+  const int h = kvh * G;  // first query head of the group
+  pdl_wait();  // q and the page table may come from the kernel before; scores may still be read by an older one
+  const int page_base = p.indptr[b];
+  const int n_seq_pages = p.indptr[b + 1] - page_base;
+  int n_pages = n_seq_pages;
+  if (n_pages > p.stride / kPage) {
+    n_pages = p.stride / kPage;
+    if (threadIdx.x == 0 && blockIdx.x == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+  }
+  const int first = blockIdx.x * kWarpPagesPerBlock;
+  if (first >= n_pages) return;
+  const int n_here = min(kWarpPagesPerBlock, n_pages - first);
+
+  const int tid = threadIdx.x;
+  if (tid <= kWarpPagesPerBlock) {  // one entry more than pages: the partner of an odd last page
+    int phys = -1, ntok = 0;
+    if (tid < n_here) {
+      const int seq_page = first + tid;
+      phys = p.indices[page_base + seq_page];
+      if (phys < 0 || phys >= p.num_pages_total) phys = -1;
+      if (phys < 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+      ntok = (seq_page == n_seq_pages - 1) ? p.last_len[b] : kPage;
+    }
+    sm_phys[tid] = phys;
+    sm_ntok[tid] = phys < 0 ? 0 : ntok;  // 0 tokens: every slot of the page scores -inf
+  }
+  __syncthreads();
+
+  const int lane = tid & 31, warp = tid >> 5;
+  const int gq = lane >> 2, t = lane & 3;
+  uint8_t* const ring = sm_ring + (size_t)warp * kRingDepth * kWarpStageBytes;
+  const uint32_t ring_u32 = smem_u32(ring);
+  const int n_pairs = (n_here + 1) >> 1;
+  const int my_pairs = (n_pairs > warp) ? (n_pairs - warp + kEstWarps - 1) / kEstWarps : 0;
+
+  // the five 16-byte copies of a stage, as in the 16-bit tile kernel
+  uint32_t src_off[5], dst_off[5];
+#pragma unroll
+  for (int c5 = 0; c5 < 5; ++c5) {
+    const int c = c5 * 32 + lane;
+    const int pgl = c >= 80 ? 1 : 0;
+    const int r = c - pgl * 80;
+    src_off[c5] = r * 16;
+    if (r < 64) {
+      const int tk = pgl * 16 + (r >> 2), g4 = r & 3;
+      dst_off[c5] = tk * 64 + (((g4 + (tk >> 1)) & 3) << 4);
+    } else {
+      dst_off[c5] = 2048 + (pgl * 16 + (r - 64)) * 16;
+    }
+  }
+  const bool third_is_second = lane >= 16;
+  const uint8_t* const k4_head = p.k4 + (size_t)kvh * kSlab;
+  const size_t page_stride = (size_t)p.Hkv * kSlab;
+
+  auto issue = [&](int i, int slot) {
+    if (i < my_pairs) {
+      const int pg0 = (warp + i * kEstWarps) * 2;
+      const uint32_t dst0 = ring_u32 + slot * kWarpStageBytes;
+      const uint8_t* const s0 = k4_head + (size_t)max(sm_phys[pg0], 0) * page_stride;
+      const uint8_t* const s1 = k4_head + (size_t)max(sm_phys[pg0 + 1], 0) * page_stride;
+      const uint8_t* const s2 = third_is_second ? s1 : s0;
+      cp_async16(dst0 + dst_off[0], s0 + src_off[0]);
+      cp_async16(dst0 + dst_off[1], s0 + src_off[1]);
+      cp_async16(dst0 + dst_off[2], s2 + src_off[2]);
+      cp_async16(dst0 + dst_off[3], s1 + src_off[3]);
+      cp_async16(dst0 + dst_off[4], s1 + src_off[4]);
+    }
+    cp_async_commit();  // always commit so that group counting stays uniform
+  };
+
+#pragma unroll
+  for (int i = 0; i < kRingDepth - 1; ++i) issue(i, i);
+
+  // B fragments of head gq (this lane's channels 8t..8t+7 of every group: even ones, then odd
+  // ones; hi and lo bytes), and of heads 2t and 2t+1, whose scores this lane ends up owning, the
+  // sums of the integers over each group's channels and the factor that undoes the scaling
+  uint32_t bh[4][2], bl[4][2];
+  float qs0[4], qs1[4];
+  float out_scale0, out_scale1;
+  {
+    const T* qrow = reinterpret_cast<const T*>(p.q) + (size_t)(b * p.Hq + h + (gq < G ? gq : 0)) * kD;
+    float qf[4][8];
+    float amax = 0.f;
+#pragma unroll
+    for (int grp = 0; grp < 4; ++grp) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(qrow) + 4 * grp + t);
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = Elem<T>::to_f2(u[k]);
+        qf[grp][2 * k] = gq < G ? f.x : 0.f;
+        qf[grp][2 * k + 1] = gq < G ? f.y : 0.f;
+        amax = fmaxf(amax, fmaxf(fabsf(qf[grp][2 * k]), fabsf(qf[grp][2 * k + 1])));
+      }
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));  // over the head's 128 channels
+    int e = (amax > 0.f && amax < INFINITY) ? (12 - ilogbf(amax)) : 0;  // amax * 2^e in [2^12, 2^13)
+    e = max(-100, min(100, e));
+    const float up = ldexpf(1.f, e);
+    const float undo = p.sm_scale * ldexpf(1.f, -e);
+    out_scale0 = __shfl_sync(0xffffffffu, undo, (2 * t) * 4);
+    out_scale1 = __shfl_sync(0xffffffffu, undo, (2 * t + 1) * 4);
+#pragma unroll
+    for (int grp = 0; grp < 4; ++grp) {
+      int sum = 0;
+      uint32_t he = 0, ho = 0, le = 0, lo = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int a = __float2int_rn(qf[grp][2 * k] * up);      // channel 8t + 2k
+        const int c = __float2int_rn(qf[grp][2 * k + 1] * up);  // channel 8t + 2k + 1
+        sum += a + c;
+        he |= (uint32_t)((a >> 8) & 0xFF) << (8 * k);
+        le |= (uint32_t)(a & 0xFF) << (8 * k);
+        ho |= (uint32_t)((c >> 8) & 0xFF) << (8 * k);
+        lo |= (uint32_t)(c & 0xFF) << (8 * k);
+      }
+      bh[grp][0] = he; bh[grp][1] = ho;
+      bl[grp][0] = le; bl[grp][1] = lo;
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);  // over the group's 32 channels, head gq
+      qs0[grp] = (float)__shfl_sync(0xffffffffu, sum, (2 * t) * 4);
+      qs1[grp] = (float)__shfl_sync(0xffffffffu, sum, (2 * t + 1) * 4);
+    }
+  }
+
+  uint32_t code_off[4];
+#pragma unroll
+  for (int grp = 0; grp < 4; ++grp) code_off[grp] = gq * 64 + (((grp + (gq >> 1)) & 3) << 4) + t * 4;
+  const uint32_t sz_off = 2048 + gq * 16;  // {scale, min} x 4 groups of token gq; +128 per eight tokens
+
+  float* const out0 = p.scores + (size_t)(b * p.Hq + h + 2 * t) * p.stride + (size_t)first * kPage + gq;
+  const bool own0 = 2 * t < G, own1 = 2 * t + 1 < G;
+  const uint8_t* stage = ring;
+  int fill_slot = kRingDepth - 1;
+  constexpr int kMagicBits = 0x4B400000;   // 1.5 * 2^23 as a float
+  constexpr float kMagic = 12582912.f;
+  for (int i = 0; i < my_pairs; ++i) {
+    cp_async_wait<kRingDepth - 2>();  // pair i has landed (this thread's copies)
+    __syncwarp();                     // ... and every other lane's
+    float res[2][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {  // one page = one m16 tile per group
+      const uint4 sza = *reinterpret_cast<const uint4*>(stage + sz_off + mt * 256);
+      const uint4 szb = *reinterpret_cast<const uint4*>(stage + sz_off + mt * 256 + 128);
+      const uint32_t sa[4] = {sza.x, sza.y, sza.z, sza.w}, sb[4] = {szb.x, szb.y, szb.z, szb.w};
+      float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
+#pragma unroll
+      for (int grp = 0; grp < 4; ++grp) {
+        const uint32_t wa = *reinterpret_cast<const uint32_t*>(stage + code_off[grp] + mt * 1024);
+        const uint32_t wb = *reinterpret_cast<const uint32_t*>(stage + code_off[grp] + mt * 1024 + 512);
+        const uint32_t a0 = wa & 0x0F0F0F0Fu, a2 = (wa >> 4) & 0x0F0F0F0Fu;
+        const uint32_t a1 = wb & 0x0F0F0F0Fu, a3 = (wb >> 4) & 0x0F0F0F0Fu;
+        int dl[4], dh[4];
+        ImmaTile::run_u8(dl, a0, a1, a2, a3, bl[grp][0], bl[grp][1], kMagicBits);
+        ImmaTile::run_s8(dh, a0, a1, a2, a3, bh[grp][0], bh[grp][1], 0);
+        const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&sa[grp]));  // {scale, min}
+        const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&sb[grp]));
+        r0 = fmaf(fa.x, __int_as_float(dh[0] * 256 + dl[0]) - kMagic, fmaf(fa.y, qs0[grp], r0));
+        r1 = fmaf(fa.x, __int_as_float(dh[1] * 256 + dl[1]) - kMagic, fmaf(fa.y, qs1[grp], r1));
+        r2 = fmaf(fb.x, __int_as_float(dh[2] * 256 + dl[2]) - kMagic, fmaf(fb.y, qs0[grp], r2));
+        r3 = fmaf(fb.x, __int_as_float(dh[3] * 256 + dl[3]) - kMagic, fmaf(fb.y, qs1[grp], r3));
+      }
+      res[mt][0] = r0; res[mt][1] = r1; res[mt][2] = r2; res[mt][3] = r3;
+    }
+    __syncwarp();      // all lanes are done reading the slot that the next issue overwrites
+    issue(i + kRingDepth - 1, fill_slot);
+    fill_slot = (fill_slot + 1 == kRingDepth) ? 0 : fill_slot + 1;
+    stage = (stage + kWarpStageBytes == ring + kRingDepth * kWarpStageBytes) ? ring : stage + kWarpStageBytes;
+    const int pg0 = (warp + i * kEstWarps) * 2;
+    if (own0) {
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const int pg = pg0 + mt;
+        if (pg < n_here) {
+          const int ntok = sm_ntok[pg];  // 0 for a page whose table entry was out of range
+          float* const o0 = out0 + pg * kPage;
+          o0[0] = gq < ntok ? res[mt][0] * out_scale0 : -INFINITY;
+          o0[8] = gq + 8 < ntok ? res[mt][2] * out_scale0 : -INFINITY;
+          if (own1) {
+            o0[p.stride] = gq < ntok ? res[mt][1] * out_scale1 : -INFINITY;
+            o0[p.stride + 8] = gq + 8 < ntok ? res[mt][3] * out_scale1 : -INFINITY;
+          }
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+}
+
 template <typename T, int G, int VARIANT>
 static int launch_one(const EstParams& p, int rows, int max_row_pages, bool ldg, cudaStream_t st) {
   if (rows > 65535) return TWL_ERR_TOO_LARGE;
   if (ldg) {
     dim3 grid((max_row_pages + kPagesPerBlock - 1) / kPagesPerBlock, rows);
     estimate_int4_kernel<T, G, VARIANT><<<grid, kEstThreads, 0, st>>>(p);
+  } else if (G > 1 && VARIANT == VAR_DP4A && !p.force_ring && !p.simt_group && !p.f16_tiles) {
+    constexpr int kBytes = kEstWarps * kRingDepth * kWarpStageBytes;
+    auto kern = estimate_int4_imma_group_kernel<T, (G > 1 ? G : 2)>;
+    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+    dim3 grid((max_row_pages + kWarpPagesPerBlock - 1) / kWarpPagesPerBlock, rows);
+    TWL_CUDA_TRY(launch_chain(kern, grid, dim3(kEstThreads), kBytes, st, p));
   } else if (G > 1 && VARIANT == VAR_DP4A && !p.force_ring && !p.simt_group) {
     constexpr int kBytes = kEstWarps * kRingDepth * kWarpStageBytes;
     auto kern = estimate_int4_mma_group_kernel<T, (G > 1 ? G : 2)>;
@@ -1281,6 +1518,7 @@ static int launch_dtype(const EstParams& p, bool has_cand, int max_row_pages, in
   const_cast<EstParams&>(p).force_ring = (variant & 128) != 0;
   const_cast<EstParams&>(p).simt_group = (variant & 32) != 0;  // +32: integer-dot kernel for query-head groups
   const_cast<EstParams&>(p).bulk_warp = (variant & 64) != 0;   // +64: warp-private rings fed by bulk copies
+  const_cast<EstParams&>(p).f16_tiles = (variant & 256) != 0;  // +256: 16-bit float tiles for query-head groups
   const bool ldg = (variant & 16) != 0;
   switch (variant & 15) {
     case VAR_F32: return launch_variant<T, VAR_F32>(p, has_cand, max_row_pages, ldg, st);

@@ -175,7 +175,8 @@ extern "C" int twl_select_prune_attend_step(
                                            budget, weights, batch, num_q_heads, num_kv_heads, num_pages_total,
                                            sm_scale, out, ws + l.attn, (size_t)l.attn_bytes, attn_chunk, status,
                                            stream);
-  return twl_sparse_decode_attn(q, dtype, k_pages, v_pages, kv_indptr, kv_indices, indices, l.stride, budget,
-                                batch, num_q_heads, num_kv_heads, num_pages_total, sm_scale, out, ws + l.attn,
-                                (size_t)l.attn_bytes, attn_chunk, status, stream);
+  return twl::sparse_decode_attn_bounded(q, dtype, k_pages, v_pages, kv_indptr, kv_indices, indices, l.stride,
+                                         budget, nullptr, batch, num_q_heads, num_kv_heads, num_pages_total,
+                                         sm_scale, out, ws + l.attn, (size_t)l.attn_bytes, attn_chunk, status,
+                                         stream, max_pages);
 }

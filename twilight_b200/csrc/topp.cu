@@ -853,18 +853,24 @@ topp_prune_kernel(const PruneParams p) {
       if (i < s_end) v = *reinterpret_cast<const float4*>(row + i);
       const bool any = (v.x > low) || (v.y > low) || (v.z > low) || (v.w > low);
       if (__ballot_sync(0xffffffffu, any) == 0) continue;
+      // (no branches below: the four sub-steps' loads are issued together)
+      float e[4];
+      int page[4];
 #pragma unroll
       for (int sub = 0; sub < 4; ++sub) {
         const int j = i0 + sub * 32 + lane;
-        const float e = j < s_end ? row[j] : -INFINITY;
-        const bool keep = e > low;
+        e[sub] = j < s_end ? row[j] : -INFINITY;
+        page[sub] = (has_cand && j < s_end) ? cand[j / kPage] : (j / kPage);
+      }
+#pragma unroll
+      for (int sub = 0; sub < 4; ++sub) {
+        const int j = i0 + sub * 32 + lane;
+        const bool keep = e[sub] > low;
         const unsigned mk = __ballot_sync(0xffffffffu, keep);
-        if (mk == 0) continue;
         const int pos = off + __popc(mk & lt_mask);
         if (keep && pos < p.index_stride) {
-          const int page = has_cand ? cand[j / kPage] : (j / kPage);
-          out[pos] = page * kPage + (j % kPage);
-          if (out_w) out_w[pos] = thresh_mode ? fexp(e) : e * out_scale;
+          out[pos] = page[sub] * kPage + (j % kPage);
+          if (out_w) out_w[pos] = thresh_mode ? fexp(e[sub]) : e[sub] * out_scale;
         }
         off += __popc(mk);
       }
