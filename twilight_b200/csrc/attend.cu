@@ -484,7 +484,11 @@ sparse_decode_attn_kernel(const AttParams p) {
 constexpr int kGrpWarps = 2;
 constexpr int kGrpThreads = kGrpWarps * 32;
 constexpr int kGrpStageBytes = 2 * kPage * kD * 2;                       // K page, then V page: 8 KiB
-__host__ __device__ constexpr int grp_ring_bytes(int stages) { return kGrpWarps * stages * kGrpStageBytes; }  // 16 KiB a stage
+// ring of a block: `stages` whole-page stages (K page, then V page) per warp, or, with stages == 1,
+// three half-stages (one K or V page each) per warp
+__host__ __device__ constexpr int grp_ring_bytes(int stages) {
+  return stages == 1 ? kGrpWarps * 3 * (kGrpStageBytes / 2) : kGrpWarps * stages * kGrpStageBytes;
+}
 constexpr int kGrpMaxChunkPages = 256;                                   // pages of one work item
 constexpr int kGrpMinChunkPages = 64;
 
@@ -522,7 +526,7 @@ __device__ __forceinline__ int warp_lower_bound(const int32_t* idx, int n, int k
 }
 
 template <typename T, int G, int kGrpStages>
-__global__ void __launch_bounds__(kGrpThreads)
+__global__ void __launch_bounds__(kGrpThreads, kGrpStages == 1 ? 8 : 6)
 group_decode_attn_kernel(const AttParams p) {
   static_assert(G == 2 || G == 4 || G == 8, "the group sits in the upper rows of one m16 tile");
   extern __shared__ __align__(128) unsigned char sm_dyn[];  // the rings; later the warps' results
@@ -629,7 +633,7 @@ group_decode_attn_kernel(const AttParams p) {
     }
   }
 
-  unsigned char* const my_ring = sm_dyn + warp * (kGrpStages * kGrpStageBytes);
+  unsigned char* const my_ring = sm_dyn + warp * (grp_ring_bytes(kGrpStages) / kGrpWarps);
   const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
   const int my_n = (n_union > warp) ? (n_union - warp + kGrpWarps - 1) / kGrpWarps : 0;
   const T* const kbase = reinterpret_cast<const T*>(p.k);
@@ -660,11 +664,34 @@ group_decode_attn_kernel(const AttParams p) {
   };
   {
     uint4* z = reinterpret_cast<uint4*>(my_ring);
-    for (int i = lane; i < kGrpStages * kGrpStageBytes / 16; i += 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = lane; i < grp_ring_bytes(kGrpStages) / kGrpWarps / 16; i += 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncwarp();
   }
+  // the n-th half-stage of the warp: the K page (n even) or the V page (n odd) of its page n / 2
+  auto issue_half = [&](int n, int hslot) {
+    const int i = n >> 1;
+    if (i < my_n) {
+      const int phys = sm_uphys[warp + i * kGrpWarps];
+      const uint32_t ub = sm_ubits[warp + i * kGrpWarps];
+      const size_t off = ((size_t)phys * p.Hkv + kvh) * (kPage * kD);
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(((n & 1) ? vbase : kbase) + off) + lane * 16;
+      const uint32_t dst = ring_s + hslot * (kGrpStageBytes / 2);
 #pragma unroll
-  for (int i = 0; i < kGrpStages - 1; ++i) issue(i, i);
+      for (int j = 0; j < 8; ++j) {
+        const int r = 2 * j + (lane >> 4), ch = lane & 15;
+        if ((ub >> r) & 1u) cp_async16(dst + r * 256 + ((ch ^ (r & 7)) << 4), src + j * 512);
+      }
+    }
+    cp_async_commit();
+  };
+  if (kGrpStages == 1) {
+    issue_half(0, 0);
+    issue_half(1, 1);
+    issue_half(2, 2);
+  } else {
+#pragma unroll
+    for (int i = 0; i < kGrpStages - 1; ++i) issue(i, i);
+  }
 
   // ldmatrix lane addressing: matrix mi = lane >> 3, row r8 = lane & 7 of it
   const int mi = lane >> 3, r8 = lane & 7;
@@ -673,18 +700,32 @@ group_decode_attn_kernel(const AttParams p) {
   // V, transposed: (tokens 0-7, chunk 2jj) (tokens 8-15, 2jj) (tokens 0-7, 2jj+1) (tokens 8-15, 2jj+1)
   const int v_tok = r8 + (mi & 1) * 8, v_sub = mi >> 1;
 
-  float o[16][4];
+  // O is kept transposed, Oᵀ = Vᵀ·Pᵀ: tile jj holds channels 16jj..16jj+15 as rows and the heads as
+  // columns, so every accumulator register is used (this lane: channels 16jj+g and 16jj+8+g of heads
+  // 2t and 2t+1).  Pᵀ as the B operand has the layout of the Sᵀ accumulators: nothing is moved.
+  float o[8][4];
 #pragma unroll
-  for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+  for (int jj = 0; jj < 8; ++jj) o[jj][0] = o[jj][1] = o[jj][2] = o[jj][3] = 0.f;
   float m_run = kNegBig, l_run = 0.f;  // of head g, over this lane's tokens (columns 2t, 2t+1, 8+2t, 9+2t)
+  // Half-stages: K of page i sits in slot 2i mod 3, V in slot (2i+1) mod 3.  Once a page's K fragments
+  // are in registers its slot takes V of the next page, once the V fragments are, theirs takes K of
+  // the page after the next: two half-stages in flight all the time in 12 KiB per warp.
   int slot = 0, fill = kGrpStages - 1;
+  int kslot = 0, vslot = 1;
   for (int i = 0; i < my_n; ++i) {
-    cp_async_wait<kGrpStages - 2>();
-    __syncwarp();
-    // the slot of the page worked on in the last iteration is refilled before this page is worked
-    // on: kGrpStages - 1 pages of the warp are in flight all the time
-    issue(i + kGrpStages - 1, fill);
-    const uint32_t st = ring_s + slot * kGrpStageBytes;
+    uint32_t st;
+    if (kGrpStages == 1) {
+      cp_async_wait<2>();
+      __syncwarp();
+      st = ring_s + kslot * (kGrpStageBytes / 2);
+    } else {
+      cp_async_wait<(kGrpStages >= 2 ? kGrpStages - 2 : 0)>();
+      __syncwarp();
+      // the slot of the page worked on in the last iteration is refilled before this page is worked
+      // on: kGrpStages - 1 pages of the warp are in flight all the time
+      issue(i + kGrpStages - 1, fill);
+      st = ring_s + slot * kGrpStageBytes;
+    }
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
     {
       // all fragment loads of the page first, then the tiles: the loads' latencies overlap instead
@@ -696,6 +737,10 @@ group_decode_attn_kernel(const AttParams p) {
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                      : "=r"(kb[ks][0]), "=r"(kb[ks][1]), "=r"(kb[ks][2]), "=r"(kb[ks][3])
                      : "r"(addr));
+      }
+      if (kGrpStages == 1) {
+        __syncwarp();  // every lane has its K fragments
+        issue_half(2 * i + 3, kslot);
       }
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
@@ -721,14 +766,22 @@ group_decode_attn_kernel(const AttParams p) {
     l_run = l_run * alpha + (pw[0] + pw[1]) + (pw[2] + pw[3]);
     m_run = m_new;
     if (__any_sync(0xffffffffu, alpha != 1.f)) {
+      const float al0 = __shfl_sync(0xffffffffu, alpha, 8 * t), al1 = __shfl_sync(0xffffffffu, alpha, 8 * t + 4);
 #pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
-        o[nt][0] *= alpha;
-        o[nt][1] *= alpha;
+      for (int jj = 0; jj < 8; ++jj) {
+        o[jj][0] *= al0;
+        o[jj][1] *= al1;
+        o[jj][2] *= al0;
+        o[jj][3] *= al1;
       }
     }
     const uint32_t pa0 = pack_pair<T>(pw[0], pw[1]), pa2 = pack_pair<T>(pw[2], pw[3]);
-    const uint32_t sv = st + kPage * kD * 2;
+    uint32_t sv = st + kPage * kD * 2;
+    if (kGrpStages == 1) {
+      cp_async_wait<2>();
+      __syncwarp();
+      sv = ring_s + vslot * (kGrpStageBytes / 2);
+    }
     {
       uint32_t vb[8][4];
 #pragma unroll
@@ -738,15 +791,21 @@ group_decode_attn_kernel(const AttParams p) {
                      : "=r"(vb[jj][0]), "=r"(vb[jj][1]), "=r"(vb[jj][2]), "=r"(vb[jj][3])
                      : "r"(addr));
       }
+      if (kGrpStages == 1) {
+        __syncwarp();  // every lane has its V fragments
+        issue_half(2 * i + 4, vslot);
+      }
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) {
-        MmaTile<T>::run(o[2 * jj], pa0, 0u, pa2, 0u, vb[jj][0], vb[jj][1]);      // channels 16jj .. 16jj+7
-        MmaTile<T>::run(o[2 * jj + 1], pa0, 0u, pa2, 0u, vb[jj][2], vb[jj][3]);  // channels 16jj+8 .. 16jj+15
+        // A = Vᵀ: (channels 16jj.., tokens 0-7) (16jj+8.., 0-7) (16jj.., 8-15) (16jj+8.., 8-15)
+        MmaTile<T>::run(o[jj], vb[jj][0], vb[jj][2], vb[jj][1], vb[jj][3], pa0, pa2);
       }
     }
     __syncwarp();  // every lane is done with the slot before the next iteration refills it
     slot = (slot + 1 == kGrpStages) ? 0 : slot + 1;
     fill = (fill + 1 == kGrpStages) ? 0 : fill + 1;
+    kslot = (kslot >= 1) ? kslot - 1 : 2;  // 2(i+1) mod 3
+    vslot = (vslot >= 1) ? vslot - 1 : 2;
   }
   cp_async_wait<0>();
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
@@ -755,17 +814,22 @@ group_decode_attn_kernel(const AttParams p) {
 
   // ---- merge the warps: per head (max, sum, 128 channels) ----
   float* const res = reinterpret_cast<float*>(sm_dyn);  // [warp][G][130]
-  if (g < G) {
-    float* mine_o = res + ((size_t)warp * G + g) * 130;
+  if (2 * t < G) {
+    float* const o0 = res + ((size_t)warp * G + 2 * t) * 130;
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
-      mine_o[8 * nt + 2 * t] = o[nt][0];
-      mine_o[8 * nt + 2 * t + 1] = o[nt][1];
+    for (int jj = 0; jj < 8; ++jj) {
+      o0[16 * jj + g] = o[jj][0];
+      o0[16 * jj + 8 + g] = o[jj][2];
+      if (2 * t + 1 < G) {
+        o0[130 + 16 * jj + g] = o[jj][1];
+        o0[130 + 16 * jj + 8 + g] = o[jj][3];
+      }
     }
-    if (t == 0) {
-      mine_o[128] = m_run;
-      mine_o[129] = l_run;
-    }
+  }
+  if (g < G && t == 0) {
+    float* const mine_o = res + ((size_t)warp * G + g) * 130;
+    mine_o[128] = m_run;
+    mine_o[129] = l_run;
   }
   __syncthreads();
   for (int e = tid; e < G * kD; e += kGrpThreads) {
@@ -829,10 +893,11 @@ static int launch_attn(const AttParams& p_in, int dtype, size_t rows, int32_t in
     const char* e = getenv("TWL_ATTN_FETCH_ALL");
     return e && e[0] == '1';
   }();
-  // TWL_ATTN_GROUP_STAGES=3: three pages per warp in the group kernel's rings instead of two
+  // TWL_ATTN_GROUP_STAGES=2 / 3: whole-page stages (two or three per warp) in the group kernel's
+  // rings instead of three half-stages (for measurement)
   static const int grp_stages = [] {
     const char* e = getenv("TWL_ATTN_GROUP_STAGES");
-    return (e && e[0] == '3') ? 3 : 2;
+    return (e && e[0] == '3') ? 3 : (e && e[0] == '2') ? 2 : 1;
   }();
   AttParams p = p_in;
   p.group_skip_rows = fetch_all ? 0 : 1;
@@ -867,7 +932,9 @@ static int launch_attn(const AttParams& p_in, int dtype, size_t rows, int32_t in
   } while (0)
 #define TWL_LAUNCH_GRP(TYPE, GG)                                                                   \
   do {                                                                                             \
-    if (grp_stages == 3) TWL_LAUNCH_GRP_S(TYPE, GG, 3); else TWL_LAUNCH_GRP_S(TYPE, GG, 2);        \
+    if (grp_stages == 3) TWL_LAUNCH_GRP_S(TYPE, GG, 3);                                            \
+    else if (grp_stages == 2) TWL_LAUNCH_GRP_S(TYPE, GG, 2);                                       \
+    else TWL_LAUNCH_GRP_S(TYPE, GG, 1);                                                            \
   } while (0)
     if (dtype == TWL_F16) {
       if (g == 2) TWL_LAUNCH_GRP(__half, 2); else if (g == 4) TWL_LAUNCH_GRP(__half, 4); else TWL_LAUNCH_GRP(__half, 8);
