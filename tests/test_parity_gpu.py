@@ -425,6 +425,49 @@ def test_prune_synthetic_rows_all_paths(n):
         assert abs(float(thr[0, r, 0]) - float(low)) <= P_TOL
 
 
+@pytest.mark.parametrize("n", [8192, 16384, 32768])
+def test_prune_rows_that_overload_one_lane_of_the_window_search(n):
+    """The block-wide search lets every lane collect the window elements among the slots it reads
+    (four consecutive slots of every 128 of its warp's slice).  Rows whose large values all sit in
+    the slots of the same lanes make those lanes' columns overflow, so the warps stay on the row
+    and try again in later rounds; flat rows with a large or a tiny token 0 run many or few
+    rounds.  All against the oracle."""
+    g = torch.Generator(device=DEV).manual_seed(1000 + n)
+    pos = torch.arange(n, device=DEV)
+    rows = []
+    a = torch.randn(n, generator=g, device=DEV) * 0.3 - 6.0
+    a[(pos % 128) < 4] = torch.randn(int(((pos % 128) < 4).sum()), generator=g, device=DEV) * 0.5 + 2.0   # lane 0 only
+    a[0] = 2.5
+    rows.append(a)
+    b = torch.randn(n, generator=g, device=DEV) * 0.3 - 6.0
+    sel = ((pos % 128) >= 60) & ((pos % 128) < 68)                                                      # lanes 15 and 16
+    b[sel] = torch.randn(int(sel.sum()), generator=g, device=DEV) * 1.0 + 1.0
+    b[0] = 6.0
+    rows.append(b)
+    c = torch.randn(n, generator=g, device=DEV)            # flat, token 0 far above: high falls for many rounds
+    c[0] = 9.0
+    rows.append(c)
+    d = torch.randn(n, generator=g, device=DEV)            # flat, token 0 far below: one or two rounds
+    d[0] = -8.0
+    rows.append(d)
+    scores = torch.stack(rows).reshape(1, 4, n).contiguous()
+    indptr, _, last, _ = PagedKVCache.page_table([n], DEV)
+    pages = np.arange(n // PAGE)
+    for top_p in (0.5, 0.9, 0.99):
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        idx, bud = ops.topp_prune(scores, indptr, last, top_p, status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        for r in range(4):
+            row = scores[0, r].cpu().numpy()
+            probs, keep, low = U.oracle_prune_row(row, pages, top_p)
+            k = int(bud[0, r])
+            got = idx[0, r, :k].cpu().numpy()
+            assert (np.diff(got) > 0).all()
+            dd = U.check_index_parity(got, probs, keep, low, pages, P_TOL)
+            assert abs(k - int(keep.sum())) <= dd, (n, top_p, r, k, int(keep.sum()))
+
+
 def test_prune_randomised_rows_vs_oracle():
     """Seeded random row lengths, score shapes and top-p values; every row against the oracle."""
     rng = np.random.default_rng(123)
