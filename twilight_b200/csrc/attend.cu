@@ -668,19 +668,25 @@ group_decode_attn_kernel(const AttParams p) {
     __syncwarp();
   }
   // the n-th half-stage of the warp: the K page (n even) or the V page (n odd) of its page n / 2
+  // this lane's eight copies of a page: token rows 2j + (lane >> 4), chunk lane & 15; rows r and r + 8
+  // are swizzled alike, so four offsets do
+  uint32_t doff[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int r = 2 * j + (lane >> 4), ch = lane & 15;
+    doff[j] = r * 256 + ((ch ^ (r & 7)) << 4);
+  }
   auto issue_half = [&](int n, int hslot) {
     const int i = n >> 1;
     if (i < my_n) {
       const int phys = sm_uphys[warp + i * kGrpWarps];
-      const uint32_t ub = sm_ubits[warp + i * kGrpWarps];
+      const uint32_t ub = (uint32_t)sm_ubits[warp + i * kGrpWarps] >> (lane >> 4);  // bit 2j: this lane's row of step j
       const size_t off = ((size_t)phys * p.Hkv + kvh) * (kPage * kD);
       const unsigned char* src = reinterpret_cast<const unsigned char*>(((n & 1) ? vbase : kbase) + off) + lane * 16;
       const uint32_t dst = ring_s + hslot * (kGrpStageBytes / 2);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int r = 2 * j + (lane >> 4), ch = lane & 15;
-        if ((ub >> r) & 1u) cp_async16(dst + r * 256 + ((ch ^ (r & 7)) << 4), src + j * 512);
-      }
+      for (int j = 0; j < 8; ++j)
+        if (ub & (1u << (2 * j))) cp_async16(dst + doff[j & 3] + (j >> 2) * 2048, src + j * 512);
     }
     cp_async_commit();
   };

@@ -1424,7 +1424,23 @@ estimate_int4_imma_group_kernel(const EstParams p) {
     fill_slot = (fill_slot + 1 == kRingDepth) ? 0 : fill_slot + 1;
     stage = (stage + kWarpStageBytes == ring + kRingDepth * kWarpStageBytes) ? ring : stage + kWarpStageBytes;
     const int pg0 = (warp + i * kEstWarps) * 2;
-    if (own0) {
+    if (pg0 + 1 < n_here && sm_ntok[pg0] == kPage && sm_ntok[pg0 + 1] == kPage) {
+      // two whole pages (all but the last stage of a sequence): nothing to mask
+      if (own0) {
+        float* const o0 = out0 + pg0 * kPage;
+        o0[0] = res[0][0] * out_scale0;
+        o0[8] = res[0][2] * out_scale0;
+        o0[kPage] = res[1][0] * out_scale0;
+        o0[kPage + 8] = res[1][2] * out_scale0;
+        if (own1) {
+          float* const o1 = o0 + p.stride;
+          o1[0] = res[0][1] * out_scale1;
+          o1[8] = res[0][3] * out_scale1;
+          o1[kPage] = res[1][1] * out_scale1;
+          o1[kPage + 8] = res[1][3] * out_scale1;
+        }
+      }
+    } else if (own0) {
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
         const int pg = pg0 + mt;
