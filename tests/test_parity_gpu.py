@@ -385,7 +385,7 @@ def test_prune_with_candidates_and_missing_sink():
 @pytest.mark.parametrize("n", [16, 2048, 8192, 40960, 40976, 65536])
 def test_prune_synthetic_rows_all_paths(n):
     """Rows written directly (no estimator): up to 40960 slots a row is searched in shared memory
-    with the shrinking working list, longer rows from global memory.  Shapes: one heavy sink,
+    with the working set squeezed to the search window, longer rows from global memory.  Shapes: one heavy sink,
     a flat row, a row where half the slots tie with the sink (the first round's survivors do not
     fit the list, so the search stays on the row), and a row whose kept set grows in later rounds."""
     g = torch.Generator(device=DEV).manual_seed(n)

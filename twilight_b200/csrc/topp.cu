@@ -25,7 +25,8 @@ constexpr int kSearchRoundCap = 128;
 constexpr float kSearchEps = 1e-5f;
 // floats of a row that fit in shared memory next to the reduction scratch
 constexpr int kRowCap = 56 * 1024;
-// rows of the fused pruner also need a working list of a quarter of the row (6 bytes an entry)
+// rows of the fused pruner also need the cut list (a quarter of the row, 6 bytes an entry), whose
+// memory the block-wide search then works in
 constexpr int kPruneRowCap = 40 * 1024;
 // elements of a row that one warp searches on its own (see topp_search_solo)
 constexpr int kSoloCap = 1024;
@@ -596,7 +597,7 @@ topp_prune_kernel(const PruneParams p) {
   float* red = smem;                                  // 256 words
   int* wsum = reinterpret_cast<int*>(smem + 256);     // 96 ints: 33 of scan scratch, 32 segment counts
   float* solo = smem + 352;                           // kSoloCap values: the short list one warp searches
-  float* row = smem + kPruneHeaderWords;              // the row when IN_SMEM, then the working list
+  float* row = smem + kPruneHeaderWords;              // the row when IN_SMEM, then the cut list / search area
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   pdl_release();  // the attention kernel's blocks may move in while this small grid works
   const int r = blockIdx.x;
@@ -682,7 +683,7 @@ topp_prune_kernel(const PruneParams p) {
   } else if (IN_SMEM) {
     // pass 2: exponentials in place and their sum.  The search runs on the un-normalised values
     // (p and the stop width scaled by the sum instead of every element divided by it).  The same
-    // pass collects every element above x0/256 into the working list, with the smallest positive
+    // pass collects every element above x0/256 into the cut list, with the smallest positive
     // element and the largest element that was not collected: what the short-list search needs.
     x0 = sink_present ? fexp(row[0]) : 0.f;
     __syncthreads();  // row[0] is read by everyone before its owner overwrites it
