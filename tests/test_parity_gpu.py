@@ -468,6 +468,40 @@ def test_prune_rows_that_overload_one_lane_of_the_window_search(n):
             assert abs(k - int(keep.sum())) <= dd, (n, top_p, r, k, int(keep.sum()))
 
 
+@pytest.mark.parametrize("n", [2048, 8192, 32768])
+def test_prune_keeps_everything_when_the_mass_above_every_pivot_stays_below_p(n):
+    """K1 ends with low = 0 when no pivot it tries has mass >= p above it before its window closes:
+    a sink holding 93 % of the mass over flat dust with p = 0.95, or p = 0.999 on rows whose smallest
+    elements together hold more than 0.1 %.  The reference's mask is then probs > 0, i.e. every
+    candidate - not just the few large elements the short-list search looked at."""
+    g = torch.Generator(device=DEV).manual_seed(77 + n)
+    rows = []
+    dust = torch.randn(n, generator=g, device=DEV) * 0.3
+    a = dust.clone()
+    a[0] = float(np.log(0.93 / 0.07 * n))             # sink ~ 93 % of the mass
+    rows.append(a)
+    b = torch.randn(n, generator=g, device=DEV) * 4.0  # wide row: the smallest elements add up to > 0.1 %
+    rows.append(b)
+    c = dust.clone()
+    c[0] = float(np.log(0.5 * n))
+    c[1: 1 + n // 64] += 3.0                           # a few hundred heavier tokens, still far below p with the sink
+    rows.append(c)
+    scores = torch.stack(rows).reshape(1, 3, n).contiguous()
+    indptr, _, last, _ = PagedKVCache.page_table([n], DEV)
+    pages = np.arange(n // PAGE)
+    for top_p in (0.95, 0.999):
+        idx, bud = ops.topp_prune(scores, indptr, last, top_p)
+        for r in range(3):
+            row = scores[0, r].cpu().numpy()
+            probs, keep, low = U.oracle_prune_row(row, pages, top_p)
+            k = int(bud[0, r])
+            got = idx[0, r, :k].cpu().numpy()
+            d = U.check_index_parity(got, probs, keep, low, pages, P_TOL)
+            assert abs(k - int(keep.sum())) <= d, (n, top_p, r, k, int(keep.sum()), float(low))
+            if float(low) == 0.0:
+                assert k == int((probs > 0).sum())
+
+
 def test_prune_randomised_rows_vs_oracle():
     """Seeded random row lengths, score shapes and top-p values; every row against the oracle."""
     rng = np.random.default_rng(123)

@@ -52,8 +52,12 @@ def oracle_prune_row(scores_row, pages, top_p):
     return probs, keep, np.float32(low)
 
 
-def check_index_parity(got_tokens, probs, keep, low, pages, tol=1e-4):
-    """Kept token sets must match except tokens whose probability is within tol of the threshold."""
+def check_index_parity(got_tokens, probs, keep, low, pages, tol=1e-4, mass_tol=2e-4):
+    """Kept token sets must match except tokens whose probability is within tol of the threshold.
+    For a token whose probability is itself of the order of tol that test says nothing (on a long
+    flat row every probability lies within tol of any threshold), so such tokens may not carry more
+    than mass_tol of the row's probability together: a pruner that dropped a row's whole tail would
+    pass the first test and fails this one."""
     want_slots = np.nonzero(keep)[0]
     want = set(slots_to_tokens(pages, want_slots).tolist())
     got = set(int(t) for t in got_tokens)
@@ -62,9 +66,13 @@ def check_index_parity(got_tokens, probs, keep, low, pages, tol=1e-4):
         return 0
     tok_of_slot = slots_to_tokens(pages, np.arange(len(probs)))
     p_of_tok = dict(zip(tok_of_slot.tolist(), probs.tolist()))
+    mass = 0.0
     for t in diff:
         assert t in p_of_tok, f"token {t} is not a candidate"
         assert abs(p_of_tok[t] - float(low)) <= tol, (t, p_of_tok[t], float(low))
+        if p_of_tok[t] <= 2 * tol:
+            mass += p_of_tok[t]
+    assert mass <= mass_tol, (len(diff), mass, float(low))
     return len(diff)
 
 

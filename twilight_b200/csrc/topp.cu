@@ -774,10 +774,12 @@ topp_prune_kernel(const PruneParams p) {
       }
       __syncthreads();  // seg_cnt and red are reused by the block-wide search
       if (done) {
-        // every element above low (>= the collection cut, or 0 with everything positive collected)
-        // is in the list, each warp's segment in row order
+        // A low that has risen is a pivot >= the collection cut: every element above it is in the
+        // list, each warp's segment in row order.  A search that ended with low still 0 (the mass
+        // above every pivot stayed below p until the window closed) keeps every positive element,
+        // listed or not: those come from the row.
         low = lo0;
-        from_list = true;
+        from_list = lo0 > 0.f;
         list_cnt = first_cnt;
       } else {
         // the cut list is dead from here on: its memory is the working area of the block-wide search
