@@ -502,6 +502,64 @@ def test_prune_keeps_everything_when_the_mass_above_every_pivot_stays_below_p(n)
                 assert k == int((probs > 0).sum())
 
 
+def test_prune_seeded_fuzz_vs_oracle():
+    """Many seeded rows of 16 ... 50000 slots, seven score shapes, seven p values, every block size of
+    the pruner: kept sets against the oracle, run twice (identical results)."""
+    rng = np.random.default_rng(2026)
+    g = torch.Generator(device=DEV).manual_seed(7)
+    shapes = ("flat", "sink", "heavy", "ties", "tiny_sink", "two_level", "steps")
+    differing = 0
+    for case in range(16):
+        nb, hq = 6, 4
+        lens = [int(x) for x in rng.choice([16, 48, 700, 2048, 4096, 8192, 9000, 16384, 20000, 32768, 40960, 50000],
+                                           size=nb)]
+        stride = ((max(lens) + PAGE - 1) // PAGE) * PAGE
+        scores = torch.full((nb, hq, stride), float("-inf"), device=DEV)
+        for b, n in enumerate(lens):
+            for h in range(hq):
+                kind = shapes[int(rng.integers(len(shapes)))]
+                row = torch.randn(n, generator=g, device=DEV) * float(rng.choice([0.1, 0.5, 1.0, 2.0, 4.0]))
+                if kind == "sink":
+                    row[0] += float(rng.uniform(2, 12))
+                elif kind == "heavy":
+                    row[0] += 12.0
+                    k = max(1, int(n * rng.uniform(0.001, 0.2)))
+                    at = torch.randperm(n, generator=g, device=DEV)[:k]
+                    row[at] = 10.0 + 0.3 * torch.randn(k, generator=g, device=DEV)
+                elif kind == "ties":
+                    row[n // 3: n // 3 + max(1, n // 5)] = row[0]
+                elif kind == "tiny_sink":
+                    row[0] -= 10.0
+                elif kind == "two_level":
+                    row[: n // 2] += 5.0
+                elif kind == "steps":
+                    row = torch.round(row * 2) / 2
+                scores[b, h, :n] = row
+        indptr, _, last, _ = PagedKVCache.page_table(lens, DEV)
+        top_p = torch.tensor(rng.choice([0.3, 0.5, 0.8, 0.9, 0.95, 0.99, 0.999], size=nb * hq), dtype=torch.float32,
+                             device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        idx, bud = ops.topp_prune(scores, indptr, last, top_p, status=status)
+        idx2, bud2 = ops.topp_prune(scores, indptr, last, top_p)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0 and torch.equal(bud, bud2)
+        for b, n in enumerate(lens):
+            npg = (n + PAGE - 1) // PAGE
+            pages = np.arange(npg)
+            for h in range(hq):
+                row = scores[b, h, : npg * PAGE].cpu().numpy()
+                probs, keep, low = U.oracle_prune_row(row, pages, float(top_p[b * hq + h]))
+                k = int(bud[b, h])
+                got = idx[b, h, :k].cpu().numpy()
+                assert np.array_equal(got, idx2[b, h, :k].cpu().numpy())
+                assert (np.diff(got) > 0).all() and (got < n).all()
+                d = U.check_index_parity(got, probs, keep, low, pages, P_TOL)
+                assert abs(k - int(keep.sum())) <= d, (case, b, h, n, k, int(keep.sum()))
+                differing += d > 0
+    U.record("prune_fuzz", rows=16 * 24, rows_differing=differing)
+    assert differing <= 4
+
+
 def test_prune_randomised_rows_vs_oracle():
     """Seeded random row lengths, score shapes and top-p values; every row against the oracle."""
     rng = np.random.default_rng(123)
@@ -785,6 +843,65 @@ def test_group_attention_of_dense_heads(hq, hkv, dt):
         errs.append(np.abs(out[b, h].float().cpu().numpy() - want))
     errs = np.stack(errs)
     assert errs.max() <= ATOL_MAX and errs.mean() <= ATOL_MEAN
+
+
+def test_attention_seeded_fuzz_vs_fp32_reference():
+    """Seeded mixes of group sizes, ragged lengths and per-head budgets (dense heads, sparse heads,
+    empty heads inside served groups, single tokens): both attention kernels against an fp32
+    reference on the same kept tokens."""
+    rng = np.random.default_rng(11)
+    worst = 0.0
+    for case in range(14):
+        nb = int(rng.integers(1, 5))
+        hkv = int(rng.choice([1, 2, 4]))
+        g = int(rng.choice([1, 2, 4, 8]))
+        hq = hkv * g
+        dt = [torch.bfloat16, torch.float16][case % 2]
+        lens = [int(x) for x in rng.choice([1, 15, 16, 17, 100, 1000, 2049, 4096, 5000, 9000, 20000], size=nb)]
+        q, cache = make_decode_inputs(nb, hq, hkv, lens, rho=0.02, dtype=dt, device=DEV, seed=100 + case,
+                                      recipe="calibrated", shuffle_pages=True, build_aux=False)
+        stride = cache.max_pages * PAGE
+        gen = torch.Generator().manual_seed(case)
+        indices = torch.zeros(nb, hq, stride, dtype=torch.int32)
+        budget = torch.zeros(nb, hq, dtype=torch.int32)
+        for b, n in enumerate(lens):
+            mode = int(rng.integers(4))
+            for h in range(hq):
+                if mode == 0:
+                    frac = rng.uniform(0.5, 1.0)
+                elif mode == 1:
+                    frac = rng.choice([0.0, 0.01, 0.3, 0.9, 1.0])
+                elif mode == 2:
+                    frac = rng.uniform(0.0, 0.05)
+                else:
+                    frac = 0.0 if h % g == 0 else 1.0
+                kept = min(n, int(round(frac * n)))
+                budget[b, h] = kept
+                if kept:
+                    indices[b, h, :kept] = torch.sort(torch.randperm(n, generator=gen)[:kept])[0].int()
+        indices, budget = indices.to(DEV), budget.to(DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        out = ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices, indices,
+                                     budget, chunk=int(rng.choice([256, 512])), status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        for b, n in enumerate(lens):
+            for h in range(hq):
+                kd, vd = cache.dense_kv(b, h // g)
+                kept = int(budget[b, h])
+                if kept == 0:
+                    ref = torch.zeros(128, device=DEV)
+                else:
+                    at = indices[b, h, :kept].long()
+                    pr = torch.softmax((kd[at].float() @ q[b, h].float()) * U.SM_SCALE, -1).to(dt).float()
+                    ref = pr @ vd[at].float()
+                e = (out[b, h].float() - ref).abs()
+                assert torch.isfinite(out[b, h].float()).all()
+                # mean bound plus the rounding of a 16-bit output, which a row of a few tokens shows undiluted
+                assert float(e.max()) <= 2e-2 and float(e.mean()) <= 1e-3 + 2.0 ** -9 * float(ref.abs().mean()), \
+                    (case, b, h, n, kept, float(e.max()), float(e.mean()))
+                worst = max(worst, float(e.max()))
+    U.record("attention_fuzz", worst_max_abs=worst)
 
 
 def test_group_attention_flags_tokens_past_the_sequence():
