@@ -291,8 +291,9 @@ quest_page_scores_kernel(const ScoreParams p) {
 // heads 2t, 2t+1.  With four heads the upper four columns of B are zero.
 // NW warps per block, PPB pages per block: a warp should stream many steps per block it belongs
 // to, because a block's set-up (page table look-ups, a barrier) moves no metadata.
+// PIPE: two steps of loads in flight per warp instead of one (193 registers instead of 120).
 template <typename T, int G, int NW, int PPB, bool PIPE>
-__global__ void __launch_bounds__(NW * 32, (PIPE ? 256 : 768) / (NW * 32))
+__global__ void __launch_bounds__(NW * 32, (PIPE ? 256 : 512) / (NW * 32))
 quest_page_scores_mma_kernel(const ScoreParams p) {
   static_assert(G == 4 || G == 8, "one n8 tile holds the group");
   constexpr int kThreads = NW * 32;
@@ -561,24 +562,29 @@ static int launch_scores_mma_shape(const ScoreParams& p, cudaStream_t st) {
 
 template <typename T, int G>
 static int launch_scores_mma(const ScoreParams& p, cudaStream_t st) {
-  // Two warps per block, each with two steps (2 x 8 KiB) of loads in flight.  Measured on one KV
-  // head x 128 sequences x 4096 pages (268 MB of metadata, 17 MB of scores written): 56-57 us, the
-  // same within 2 us for 1 or 2 warps x 128..512 pages with two steps in flight and for 8 warps x
-  // 256 pages with one; 2 warps x 256 pages with one step in flight: 66 us.  Staging the slabs
+  // Two warps per block, one step (8 KiB) of loads in flight per warp, 120 registers: eight blocks =
+  // 16 warps per SM.  Measured on one KV head x 128 sequences x 4096 pages (268 MB of metadata,
+  // 17 MB of scores written): 49.7 us with 256 pages per block, 51.8 with 512, 50.3 with four warps
+  // x 512 pages, 51.6 with eight warps x 256 pages.  Two steps in flight per warp need 193
+  // registers, so an SM holds half the warps: 55.6 us whatever the block shape (1, 2 or 8 warps x
+  // 128..512 pages) - this kernel wants warps, not bytes in flight per warp.  Staging the slabs
   // through a shared-memory ring (whole-slab cp.async copies, ldmatrix fragments) was slower (60-68
   // us) and is not kept; neither is a one-wave grid whose blocks walk the (row, page run) items
-  // (58.9 us with runs of 128 pages, 59.9 us with 256).  Pages per block: as many as still leave every SM four blocks, so that
-  // small problems spread out.  TWL_SCORES_MMA_SHAPE=1 selects 8 warps x 256 pages, one step in
-  // flight (for measurement).
+  // (58.9 us with runs of 128 pages, 59.9 us with 256).  Pages per block: 256 while that still
+  // fills the GPU once, else 128 so that small problems spread out.
+  // TWL_SCORES_MMA_SHAPE (for measurement): 1 = 8 warps x 256 pages, 5 = 2 x 512, 6 = 4 x 512, all
+  // with one step in flight; 7 = 2 x 512 with two steps in flight.
   static const int forced = [] {
     const char* e = getenv("TWL_SCORES_MMA_SHAPE");
     return e ? atoi(e) : 0;
   }();
   if (forced == 1) return launch_scores_mma_shape<T, G, 8, 256, false>(p, st);
-  const long rows = (long)p.B * p.Hkv, want = 4L * num_sms();
-  if (rows * ((p.max_pages + 511) / 512) >= want) return launch_scores_mma_shape<T, G, 2, 512, true>(p, st);
-  if (rows * ((p.max_pages + 255) / 256) >= want) return launch_scores_mma_shape<T, G, 2, 256, true>(p, st);
-  return launch_scores_mma_shape<T, G, 2, 128, true>(p, st);
+  if (forced == 5) return launch_scores_mma_shape<T, G, 2, 512, false>(p, st);
+  if (forced == 6) return launch_scores_mma_shape<T, G, 4, 512, false>(p, st);
+  if (forced == 7) return launch_scores_mma_shape<T, G, 2, 512, true>(p, st);
+  const long rows = (long)p.B * p.Hkv, one_wave = 8L * num_sms();
+  if (rows * ((p.max_pages + 255) / 256) >= one_wave) return launch_scores_mma_shape<T, G, 2, 256, false>(p, st);
+  return launch_scores_mma_shape<T, G, 2, 128, false>(p, st);
 }
 
 template <typename T>
