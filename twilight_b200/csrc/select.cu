@@ -424,21 +424,48 @@ __device__ void topk_row(const float* src, int n, int k, int32_t* out, uint32_t*
   int (&wsum)[33] = sc.wsum;
   uint32_t& sh_prefix = sc.prefix;
   int& sh_krem = sc.krem;
-  for (int i = threadIdx.x; i < n; i += kTopkThreads) keys[i] = order_key(__ldcg(src + i));
-  if (threadIdx.x == 0) {
-    sh_prefix = 0;
-    sh_krem = k;
+  // keys, and the smallest and the largest of them: the leading bits they share need no pass
+  uint32_t kmin = 0xFFFFFFFFu, kmax = 0u;
+  for (int i = threadIdx.x; i < n; i += kTopkThreads) {
+    const uint32_t key = order_key(__ldcg(src + i));
+    keys[i] = key;
+    kmin = min(kmin, key);
+    kmax = max(kmax, key);
+  }
+  kmin = __reduce_min_sync(0xffffffffu, kmin);
+  kmax = __reduce_max_sync(0xffffffffu, kmax);
+  if ((threadIdx.x & 31) == 0) {
+    wsum[threadIdx.x >> 5] = (int)kmin;
+    wsum[8 + (threadIdx.x >> 5)] = (int)kmax;
   }
   __syncthreads();
-  // MSB-first radix select of the k-th largest key, 8 bits per pass
-  uint32_t mask = 0;
-  for (int shift = 24; shift >= 0; shift -= 8) {
+  {
+    constexpr int kW = kTopkThreads / 32;
+    const int lane = threadIdx.x & 31;
+    kmin = __reduce_min_sync(0xffffffffu, lane < kW ? (uint32_t)wsum[lane] : 0xFFFFFFFFu);
+    kmax = __reduce_max_sync(0xffffffffu, lane < kW ? (uint32_t)wsum[8 + lane] : 0u);
+  }
+  // MSB-first radix select of the k-th largest key, up to 8 bits per pass, starting below the
+  // leading bits that all keys share (page scores of one row often lie within a few octaves: the
+  // sign and most exponent bits are common then, and the select takes three passes instead of four;
+  // 25.1 -> 22.9 us on 1024 rows x 4096 pages)
+  int top = 32 - __clz(kmin ^ kmax);  // bits still undetermined: keys agree above bit `top`
+  if (threadIdx.x == 0) {
+    sh_prefix = top < 32 ? (kmax >> top) << top : 0u;
+    sh_krem = k;
+  }
+  __syncthreads();  // wsum is free again; prefix and krem are set
+  while (top > 0) {
+    const int width = min(8, top), shift = top - width;
+    const uint32_t mask = top < 32 ? 0xFFFFFFFFu << top : 0u, dmask = (1u << width) - 1u;
     hist[threadIdx.x] = 0;  // kTopkThreads == 256 bins
     __syncthreads();
     const uint32_t prefix = sh_prefix;
+    // (plain per-lane adds: letting a warp whose keys share a bin add once - by a vote, or by
+    // __match_any_sync groups - was slower, 14.8 and 18.8 against 12.7 us on 512 rows x 2048 pages)
     for (int i = threadIdx.x; i < n; i += kTopkThreads) {
       const uint32_t key = keys[i];
-      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFF], 1);
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & dmask], 1);
     }
     __syncthreads();
     if (threadIdx.x < 32) {
@@ -468,7 +495,7 @@ __device__ void topk_row(const float* src, int n, int k, int32_t* out, uint32_t*
         }
       }
     }
-    mask |= 0xFFu << shift;
+    top = shift;
     __syncthreads();
   }
   const uint32_t thr = sh_prefix;  // k-th largest key
