@@ -1237,6 +1237,51 @@ def test_quest_pages_with_scores_rounded_to_dtype_match_reference_ranking(golden
                     assert psn[b, hh, pg] == kth, (budget, b, hh, pg, psn[b, hh, pg], kth)
 
 
+def test_topk_pages_seeded_fuzz_exact():
+    """The page selection on given scores against an exact reference (descending score, ties to the
+    lower page, -0 tying with +0): narrow ranges (leading key bits shared), rounded scores (many
+    ties), constant rows, -inf entries, all-negative rows, one outlier; budgets from one page to all."""
+    rng = np.random.default_rng(3)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    for case in range(24):
+        nb, hq = int(rng.integers(1, 5)), int(rng.choice([1, 3, 8]))
+        lens = [int(x) for x in rng.choice([16, 17, 100, 1000, 4096, 5000, 20000, 32768, 65536], size=nb)]
+        npg = [(n + PAGE - 1) // PAGE for n in lens]
+        mp = max(npg)
+        ps = torch.zeros(nb, hq, mp, device=DEV)
+        for b in range(nb):
+            for h in range(hq):
+                kind, n = int(rng.integers(7)), npg[b]
+                x = torch.randn(n, generator=g, device=DEV) * float(rng.choice([1e-3, 1.0, 50.0]))
+                if kind == 1:
+                    x = x + 100.0
+                elif kind == 2:
+                    x = torch.round(x)
+                elif kind == 3:
+                    x[:] = 3.25
+                elif kind == 4:
+                    x[torch.rand(n, generator=g, device=DEV) < 0.3] = float("-inf")
+                elif kind == 5:
+                    x = -x.abs() - 1.0
+                elif kind == 6:
+                    x[0] = 1e6
+                ps[b, h, :n] = x
+        indptr, _, _, _ = PagedKVCache.page_table(lens, DEV)
+        budget = int(rng.choice([16, 17, 100, 1024, 8192, 16384, 1 << 20]))
+        cp, cn, _ = ops.quest_topk(ps, indptr, budget, max_pages=mp)
+        torch.cuda.synchronize()
+        kwant = max(1, budget // PAGE) + (1 if budget % PAGE else 0)
+        for b in range(nb):
+            for h in range(hq):
+                n = npg[b]
+                k = min(kwant, n)
+                x = ps[b, h, :n].cpu().numpy()
+                order = np.lexsort((np.arange(n), -x))
+                assert int(cn[b, h]) == k
+                assert np.array_equal(cp[b, h, :k].cpu().numpy(), np.sort(order[:k])), (case, b, h, n, k)
+
+
+
 @pytest.mark.parametrize("hq,hkv,sel", [(8, 8, "quest"), (8, 2, "quest"), (8, 2, "none")])
 def test_step_ragged_gqa(hq, hkv, sel):
     lens = ragged_lengths(6, 500, 3000, seed=3) + [16, 17]

@@ -409,7 +409,8 @@ quest_page_scores_mma_kernel(const ScoreParams p) {
 
 // ---- top-k pages of one (batch, query head) row ---------------------------------------------
 __device__ __forceinline__ uint32_t order_key(float f) {
-  const uint32_t u = __float_as_uint(f);
+  uint32_t u = __float_as_uint(f);
+  if (u == 0x80000000u) u = 0u;  // -0 ties with +0, as it does for a comparison of the floats
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);  // larger float <=> larger key
 }
 
