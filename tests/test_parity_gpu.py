@@ -560,6 +560,54 @@ def test_prune_seeded_fuzz_vs_oracle():
     assert differing <= 4
 
 
+def test_prune_seeded_fuzz_with_candidate_lists_vs_oracle():
+    """Random ascending candidate page lists (with and without page 0, short and full, the last page
+    of a sequence partly past its end) and scores in candidate-slot order: kept tokens against the
+    oracle, which sees token 0 only when page 0 is a candidate."""
+    rng = np.random.default_rng(77)
+    g = torch.Generator(device=DEV).manual_seed(77)
+    for case in range(12):
+        nb, hq = 3, 4
+        lens = [int(x) for x in rng.choice([100, 1000, 5000, 20000, 40000, 70000], size=nb)]
+        npg = [(n + PAGE - 1) // PAGE for n in lens]
+        max_k = int(rng.choice([1, 4, 64, 512, 1024, 2048]))
+        scores = torch.full((nb, hq, max_k * PAGE), float("-inf"), device=DEV)
+        cand = torch.zeros(nb, hq, max_k, dtype=torch.int32)
+        cnp = torch.zeros(nb, hq, dtype=torch.int32)
+        for b, n in enumerate(lens):
+            for h in range(hq):
+                k = min(max_k, npg[b]) if rng.random() < 0.7 else int(rng.integers(1, min(max_k, npg[b]) + 1))
+                pages = np.sort(rng.choice(npg[b], size=k, replace=False))
+                if rng.random() < 0.6 and pages[0] != 0:
+                    pages[0] = 0
+                cand[b, h, :k] = torch.from_numpy(pages.astype(np.int32))
+                cnp[b, h] = k
+                row = torch.randn(k * PAGE, generator=g, device=DEV) * float(rng.choice([0.3, 1.0, 3.0]))
+                if pages[0] == 0 and rng.random() < 0.7:
+                    row[0] += float(rng.uniform(2, 10))
+                if pages[-1] == npg[b] - 1 and n % PAGE:
+                    row[(k - 1) * PAGE + n % PAGE:] = float("-inf")
+                scores[b, h, : k * PAGE] = row
+        cand, cnp = cand.to(DEV), cnp.to(DEV)
+        indptr, _, last, _ = PagedKVCache.page_table(lens, DEV)
+        top_p = torch.tensor(rng.choice([0.5, 0.9, 0.95, 0.99], size=nb * hq), dtype=torch.float32, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        idx, bud = ops.topp_prune(scores, indptr, last, top_p, cand_pages=cand, cand_npages=cnp, status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        for b, n in enumerate(lens):
+            for h in range(hq):
+                k = int(cnp[b, h])
+                pages = cand[b, h, :k].cpu().numpy()
+                row = scores[b, h, : k * PAGE].cpu().numpy()
+                probs, keep, low = U.oracle_prune_row(row, pages, float(top_p[b * hq + h]))
+                kept = int(bud[b, h])
+                got = idx[b, h, :kept].cpu().numpy()
+                assert (np.diff(got) > 0).all() and (got < n).all()
+                d = U.check_index_parity(got, probs, keep, low, pages, P_TOL)
+                assert abs(kept - int(keep.sum())) <= d, (case, b, h, kept, int(keep.sum()))
+
+
 def test_prune_randomised_rows_vs_oracle():
     """Seeded random row lengths, score shapes and top-p values; every row against the oracle."""
     rng = np.random.default_rng(123)
@@ -1235,6 +1283,49 @@ def test_quest_pages_with_scores_rounded_to_dtype_match_reference_ranking(golden
                 kth = np.sort(psn[b, hh])[::-1][kk - 1]
                 for pg in ours ^ theirs:
                     assert psn[b, hh, pg] == kth, (budget, b, hh, pg, psn[b, hh, pg], kth)
+
+
+def test_page_scores_seeded_fuzz_vs_fp64():
+    """Quest page scores of every group size (FMA form for 1 and 2 heads per KV head, tensor-core form
+    for 4 and 8) on ragged shuffled caches, with zero, all-negative and outlier-channel queries, and once
+    at a size that takes the large block shape: against sum_d max(q_d*kmax_d, q_d*kmin_d) in fp64."""
+    rng = np.random.default_rng(9)
+    worst = 0.0
+    for case in range(12):
+        nb = int(rng.integers(1, 6))
+        hkv, g = int(rng.choice([1, 2, 4, 8])), int(rng.choice([1, 2, 4, 8]))
+        dt = [torch.bfloat16, torch.float16][case % 2]
+        lens = [int(x) for x in rng.choice([1, 16, 17, 100, 2049, 4101, 9000, 33000], size=nb)]
+        if case == 11:
+            nb, hkv, g, lens = 20, 8, 8, [65536] * 20
+        hq = hkv * g
+        q, cache = make_decode_inputs(nb, hq, hkv, lens, rho=0.02, dtype=dt, device=DEV, seed=500 + case,
+                                      recipe=["mid", "calibrated", "literal"][case % 3], shuffle_pages=True)
+        if case % 4 == 1:
+            q[:, ::2] = 0
+        elif case % 4 == 2:
+            q = (-q.abs()).contiguous()
+        elif case % 4 == 3:
+            q[:, :, ::5] *= 30
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ps = ops.quest_page_scores(q, cache.kmeta, cache.kv_indptr, cache.kv_indices, max_pages=cache.max_pages,
+                                   status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        for b, n in enumerate(lens):
+            npg = (n + PAGE - 1) // PAGE
+            for kh in range(hkv):
+                kmin, kmax = (t.float() for t in cache.dense_meta(b, kh))
+                for hh in range(g):
+                    h = kh * g + hh
+                    qq = q[b, h].float()
+                    want = torch.maximum(qq[None, :] * kmax, qq[None, :] * kmin).double().sum(-1)
+                    got = ps[b, h, :npg].double()
+                    err = float((got - want).abs().max()) / max(1e-6, float(want.abs().max()))
+                    assert torch.isfinite(got).all() and err <= 2e-5, (case, b, h, n, g, err)
+                    worst = max(worst, err)
+        del q, cache
+    U.record("page_scores_fuzz", worst_rel=worst)
 
 
 def test_topk_pages_seeded_fuzz_exact():

@@ -57,6 +57,38 @@ def test_reference_kernel_sink_quirks(ref):
     assert k1 == [False, True, True, True, False, False, False, False]
 
 
+@pytest.mark.parametrize("L", [2048, 8192, 32768])
+def test_reference_kernel_keeps_everything_when_no_pivot_reaches_p(ref, L):
+    """A sink with 93 % of the mass over flat dust and p = 0.95: the mass above every pivot the search
+    tries stays below p until its window closes, low stays 0 and the reference's kernel keeps every
+    token with non-zero probability.  The mask operator and the fused pruner (on the logits whose
+    softmax these probabilities are) must do the same - not keep just the sink."""
+    from twilight_b200.cache import PAGE, PagedKVCache
+    from twilight_b200.kernel import ops, top_p_fp32_return_mask
+    g = torch.Generator().manual_seed(L)
+    logits = torch.randn(1, 2, 1, L, generator=g) * 0.3
+    logits[..., 0] = float(np.log(0.93 / 0.07 * L))
+    probs = torch.softmax(logits, -1)
+    dev = probs.cuda().contiguous()
+    k1 = _k1(ref, dev, 0.95).cpu().reshape(2, L)
+    ours = top_p_fp32_return_mask(dev, 0.95).cpu().reshape(2, L)
+    assert torch.equal(k1, ours)
+    scores = logits.reshape(1, 2, L).cuda().contiguous()
+    indptr, _, last, _ = PagedKVCache.page_table([L], "cuda")
+    idx, bud = ops.topp_prune(scores, indptr, last, 0.95)
+    for r in range(2):
+        low, _ = O.top_p_search(probs.reshape(2, L)[r].numpy(), 0.95)
+        kept_ref = int(k1[r].sum())
+        if float(low) == 0.0:
+            assert kept_ref == int((probs.reshape(2, L)[r] > 0).sum())
+        got = torch.zeros(L, dtype=torch.bool)
+        got[idx[0, r, : int(bud[0, r])].cpu().long()] = True
+        diff = (got != k1[r]).nonzero().flatten()
+        # the fused pruner computes its own softmax: tokens may differ only at the threshold
+        assert (probs.reshape(2, L)[r][diff] - float(low)).abs().max().item() <= P_TOL if len(diff) else True
+        assert float(probs.reshape(2, L)[r][diff].sum()) <= 2e-4, (L, r, len(diff), kept_ref, int(bud[0, r]))
+
+
 @pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("L", [64, 1000, 4096, 32768])
 def test_fp16_entry_reference_kernel_vs_library_vs_oracle(ref, dt, L):
