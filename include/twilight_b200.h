@@ -254,7 +254,8 @@ TWL_API int twl_sparse_decode_attn_static(const void* q, int dtype, const void* 
  * Quest page scores and top-k pages (token_budget > 0; <= 0 means selector "none"), the INT4
  * estimate, the pruner (TWL_PRUNER_TOP_P with pruner_value = p or the per-row top_p_arr,
  * TWL_PRUNER_THRESHOLD with pruner_value = the threshold, TWL_PRUNER_NONE) and the sparse
- * attention, as three launches (five with Quest) on `stream`.
+ * attention, as three launches (five with Quest; one more where 2, 4 or 8 query heads share a KV head:
+ * the group attention kernel runs before the per-head one) on `stream`.
  * flags: TWL_STEP_ESTIMATED_WEIGHTS = attend with the estimated weights (attention.py:295-296);
  *        TWL_STEP_ROUND_TO_DTYPE = round the Quest page scores and the estimated logits to the model
  *        dtype where the reference's matmuls return that dtype (quest.py:76-84; attention.py:252-254,
