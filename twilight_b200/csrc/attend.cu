@@ -481,7 +481,11 @@ sparse_decode_attn_kernel(const AttParams p) {
 // merge and the output are the same.  Whether a row is served here is decided on the device from
 // the budgets (the host never sees them) and published in group_flags for the per-head kernel,
 // which runs afterwards and skips those rows.
-constexpr int kGrpWarps = 2;
+// Four warps share a work item (a chunk of 64-256 pages of one sequence and KV head): with two, an
+// item lives twice as long and the grid's tail - SMs running out of items - cost 7-9 % (config 2
+// 943 -> 877 us, config-4 shard 637 -> 583 us); with eight, a warp gets too few pages to fill its ring
+// (1011 us on config 2).
+constexpr int kGrpWarps = 4;
 constexpr int kGrpThreads = kGrpWarps * 32;
 constexpr int kGrpStageBytes = 2 * kPage * kD * 2;                       // K page, then V page: 8 KiB
 // ring of a block: `stages` whole-page stages (K page, then V page) per warp, or, with stages == 1,
@@ -526,7 +530,7 @@ __device__ __forceinline__ int warp_lower_bound(const int32_t* idx, int n, int k
 }
 
 template <typename T, int G, int kGrpStages>
-__global__ void __launch_bounds__(kGrpThreads, kGrpStages == 1 ? 8 : 6)
+__global__ void __launch_bounds__(kGrpThreads, (kGrpStages == 1 ? 16 : 12) / kGrpWarps)
 group_decode_attn_kernel(const AttParams p) {
   static_assert(G == 2 || G == 4 || G == 8, "the group sits in the upper rows of one m16 tile");
   extern __shared__ __align__(128) unsigned char sm_dyn[];  // the rings; later the warps' results
