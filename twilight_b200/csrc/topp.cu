@@ -982,6 +982,14 @@ static int run_prune(PruneParams& p, int batch, int num_q_heads, int score_strid
   // the pruner slower: 30.9 against 24.6 us on 512 rows of 8192 slots with budgets near 330.)
   const bool one_wave_512 = rows <= 3 * num_sms();
   const bool one_wave_1024 = rows <= num_sms();
+  // TWL_PRUNE_THREADS=256|512|1024 forces the block size where the row fits (for measurement)
+  static const int forced = [] {
+    const char* e = getenv("TWL_PRUNE_THREADS");
+    return e ? atoi(e) : 0;
+  }();
+  if (forced == 256 && n_max <= 8192) return launch_prune<256>(p, rows, n_max, st);
+  if (forced == 512 && n_max <= 16384) return launch_prune<512>(p, rows, n_max, st);
+  if (forced == 1024) return launch_prune<1024>(p, rows, n_max, st);
   if (n_max <= 2048) return launch_prune<256>(p, rows, n_max, st);
   if (n_max <= 8192) return one_wave_512 ? launch_prune<512>(p, rows, n_max, st) : launch_prune<256>(p, rows, n_max, st);
   if (n_max <= 16384) return one_wave_1024 ? launch_prune<1024>(p, rows, n_max, st) : launch_prune<512>(p, rows, n_max, st);
