@@ -1383,6 +1383,65 @@ def test_step_ragged_gqa(hq, hkv, sel):
     _step_vs_oracle(q, cache, hq, cfg, rows)
 
 
+def test_step_seeded_fuzz_pruner_vs_oracle_and_attention_vs_fp32():
+    """Random (batch, head grouping, lengths, selector, budget, pruner, threshold, dtype, recipe) through the
+    one-call step.  Each row's kept set is checked against the oracle pruner run on the scores the step itself
+    wrote (so the check does not depend on the estimator's rounding), and each row's output against fp32
+    attention over exactly the tokens the step kept."""
+    import math
+    rng = np.random.default_rng(21)
+    rows = 0
+    for case in range(18):
+        B = int(rng.integers(1, 4))
+        hkv = int(rng.choice([1, 2, 4]))
+        g = int(rng.choice([1, 2, 4, 8]))
+        hq = hkv * g
+        dt = [torch.bfloat16, torch.float16][case % 2]
+        lens = [int(x) for x in rng.choice([1, 17, 100, 1000, 2049, 4096, 9000, 20000], size=B)]
+        q, cache = make_decode_inputs(B, hq, hkv, lens, rho=0.02, dtype=dt, device=DEV, seed=900 + case,
+                                      recipe=["mid", "calibrated", "literal"][case % 3], shuffle_pages=True)
+        sel = str(rng.choice(["none", "quest"]))
+        tb = int(rng.choice([16, 100, 1024, 4096])) if sel == "quest" else -1
+        pr = str(rng.choice(["top_p", "top_p", "threshold", "none"]))
+        thr = float(rng.choice([0.5, 0.9, 0.95, 0.99])) if pr == "top_p" else float(rng.choice([0.5, 2.0, 6.0]))
+        cfg = SparseConfig(selector=sel, token_budget=tb, weight_pruner=pr, threshold=thr)
+        ws = DecodeWorkspace.for_cache(cache, hq, cfg)
+        out = select_prune_attend_step(q, cache, ws).clone()
+        again = select_prune_attend_step(q, cache, ws)
+        _status_ok(ws)
+        assert torch.equal(out, again), f"case {case}: a second step on the same workspace differs"
+        for b, n in enumerate(lens):
+            for h in range(hq):
+                rows += 1
+                tag = f"case {case} row ({b},{h}) len {n} group {g} {sel}/{tb} {pr}/{thr}"
+                kept = int(ws.budget[b, h])
+                idx = ws.indices[b, h, :kept].long()
+                if kept:
+                    assert bool((idx[1:] > idx[:-1]).all()) and int(idx.max()) < n, tag
+                if sel == "quest":
+                    pages = ws.cand_pages[b, h, : int(ws.cand_npages[b, h])].cpu().numpy()
+                else:
+                    pages = np.arange((n + PAGE - 1) // PAGE)
+                row = ws.scores[b, h, : len(pages) * PAGE].cpu().numpy()
+                if pr == "top_p":
+                    probs, keep, low = U.oracle_prune_row(row, pages, thr)
+                    d = U.check_index_parity(idx.cpu().numpy(), probs, keep, low, pages, P_TOL)
+                    assert abs(kept - int(keep.sum())) <= d, tag
+                elif pr == "none":
+                    assert kept == int(np.isfinite(row).sum()), tag
+                kd, vd = cache.dense_kv(b, h // g)
+                if kept == 0:
+                    ref = torch.zeros(128, device=DEV)
+                else:
+                    s = (kd[idx].float() @ q[b, h].float()) / math.sqrt(128)
+                    ref = torch.softmax(s, -1).to(dt).float() @ vd[idx].float()
+                err = (out[b, h].float() - ref).abs()
+                assert torch.isfinite(out[b, h].float()).all(), tag
+                assert float(err.max()) <= ATOL_MAX, tag
+                assert float(err.mean()) <= ATOL_MEAN + 2.0 ** -9 * float(ref.abs().mean()), tag
+    assert rows > 200
+
+
 def test_step_repeatable_and_graph_capturable():
     q, cache = make_decode_inputs(2, 8, 8, 2048, rho=0.01, dtype=torch.bfloat16, device=DEV, seed=16, recipe="mid")
     cfg = SparseConfig(selector="quest", token_budget=512, threshold=0.95)
