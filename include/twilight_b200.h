@@ -135,10 +135,12 @@ TWL_API int twl_quest_select(const void* q, int dtype, const void* kmeta, const 
  * default's block shape and bytes in flight, the copy engine instead of per-lane copies), add 32 for the
  * integer-dot kernel on query-head groups, add 256 for 16-bit float tensor-core tiles on them (codes
  * and q exact in fp16, fp32 accumulation).  By default groups of 2, 4 or 8 heads that share a KV
- * head's pages are scored with 8-bit integer tensor-core tiles: one m16n8k32 tile per page and
- * 32-channel quantisation group against the high and one against the low bytes of q as 13-bit
- * block-scaled integers (the integer dot product is exact; q is rounded to 2^-13 of the head's
- * largest element, as in the single-head kernel).  The non-default variants exist for measurement. */
+ * head's pages are scored with 8-bit integer tensor-core tiles: q as 13-bit block-scaled integers
+ * split into a high and a low byte (the integer dot product is exact; q is rounded to 2^-13 of the
+ * head's largest element, as in the single-head kernel).  Groups of 2 and 4 heads put both bytes of
+ * every head into the eight columns of ONE m16n8k32 tile per page and 32-channel quantisation
+ * group; groups of 8 heads use one tile for the high and one for the low bytes (add 512 to use
+ * that form for the smaller groups too).  The non-default variants exist for measurement. */
 TWL_API int twl_estimate_int4(const void* q, int dtype, const uint8_t* k4_pages,
                       const int32_t* kv_indptr, const int32_t* kv_indices,
                       const int32_t* kv_last_page_len, const int32_t* cand_pages,

@@ -992,9 +992,10 @@ def test_attention_workspace_and_bad_index_handling():
                                        (16, 2, torch.float16), (4, 2, torch.bfloat16)])
 def test_group_estimator_tensor_core_equals_integer_dot(hq, hkv, dt):
     """Default estimator for query-head groups (8-bit integer tensor-core tiles, q as 13-bit
-    block-scaled integers like the single-head kernel) and its 16-bit float tile form (variant +256)
-    against the integer-dot group kernel (variant +32) and the fp64 oracle, ragged lengths with odd
-    page counts."""
+    block-scaled integers like the single-head kernel; groups of 2 and 4 heads with both digits of q in
+    one tile, which variant +512 switches off), and its 16-bit float tile form (variant +256), against
+    the integer-dot group kernel (variant +32) and the fp64 oracle, ragged lengths with odd page
+    counts."""
     lens = [1, 17, 33, 1000, 2049, 4000, 16 * 129]
     q, cache = make_decode_inputs(len(lens), hq, hkv, lens, rho=0.02, dtype=dt, device=DEV, seed=61,
                                   recipe="mid", shuffle_pages=True)
@@ -1005,7 +1006,7 @@ def test_group_estimator_tensor_core_equals_integer_dot(hq, hkv, dt):
     g = hq // hkv
     # (variant, bound on the error relative to the row's largest |logit|): the float tiles multiply
     # exact values and accumulate in fp32; the integer tiles round q to 13 bits first
-    for variant, bound in ((0, 2e-4), (3 + 256, 2e-4)):
+    for variant, bound in ((0, 2e-4), (3 + 512, 2e-4), (3 + 256, 2e-4)):
         a = ops.estimate_int4(q, cache.k4_pages, cache.kv_indptr, cache.kv_indices, cache.kv_last_page_len,
                               variant=variant, **kw)
         assert int(status.item()) == 0

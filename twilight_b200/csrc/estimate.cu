@@ -36,7 +36,7 @@ struct EstParams {
   const int32_t* cand_npages;
   float* scores;
   int32_t* status;
-  int max_k, B, Hq, Hkv, num_pages_total, stride, pages_per_block, force_ring, simt_group, bulk_warp, f16_tiles;
+  int max_k, B, Hq, Hkv, num_pages_total, stride, pages_per_block, force_ring, simt_group, bulk_warp, f16_tiles, two_tiles;
   float sm_scale;
 };
 
@@ -1460,12 +1460,302 @@ estimate_int4_imma_group_kernel(const EstParams p) {
   cp_async_wait<0>();
 }
 
+// ---- groups of up to four query heads: both digits of q in one integer tile --------------------
+// With G <= 4 the eight columns of a m16n8k32 tile hold the hi digits of the G heads (columns 0..3)
+// and their lo digits (columns 4..7): q_d ~= (256*hi_d + lo_d) * 2^-e with lo in [-128, 127] and
+// |hi| <= 32, both signed bytes, so one tile per (page, group) does what the kernel above needs two
+// for.  Lanes t = 0, 1 of a quad then own hi-digit columns and lanes t = 2, 3 the lo-digit columns
+// of the same heads; each lane sums scale * dot over the page's four groups for its own columns,
+// and the two digits meet once per page (one exchange across the quad) instead of once per group:
+// the lane with the hi digits finishes token g, its partner token g + 8, and each stores its own.
+// The term sum_groups min * (sum of the group's q integers) is a 16 x 8 x 8 product of its own
+// (tokens x {group, half of the sum} x heads): one 16-bit float tile per page, whose result
+// initialises the hi lanes' sums.  The {scale, min} pairs of the slab are its A operand as they
+// lie (min duplicated into both halves); the sums are split into a 16-bit float and the exact
+// remainder, both divided by 256 so that 256 * hi + lo restores them.
+struct HmmaK8 {
+  static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "f"(0.f));
+  }
+};
+
+template <typename T, int G, int NW, int DEPTH, int NBLK>
+__global__ void __launch_bounds__(NW * 32, NBLK)
+estimate_int4_imma_digits_kernel(const EstParams p) {
+  constexpr int kPagesHere = NW * 16;  // eight ring stages of two pages per warp
+  static_assert(G >= 2 && G <= 4, "hi and lo digits of the group share one n8 tile");
+  extern __shared__ __align__(128) uint8_t sm_ring[];  // NW * DEPTH * kWarpStageBytes: a ring of two-page stages per warp
+  __shared__ int sm_phys[kPagesHere + 1];
+  __shared__ int sm_ntok[kPagesHere + 1];
+
+  const int row = blockIdx.y;
+  const int b = row / p.Hkv, kvh = row % p.Hkv;
+  const int h = kvh * G;  // first query head of the group
+  pdl_wait();  // q and the page table may come from the kernel before; scores may still be read by an older one
+  const int page_base = p.indptr[b];
+  const int n_seq_pages = p.indptr[b + 1] - page_base;
+  int n_pages = n_seq_pages;
+  if (n_pages > p.stride / kPage) {
+    n_pages = p.stride / kPage;
+    if (threadIdx.x == 0 && blockIdx.x == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+  }
+  const int first = blockIdx.x * kPagesHere;
+  if (first >= n_pages) return;
+  const int n_here = min(kPagesHere, n_pages - first);
+
+  const int tid = threadIdx.x;
+  if (tid <= kPagesHere) {  // one entry more than pages: the partner of an odd last page
+    int phys = -1, ntok = 0;
+    if (tid < n_here) {
+      const int seq_page = first + tid;
+      phys = p.indices[page_base + seq_page];
+      if (phys < 0 || phys >= p.num_pages_total) phys = -1;
+      if (phys < 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
+      ntok = (seq_page == n_seq_pages - 1) ? p.last_len[b] : kPage;
+    }
+    sm_phys[tid] = phys;
+    sm_ntok[tid] = phys < 0 ? 0 : ntok;  // 0 tokens: every slot of the page scores -inf
+  }
+  __syncthreads();
+
+  const int lane = tid & 31, warp = tid >> 5;
+  const int gq = lane >> 2, t = lane & 3;
+  uint8_t* const ring = sm_ring + (size_t)warp * DEPTH * kWarpStageBytes;
+  const uint32_t ring_u32 = smem_u32(ring);
+  const int n_pairs = (n_here + 1) >> 1;
+  const int my_pairs = (n_pairs > warp) ? (n_pairs - warp + NW - 1) / NW : 0;
+
+  // the five 16-byte copies of a stage, as in the kernels above
+  uint32_t src_off[5], dst_off[5];
+#pragma unroll
+  for (int c5 = 0; c5 < 5; ++c5) {
+    const int c = c5 * 32 + lane;
+    const int pgl = c >= 80 ? 1 : 0;
+    const int r = c - pgl * 80;
+    src_off[c5] = r * 16;
+    if (r < 64) {
+      const int tk = pgl * 16 + (r >> 2), g4 = r & 3;
+      dst_off[c5] = tk * 64 + (((g4 + (tk >> 1)) & 3) << 4);
+    } else {
+      dst_off[c5] = 2048 + (pgl * 16 + (r - 64)) * 16;
+    }
+  }
+  const bool third_is_second = lane >= 16;
+  const uint8_t* const k4_head = p.k4 + (size_t)kvh * kSlab;
+  const size_t page_stride = (size_t)p.Hkv * kSlab;
+
+  auto issue = [&](int i, int slot) {
+    if (i < my_pairs) {
+      const int pg0 = (warp + i * NW) * 2;
+      const uint32_t dst0 = ring_u32 + slot * kWarpStageBytes;
+      const uint8_t* const s0 = k4_head + (size_t)max(sm_phys[pg0], 0) * page_stride;
+      const uint8_t* const s1 = k4_head + (size_t)max(sm_phys[pg0 + 1], 0) * page_stride;
+      const uint8_t* const s2 = third_is_second ? s1 : s0;
+      cp_async16(dst0 + dst_off[0], s0 + src_off[0]);
+      cp_async16(dst0 + dst_off[1], s0 + src_off[1]);
+      cp_async16(dst0 + dst_off[2], s2 + src_off[2]);
+      cp_async16(dst0 + dst_off[3], s1 + src_off[3]);
+      cp_async16(dst0 + dst_off[4], s1 + src_off[4]);
+    }
+    cp_async_commit();  // always commit so that group counting stays uniform
+  };
+
+#pragma unroll
+  for (int i = 0; i < DEPTH - 1; ++i) issue(i, i);
+
+  // Column gq of the tile: the hi digits of head gq (gq < 4) or the lo digits of head gq - 4, this
+  // lane's channels 8t..8t+7 of every group (even ones, then odd ones).  Column gq of the min tile:
+  // head gq's group sums (rows 2t, 2t+1: group t's sum as a 16-bit float and the remainder).
+  uint32_t bd[4][2];
+  uint32_t bmin;
+  float c_own_a, c_own_b, c_x_a, c_x_b;
+  const bool hi_lane = t < 2;
+  {
+    const int hh = gq & 3;
+    const bool valid = hh < G;
+    const bool lo_digit = gq >= 4;
+    const T* qrow = reinterpret_cast<const T*>(p.q) + (size_t)(b * p.Hq + h + (valid ? hh : 0)) * kD;
+    float qf[4][8];
+    float amax = 0.f;
+#pragma unroll
+    for (int grp = 0; grp < 4; ++grp) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(qrow) + 4 * grp + t);
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = Elem<T>::to_f2(u[k]);
+        qf[grp][2 * k] = valid ? f.x : 0.f;
+        qf[grp][2 * k + 1] = valid ? f.y : 0.f;
+        amax = fmaxf(amax, fmaxf(fabsf(qf[grp][2 * k]), fabsf(qf[grp][2 * k + 1])));
+      }
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));  // over the head's 128 channels
+    int e = (amax > 0.f && amax < INFINITY) ? (12 - ilogbf(amax)) : 0;  // amax * 2^e in [2^12, 2^13)
+    e = max(-100, min(100, e));
+    const float up = ldexpf(1.f, e);
+    const float undo = p.sm_scale * ldexpf(1.f, -e);
+    const float os_a = __shfl_sync(0xffffffffu, undo, (2 * (t & 1)) * 4);      // head 2(t&1)
+    const float os_b = __shfl_sync(0xffffffffu, undo, (2 * (t & 1) + 1) * 4);  // head 2(t&1) + 1
+    c_own_a = hi_lane ? 256.f * os_a : os_a;
+    c_x_a = hi_lane ? os_a : 256.f * os_a;
+    c_own_b = hi_lane ? 256.f * os_b : os_b;
+    c_x_b = hi_lane ? os_b : 256.f * os_b;
+    int gsum[4];
+#pragma unroll
+    for (int grp = 0; grp < 4; ++grp) {
+      int sum = 0;
+      uint32_t ev = 0, od = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int a = __float2int_rn(qf[grp][2 * k] * up);      // channel 8t + 2k
+        const int c = __float2int_rn(qf[grp][2 * k + 1] * up);  // channel 8t + 2k + 1
+        sum += a + c;
+        const int ah = (a + 128) >> 8, ch = (c + 128) >> 8;     // a = 256 * ah + al, al in [-128, 127]
+        const int da = lo_digit ? a - (ah << 8) : ah;
+        const int dc = lo_digit ? c - (ch << 8) : ch;
+        ev |= (uint32_t)(da & 0xFF) << (8 * k);
+        od |= (uint32_t)(dc & 0xFF) << (8 * k);
+      }
+      bd[grp][0] = ev; bd[grp][1] = od;
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);  // over the group's 32 channels, head gq & 3
+      gsum[grp] = sum;
+    }
+    const int mine = t == 0 ? gsum[0] : t == 1 ? gsum[1] : t == 2 ? gsum[2] : gsum[3];
+    const float sf = (float)mine * (1.f / 256.f);      // |sum| < 2^18: exact
+    const __half s_hi = __float2half_rn(sf);
+    const __half s_lo = __float2half_rn(sf - __half2float(s_hi));  // a multiple of 2^-8 below 2^-1: exact
+    const __half2 pair = __halves2half2(s_hi, s_lo);
+    bmin = (gq < G) ? *reinterpret_cast<const uint32_t*>(&pair) : 0u;
+  }
+
+  // ldmatrix row addresses: matrix lane >> 3 = {tokens 0-7, tokens 8-15} x {group 2j, group 2j + 1};
+  // the lane then holds word t of token gq (and of token gq + 8) of both groups' 16-byte pieces
+  uint32_t lm_off[2];
+  {
+    const int mat = lane >> 3, tok = (lane & 7) + 8 * (mat & 1);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) lm_off[j] = tok * 64 + (((2 * j + (mat >> 1) + (tok >> 1)) & 3) << 4);
+  }
+  const uint32_t sz_off = 2048 + gq * 16;  // {scale, min} x 4 groups of token gq; +128 per eight tokens
+
+  const int tk_own = gq + (hi_lane ? 0 : 8);  // the token of a page that this lane finishes and stores
+  float* const out_a = p.scores + (size_t)(b * p.Hq + h + 2 * (t & 1)) * p.stride + (size_t)first * kPage + tk_own;
+  const bool own_a = 2 * (t & 1) < G, own_b = 2 * (t & 1) + 1 < G;
+  uint32_t stage_off = 0;
+  int fill_slot = DEPTH - 1;
+  constexpr int kMagicBits = 0x4B400000;   // 1.5 * 2^23 as a float
+  constexpr float kMagic = 12582912.f;
+  for (int i = 0; i < my_pairs; ++i) {
+    cp_async_wait<DEPTH - 2>();  // pair i has landed (this thread's copies)
+    __syncwarp();                     // ... and every other lane's
+    const uint8_t* const stage = ring + stage_off;
+    const uint32_t stage_u32 = ring_u32 + stage_off;
+    float res[2][2];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {  // one page = one m16 tile per group
+      const uint4 sza = *reinterpret_cast<const uint4*>(stage + sz_off + mt * 256);
+      const uint4 szb = *reinterpret_cast<const uint4*>(stage + sz_off + mt * 256 + 128);
+      const uint32_t ma = *reinterpret_cast<const uint32_t*>(stage + sz_off + mt * 256 + t * 4);
+      const uint32_t mb = *reinterpret_cast<const uint32_t*>(stage + sz_off + mt * 256 + 128 + t * 4);
+      float r[4];
+      HmmaK8::run(r, __byte_perm(ma, 0, 0x3232), __byte_perm(mb, 0, 0x3232), bmin);
+      const uint32_t sa[4] = {sza.x, sza.y, sza.z, sza.w}, sb[4] = {szb.x, szb.y, szb.z, szb.w};
+      uint32_t w[2][4];  // per pair of groups: {token gq, token gq+8} x {group 2j, group 2j+1}
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(w[j][0]), "=r"(w[j][1]), "=r"(w[j][2]), "=r"(w[j][3])
+                     : "r"(stage_u32 + lm_off[j] + mt * 1024));
+#pragma unroll
+      for (int grp = 0; grp < 4; ++grp) {
+        const uint32_t wa = w[grp >> 1][2 * (grp & 1)], wb = w[grp >> 1][2 * (grp & 1) + 1];
+        const uint32_t a0 = wa & 0x0F0F0F0Fu, a2 = (wa >> 4) & 0x0F0F0F0Fu;
+        const uint32_t a1 = wb & 0x0F0F0F0Fu, a3 = (wb >> 4) & 0x0F0F0F0Fu;
+        int d[4];
+        ImmaTile::run_s8(d, a0, a1, a2, a3, bd[grp][0], bd[grp][1], kMagicBits);
+        const float s0 = __low2float(*reinterpret_cast<const __half2*>(&sa[grp]));  // scale of token gq
+        const float s8 = __low2float(*reinterpret_cast<const __half2*>(&sb[grp]));  // ... of token gq + 8
+        r[0] = fmaf(s0, __int_as_float(d[0]) - kMagic, r[0]);
+        r[1] = fmaf(s0, __int_as_float(d[1]) - kMagic, r[1]);
+        r[2] = fmaf(s8, __int_as_float(d[2]) - kMagic, r[2]);
+        r[3] = fmaf(s8, __int_as_float(d[3]) - kMagic, r[3]);
+      }
+      // the hi lane finishes token gq with the partner's lo sums, the lo lane token gq + 8 with the partner's hi sums
+      const float x0 = __shfl_xor_sync(0xffffffffu, hi_lane ? r[2] : r[0], 2);
+      const float x1 = __shfl_xor_sync(0xffffffffu, hi_lane ? r[3] : r[1], 2);
+      res[mt][0] = fmaf(hi_lane ? r[0] : r[2], c_own_a, x0 * c_x_a);
+      res[mt][1] = fmaf(hi_lane ? r[1] : r[3], c_own_b, x1 * c_x_b);
+    }
+    __syncwarp();      // all lanes are done reading the slot that the next issue overwrites
+    issue(i + DEPTH - 1, fill_slot);
+    fill_slot = (fill_slot + 1 == DEPTH) ? 0 : fill_slot + 1;
+    stage_off = (stage_off + kWarpStageBytes == DEPTH * kWarpStageBytes) ? 0 : stage_off + kWarpStageBytes;
+    const int pg0 = (warp + i * NW) * 2;
+    if (pg0 + 1 < n_here && sm_ntok[pg0] == kPage && sm_ntok[pg0 + 1] == kPage) {
+      // two whole pages (all but the last stage of a sequence): nothing to mask
+      if (own_a) {
+        float* const o = out_a + pg0 * kPage;
+        o[0] = res[0][0];
+        o[kPage] = res[1][0];
+        if (own_b) {
+          o[p.stride] = res[0][1];
+          o[p.stride + kPage] = res[1][1];
+        }
+      }
+    } else if (own_a) {
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const int pg = pg0 + mt;
+        if (pg < n_here) {
+          const bool live = tk_own < sm_ntok[pg];  // 0 tokens for a page whose table entry was out of range
+          float* const o = out_a + pg * kPage;
+          o[0] = live ? res[mt][0] : -INFINITY;
+          if (own_b) o[p.stride] = live ? res[mt][1] : -INFINITY;
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+}
+
+template <typename T, int G, int NW, int DEPTH, int NBLK>
+static int launch_digits(const EstParams& p, int rows, int max_row_pages, cudaStream_t st) {
+  constexpr int kBytes = NW * DEPTH * kWarpStageBytes;
+  auto kern = estimate_int4_imma_digits_kernel<T, G, NW, DEPTH, NBLK>;
+  TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+  dim3 grid((max_row_pages + NW * 16 - 1) / (NW * 16), rows);
+  TWL_CUDA_TRY(launch_chain(kern, grid, dim3(NW * 32), kBytes, st, p));
+  return TWL_OK;
+}
+
 template <typename T, int G, int VARIANT>
 static int launch_one(const EstParams& p, int rows, int max_row_pages, bool ldg, cudaStream_t st) {
   if (rows > 65535) return TWL_ERR_TOO_LARGE;
   if (ldg) {
     dim3 grid((max_row_pages + kPagesPerBlock - 1) / kPagesPerBlock, rows);
     estimate_int4_kernel<T, G, VARIANT><<<grid, kEstThreads, 0, st>>>(p);
+  } else if (G > 1 && G <= 4 && VARIANT == VAR_DP4A && !p.force_ring && !p.simt_group && !p.f16_tiles && !p.two_tiles) {
+    // Block shape: the kernel wants warps, not ring depth.  Config 2 (856 MB of slabs, 2048 rows), warps x ring
+    // stages x blocks per SM: 8 x 5 x 2 (16 warps per SM, 110 registers) 178.5 us; 4 x 5 x 4 170.4; 10 x 4 x 2
+    // 185.2; 12 x 3 x 2 168.2; 8 x 3 x 3 (24 warps, 80 registers) 163.8-165.8; 2 x 3 x 12 162.9; 4 x 3 x 6 162.5;
+    // 8 x 2 x 4 and 4 x 2 x 8 (32 warps, 64 registers, spills) 182.4 / 177.8.
+    // TWL_EST_DIGITS_SHAPE = 1..4 picks one of the others, for measurement.
+    constexpr int GG = (G > 1 && G <= 4) ? G : 2;
+    static const int shape = [] { const char* e = getenv("TWL_EST_DIGITS_SHAPE"); return e ? atoi(e) : 0; }();
+    int rc = TWL_OK;
+    switch (shape) {
+      case 1: rc = launch_digits<T, GG, 8, 5, 2>(p, rows, max_row_pages, st); break;
+      case 2: rc = launch_digits<T, GG, 8, 3, 3>(p, rows, max_row_pages, st); break;
+      case 3: rc = launch_digits<T, GG, 2, 3, 12>(p, rows, max_row_pages, st); break;
+      case 4: rc = launch_digits<T, GG, 4, 5, 4>(p, rows, max_row_pages, st); break;
+      default: rc = launch_digits<T, GG, 4, 3, 6>(p, rows, max_row_pages, st); break;
+    }
+    if (rc != TWL_OK) return rc;
   } else if (G > 1 && VARIANT == VAR_DP4A && !p.force_ring && !p.simt_group && !p.f16_tiles) {
     constexpr int kBytes = kEstWarps * kRingDepth * kWarpStageBytes;
     auto kern = estimate_int4_imma_group_kernel<T, (G > 1 ? G : 2)>;
@@ -1535,6 +1825,7 @@ static int launch_dtype(const EstParams& p, bool has_cand, int max_row_pages, in
   const_cast<EstParams&>(p).simt_group = (variant & 32) != 0;  // +32: integer-dot kernel for query-head groups
   const_cast<EstParams&>(p).bulk_warp = (variant & 64) != 0;   // +64: warp-private rings fed by bulk copies
   const_cast<EstParams&>(p).f16_tiles = (variant & 256) != 0;  // +256: 16-bit float tiles for query-head groups
+  const_cast<EstParams&>(p).two_tiles = (variant & 512) != 0;  // +512: hi and lo digits in two integer tiles even for groups of 2 or 4
   const bool ldg = (variant & 16) != 0;
   switch (variant & 15) {
     case VAR_F32: return launch_variant<T, VAR_F32>(p, has_cand, max_row_pages, ldg, st);
