@@ -509,24 +509,50 @@ __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// First position of the ascending list idx[0..n) whose value is >= key; the warp probes 32 places
-// per step, so three dependent loads settle a list of 32768 entries.
-__device__ __forceinline__ int warp_lower_bound(const int32_t* idx, int n, int key, int lane) {
-  int lo = 0, hi = n;
-  while (lo < hi) {
-    const int step = (hi - lo + 31) >> 5;
-    const int q = lo + lane * step;
-    const bool less = q < hi && idx[q] < key;
-    const int cnt = __popc(__ballot_sync(0xffffffffu, less));  // the probes below key are a prefix
-    if (cnt == 0) {
-      hi = lo;
-    } else {
-      const int nlo = lo + (cnt - 1) * step + 1;
-      hi = min(hi, lo + cnt * step);
-      lo = nlo;
+// First positions of ascending lists whose value is >= a key: search s looks for key[s & 1] in the list
+// idx[s >> 1][0..n[s >> 1]).  The warp probes 32 places per step, so three dependent loads settle a
+// list of 32768 entries; the NS searches advance in lockstep, their probes of a step in flight
+// together, so the whole set costs the latency of one search.
+template <int NS>
+__device__ __forceinline__ void warp_lower_bounds(const int32_t* const (&idx)[NS / 2], const int (&n)[NS / 2],
+                                                  const int (&key)[2], int lane, int (&pos)[NS]) {
+  int lo[NS], hi[NS];
+#pragma unroll
+  for (int s = 0; s < NS; ++s) {
+    lo[s] = 0;
+    hi[s] = n[s >> 1];
+  }
+  while (true) {
+    bool any = false;
+    int val[NS], step[NS];
+    bool inb[NS];
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      const bool open = lo[s] < hi[s];  // warp-uniform
+      any = any || open;
+      step[s] = (hi[s] - lo[s] + 31) >> 5;
+      const int q = lo[s] + lane * step[s];
+      inb[s] = open && q < hi[s];
+      val[s] = inb[s] ? idx[s >> 1][q] : 0;
+    }
+    if (!any) break;
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      if (lo[s] < hi[s]) {
+        const bool less = inb[s] && val[s] < key[s & 1];
+        const int cnt = __popc(__ballot_sync(0xffffffffu, less));  // the probes below key are a prefix
+        if (cnt == 0) {
+          hi[s] = lo[s];
+        } else {
+          const int nlo = lo[s] + (cnt - 1) * step[s] + 1;
+          hi[s] = min(hi[s], lo[s] + cnt * step[s]);
+          lo[s] = nlo;
+        }
+      }
     }
   }
-  return lo;
+#pragma unroll
+  for (int s = 0; s < NS; ++s) pos[s] = lo[s];
 }
 
 template <typename T, int G, int kGrpStages>
@@ -540,7 +566,7 @@ group_decode_attn_kernel(const AttParams p) {
   uint32_t* const sm_mask = reinterpret_cast<uint32_t*>(sm_uphys + cpm);   // [G][cpm / 2] kept-token bits, two pages a word
   uint16_t* const sm_upage = reinterpret_cast<uint16_t*>(sm_mask + G * (cpm / 2));  // [cpm] pages with any kept token
   uint16_t* const sm_ubits = sm_upage + cpm;                               // [cpm] which of their tokens any head keeps
-  __shared__ int sm_nunion;
+  __shared__ int sm_segcnt[kGrpMaxChunkPages / 32];
   __shared__ int sm_ticket[G];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -564,67 +590,8 @@ group_decode_attn_kernel(const AttParams p) {
   if (c >= n_chunks) return;
   const int p0 = c * cp, p1 = min(pages_b, p0 + cp), npg = p1 - p0;
 
-  // ---- kept-token bits of every head for the pages of this chunk ----
-  for (int i = tid; i < G * (cpm / 2); i += kGrpThreads) sm_mask[i] = 0u;
-  __syncthreads();
-  bool bad = false;
-  for (int hh = warp; hh < G; hh += kGrpWarps) {
-    const int32_t* idx = p.idx + (size_t)(row0 + hh) * p.index_stride;
-    const int n = __shfl_sync(0xffffffffu, bud_l, hh);
-    const int s0 = warp_lower_bound(idx, n, p0 * kPage, lane);
-    const int s1 = warp_lower_bound(idx, n, p1 * kPage, lane);
-    if (c == n_chunks - 1 && s1 < n) bad = true;  // tokens past the last page of the sequence
-    const int per = (s1 - s0 + 31) >> 5;
-    const int a = s0 + lane * per, e = min(s1, a + per);
-    int cur = -1;
-    uint32_t bits = 0;
-    for (int i = a; i < e; ++i) {
-      const int tok = idx[i];
-      const int pg = (tok >> 4) - p0;
-      if (pg != cur) {
-        if (cur >= 0 && cur < npg) atomicOr(&sm_mask[hh * (cpm / 2) + (cur >> 1)], bits << ((cur & 1) * 16));
-        cur = pg;
-        bits = 0;
-      }
-      bits |= 1u << (tok & 15);
-    }
-    if (cur >= 0 && cur < npg) atomicOr(&sm_mask[hh * (cpm / 2) + (cur >> 1)], bits << ((cur & 1) * 16));
-  }
-  __syncthreads();
-  // ---- pages with any kept token, and where they lie ----
-  if (warp == 0) {
-    int n_u = 0;
-    for (int j0 = 0; j0 < npg; j0 += 32) {
-      const int j = j0 + lane;
-      uint32_t u = 0;
-      if (j < npg) {
-#pragma unroll
-        for (int hh = 0; hh < G; ++hh) u |= (sm_mask[hh * (cpm / 2) + (j >> 1)] >> ((j & 1) * 16)) & 0xFFFFu;
-      }
-      int phys = -1;
-      if (u != 0) {
-        phys = p.indices[page_base + p0 + j];
-        if (phys < 0 || phys >= p.num_pages_total) {
-          phys = -1;
-          bad = true;
-        }
-      }
-      const unsigned m = __ballot_sync(0xffffffffu, phys >= 0);
-      if (phys >= 0) {
-        const int pos = n_u + __popc(m & ((1u << lane) - 1));
-        sm_upage[pos] = (uint16_t)j;
-        sm_ubits[pos] = (uint16_t)(p.group_skip_rows ? u : 0xFFFFu);
-        sm_uphys[pos] = phys;
-      }
-      n_u += __popc(m);
-    }
-    if (lane == 0) sm_nunion = n_u;
-  }
-  __syncthreads();
-  if (__any_sync(0xffffffffu, bad) && lane == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
-  const int n_union = sm_nunion;
-
-  // ---- Q as the A operand: row g = head g (rows from G on are zero), eight k-steps of 16 channels ----
+  // ---- Q as the A operand: row g = head g (rows from G on are zero), eight k-steps of 16 channels
+  // (fetched first: the loads are under way while the index lists are searched) ----
   const int g = lane >> 2, t = lane & 3;
   uint32_t qa[8][2];
   {
@@ -636,6 +603,118 @@ group_decode_attn_kernel(const AttParams p) {
       qa[ks][1] = g < G ? __ldg(qrow + 8 * ks + 4 + t) : 0u;  // channels 16ks + 8 + 2t, +1
     }
   }
+
+  // ---- kept-token bits of every head for the pages of this chunk ----
+  for (int i = tid; i < G * (cpm / 2); i += kGrpThreads) sm_mask[i] = 0u;
+  __syncthreads();
+  bool bad = false;
+  {
+    // a warp's heads (warp, warp + kGrpWarps, ...): where the chunk begins and ends in each one's
+    // ascending index list, all searches in lockstep
+    constexpr int HPW = (G + kGrpWarps - 1) / kGrpWarps;
+    const int32_t* lists[HPW];
+    int ns[HPW], pos[2 * HPW];
+#pragma unroll
+    for (int j = 0; j < HPW; ++j) {
+      const int hh = warp + j * kGrpWarps;
+      lists[j] = p.idx + (size_t)(row0 + (hh < G ? hh : 0)) * p.index_stride;
+      ns[j] = __shfl_sync(0xffffffffu, bud_l, hh & 31);
+      if (hh >= G) ns[j] = 0;
+    }
+    const int keys[2] = {p0 * kPage, p1 * kPage};
+    warp_lower_bounds<2 * HPW>(lists, ns, keys, lane, pos);
+#pragma unroll
+    for (int j = 0; j < HPW; ++j) {
+      const int hh = warp + j * kGrpWarps;
+      if (hh >= G) continue;
+      const int32_t* idx = lists[j];
+      const int s0 = pos[2 * j], s1 = pos[2 * j + 1];
+      if (c == n_chunks - 1 && s1 < ns[j]) bad = true;  // tokens past the last page of the sequence
+      // each lane owns a run of whole 16-byte groups of the list (a row of the index array starts on a 64-byte
+      // boundary); four groups at a time are in flight before the first is used
+      const int a4 = s0 >> 2, e4 = (s1 + 3) >> 2;
+      const int per = (e4 - a4 + 31) >> 5;
+      const int la = a4 + lane * per, le = min(e4, la + per);
+      const int4* const idx4 = reinterpret_cast<const int4*>(idx);
+      int cur = -1;
+      uint32_t bits = 0;
+      for (int i = la; i < le; i += 4) {
+        int4 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = idx4[min(i + k, le - 1)];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int tk[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+          for (int m = 0; m < 4; ++m) {
+            const int at = (i + k) * 4 + m;  // position in the list
+            if (i + k < le && at >= s0 && at < s1) {
+              const int pg = (tk[m] >> 4) - p0;
+              if (pg != cur) {
+                if (cur >= 0 && cur < npg) atomicOr(&sm_mask[hh * (cpm / 2) + (cur >> 1)], bits << ((cur & 1) * 16));
+                cur = pg;
+                bits = 0;
+              }
+              bits |= 1u << (tk[m] & 15);
+            }
+          }
+        }
+      }
+      if (cur >= 0 && cur < npg) atomicOr(&sm_mask[hh * (cpm / 2) + (cur >> 1)], bits << ((cur & 1) * 16));
+    }
+  }
+  __syncthreads();
+  int n_union;
+  // ---- pages with any kept token, and where they lie: every warp takes 32-page segments of the chunk, so that
+  // the page-table reads of the whole chunk are in flight together; the segments' counts give their offsets ----
+  {
+    constexpr int kSegs = kGrpMaxChunkPages / 32, kSegsPerWarp = (kSegs + kGrpWarps - 1) / kGrpWarps;
+    static_assert(kSegs % kGrpWarps == 0 && kSegs <= 32, "whole segments per warp; one lane per segment in the scan");
+    uint32_t u[kSegsPerWarp];
+    int phys[kSegsPerWarp];
+    unsigned m[kSegsPerWarp];
+#pragma unroll
+    for (int k = 0; k < kSegsPerWarp; ++k) {
+      const int j = (warp + k * kGrpWarps) * 32 + lane;
+      u[k] = 0;
+      if (j < npg) {
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) u[k] |= (sm_mask[hh * (cpm / 2) + (j >> 1)] >> ((j & 1) * 16)) & 0xFFFFu;
+      }
+      phys[k] = u[k] != 0 ? p.indices[page_base + p0 + j] : -1;
+    }
+#pragma unroll
+    for (int k = 0; k < kSegsPerWarp; ++k) {
+      if (u[k] != 0 && (phys[k] < 0 || phys[k] >= p.num_pages_total)) {
+        phys[k] = -1;
+        bad = true;
+      }
+      m[k] = __ballot_sync(0xffffffffu, phys[k] >= 0);
+      if (lane == 0) sm_segcnt[warp + k * kGrpWarps] = __popc(m[k]);
+    }
+    __syncthreads();
+    const int cnt_l = lane < kSegs ? sm_segcnt[lane] : 0;
+    int inc = cnt_l;  // inclusive prefix sums of the segments' counts
+#pragma unroll
+    for (int o = 1; o < kSegs; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += up;
+    }
+#pragma unroll
+    for (int k = 0; k < kSegsPerWarp; ++k) {
+      const int seg = warp + k * kGrpWarps;
+      const int base = __shfl_sync(0xffffffffu, inc - cnt_l, seg & 31);
+      if (seg < kSegs && phys[k] >= 0) {
+        const int pos = base + __popc(m[k] & ((1u << lane) - 1));
+        sm_upage[pos] = (uint16_t)(seg * 32 + lane);
+        sm_ubits[pos] = (uint16_t)(p.group_skip_rows ? u[k] : 0xFFFFu);
+        sm_uphys[pos] = phys[k];
+      }
+    }
+    n_union = __shfl_sync(0xffffffffu, inc, kSegs - 1);
+  }
+  __syncthreads();
+  if (__any_sync(0xffffffffu, bad) && lane == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
 
   unsigned char* const my_ring = sm_dyn + warp * (grp_ring_bytes(kGrpStages) / kGrpWarps);
   const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
@@ -1036,7 +1115,9 @@ static int attn_entry(const void* q, int dtype, const void* k_pages, const void*
   p.idx = indices; p.budget = budget; p.out = out; p.status = status; p.weights = weights;
   char* ws = static_cast<char*>(workspace);
   p.counters = reinterpret_cast<int32_t*>(ws);
-  p.group_flags = (weights == nullptr && group_path_enabled(num_q_heads, num_kv_heads)) ? p.counters + rows : nullptr;
+  // the group kernel reads the index lists in 16-byte pieces
+  const bool lists16 = aligned(indices, 16) && index_stride % 4 == 0;
+  p.group_flags = (weights == nullptr && lists16 && group_path_enabled(num_q_heads, num_kv_heads)) ? p.counters + rows : nullptr;
   ws += align_up(2 * rows * sizeof(int32_t), 256);
   p.part_ml = reinterpret_cast<float*>(ws);
   ws += align_up(rows * kMaxChunksPerRow * 2 * sizeof(float), 256);
@@ -1159,7 +1240,8 @@ extern "C" int twl_sparse_decode_attn_static(const void* q, int dtype, const voi
   p.idx = indices; p.budget = budget; p.out = out; p.status = status; p.weights = nullptr;
   char* ws = static_cast<char*>(scratch);
   p.counters = reinterpret_cast<int32_t*>(ws);
-  p.group_flags = group_path_enabled(num_q_heads, num_kv_heads) ? p.counters + rows : nullptr;
+  const bool lists16 = aligned(indices, 16) && index_stride % 4 == 0;  // the group kernel reads 16-byte pieces
+  p.group_flags = (lists16 && group_path_enabled(num_q_heads, num_kv_heads)) ? p.counters + rows : nullptr;
   p.part_ml = reinterpret_cast<float*>(ws + kStaticCounterBytes);
   p.part_o = reinterpret_cast<float*>(ws + kStaticCounterBytes + kStaticMlBytes);
   p.index_stride = index_stride; p.rows = (int)rows; p.Hq = num_q_heads; p.Hkv = num_kv_heads;

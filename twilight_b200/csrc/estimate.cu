@@ -1244,13 +1244,14 @@ struct ImmaTile {
   }
 };
 
-template <typename T, int G>
-__global__ void __launch_bounds__(kEstThreads, 2)
+template <typename T, int G, int NW, int DEPTH, int NBLK>
+__global__ void __launch_bounds__(NW * 32, NBLK)
 estimate_int4_imma_group_kernel(const EstParams p) {
+  constexpr int kPagesHere = NW * 16;  // eight ring stages of two pages per warp
   static_assert(G >= 2 && G <= 8, "one n8 tile holds the group");
-  extern __shared__ __align__(128) uint8_t sm_ring[];  // kEstWarps * kRingDepth * kWarpStageBytes
-  __shared__ int sm_phys[kWarpPagesPerBlock + 1];
-  __shared__ int sm_ntok[kWarpPagesPerBlock + 1];
+  extern __shared__ __align__(128) uint8_t sm_ring[];  // NW * DEPTH * kWarpStageBytes
+  __shared__ int sm_phys[kPagesHere + 1];
+  __shared__ int sm_ntok[kPagesHere + 1];
 
   const int row = blockIdx.y;
   const int b = row / p.Hkv, kvh = row % p.Hkv;
@@ -1263,12 +1264,12 @@ estimate_int4_imma_group_kernel(const EstParams p) {
     n_pages = p.stride / kPage;
     if (threadIdx.x == 0 && blockIdx.x == 0) raise_flag(p.status, TWL_FLAG_BAD_INDEX);
   }
-  const int first = blockIdx.x * kWarpPagesPerBlock;
+  const int first = blockIdx.x * kPagesHere;
   if (first >= n_pages) return;
-  const int n_here = min(kWarpPagesPerBlock, n_pages - first);
+  const int n_here = min(kPagesHere, n_pages - first);
 
   const int tid = threadIdx.x;
-  if (tid <= kWarpPagesPerBlock) {  // one entry more than pages: the partner of an odd last page
+  if (tid <= kPagesHere) {  // one entry more than pages: the partner of an odd last page
     int phys = -1, ntok = 0;
     if (tid < n_here) {
       const int seq_page = first + tid;
@@ -1284,10 +1285,10 @@ estimate_int4_imma_group_kernel(const EstParams p) {
 
   const int lane = tid & 31, warp = tid >> 5;
   const int gq = lane >> 2, t = lane & 3;
-  uint8_t* const ring = sm_ring + (size_t)warp * kRingDepth * kWarpStageBytes;
+  uint8_t* const ring = sm_ring + (size_t)warp * DEPTH * kWarpStageBytes;
   const uint32_t ring_u32 = smem_u32(ring);
   const int n_pairs = (n_here + 1) >> 1;
-  const int my_pairs = (n_pairs > warp) ? (n_pairs - warp + kEstWarps - 1) / kEstWarps : 0;
+  const int my_pairs = (n_pairs > warp) ? (n_pairs - warp + NW - 1) / NW : 0;
 
   // the five 16-byte copies of a stage, as in the 16-bit tile kernel
   uint32_t src_off[5], dst_off[5];
@@ -1310,7 +1311,7 @@ estimate_int4_imma_group_kernel(const EstParams p) {
 
   auto issue = [&](int i, int slot) {
     if (i < my_pairs) {
-      const int pg0 = (warp + i * kEstWarps) * 2;
+      const int pg0 = (warp + i * NW) * 2;
       const uint32_t dst0 = ring_u32 + slot * kWarpStageBytes;
       const uint8_t* const s0 = k4_head + (size_t)max(sm_phys[pg0], 0) * page_stride;
       const uint8_t* const s1 = k4_head + (size_t)max(sm_phys[pg0 + 1], 0) * page_stride;
@@ -1325,7 +1326,7 @@ estimate_int4_imma_group_kernel(const EstParams p) {
   };
 
 #pragma unroll
-  for (int i = 0; i < kRingDepth - 1; ++i) issue(i, i);
+  for (int i = 0; i < DEPTH - 1; ++i) issue(i, i);
 
   // B fragments of head gq (this lane's channels 8t..8t+7 of every group: even ones, then odd
   // ones; hi and lo bytes), and of heads 2t and 2t+1, whose scores this lane ends up owning, the
@@ -1388,11 +1389,11 @@ estimate_int4_imma_group_kernel(const EstParams p) {
   float* const out0 = p.scores + (size_t)(b * p.Hq + h + 2 * t) * p.stride + (size_t)first * kPage + gq;
   const bool own0 = 2 * t < G, own1 = 2 * t + 1 < G;
   const uint8_t* stage = ring;
-  int fill_slot = kRingDepth - 1;
+  int fill_slot = DEPTH - 1;
   constexpr int kMagicBits = 0x4B400000;   // 1.5 * 2^23 as a float
   constexpr float kMagic = 12582912.f;
   for (int i = 0; i < my_pairs; ++i) {
-    cp_async_wait<kRingDepth - 2>();  // pair i has landed (this thread's copies)
+    cp_async_wait<DEPTH - 2>();  // pair i has landed (this thread's copies)
     __syncwarp();                     // ... and every other lane's
     float res[2][4];
 #pragma unroll
@@ -1420,10 +1421,10 @@ estimate_int4_imma_group_kernel(const EstParams p) {
       res[mt][0] = r0; res[mt][1] = r1; res[mt][2] = r2; res[mt][3] = r3;
     }
     __syncwarp();      // all lanes are done reading the slot that the next issue overwrites
-    issue(i + kRingDepth - 1, fill_slot);
-    fill_slot = (fill_slot + 1 == kRingDepth) ? 0 : fill_slot + 1;
-    stage = (stage + kWarpStageBytes == ring + kRingDepth * kWarpStageBytes) ? ring : stage + kWarpStageBytes;
-    const int pg0 = (warp + i * kEstWarps) * 2;
+    issue(i + DEPTH - 1, fill_slot);
+    fill_slot = (fill_slot + 1 == DEPTH) ? 0 : fill_slot + 1;
+    stage = (stage + kWarpStageBytes == ring + DEPTH * kWarpStageBytes) ? ring : stage + kWarpStageBytes;
+    const int pg0 = (warp + i * NW) * 2;
     if (pg0 + 1 < n_here && sm_ntok[pg0] == kPage && sm_ntok[pg0 + 1] == kPage) {
       // two whole pages (all but the last stage of a sequence): nothing to mask
       if (own0) {
@@ -1724,6 +1725,16 @@ estimate_int4_imma_digits_kernel(const EstParams p) {
 }
 
 template <typename T, int G, int NW, int DEPTH, int NBLK>
+static int launch_two_tiles(const EstParams& p, int rows, int max_row_pages, cudaStream_t st) {
+  constexpr int kBytes = NW * DEPTH * kWarpStageBytes;
+  auto kern = estimate_int4_imma_group_kernel<T, G, NW, DEPTH, NBLK>;
+  TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+  dim3 grid((max_row_pages + NW * 16 - 1) / (NW * 16), rows);
+  TWL_CUDA_TRY(launch_chain(kern, grid, dim3(NW * 32), kBytes, st, p));
+  return TWL_OK;
+}
+
+template <typename T, int G, int NW, int DEPTH, int NBLK>
 static int launch_digits(const EstParams& p, int rows, int max_row_pages, cudaStream_t st) {
   constexpr int kBytes = NW * DEPTH * kWarpStageBytes;
   auto kern = estimate_int4_imma_digits_kernel<T, G, NW, DEPTH, NBLK>;
@@ -1757,11 +1768,21 @@ static int launch_one(const EstParams& p, int rows, int max_row_pages, bool ldg,
     }
     if (rc != TWL_OK) return rc;
   } else if (G > 1 && VARIANT == VAR_DP4A && !p.force_ring && !p.simt_group && !p.f16_tiles) {
-    constexpr int kBytes = kEstWarps * kRingDepth * kWarpStageBytes;
-    auto kern = estimate_int4_imma_group_kernel<T, (G > 1 ? G : 2)>;
-    TWL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
-    dim3 grid((max_row_pages + kWarpPagesPerBlock - 1) / kWarpPagesPerBlock, rows);
-    TWL_CUDA_TRY(launch_chain(kern, grid, dim3(kEstThreads), kBytes, st, p));
+    // Block shape (warps x ring stages x blocks per SM), 64 sequences x 8 KV heads x 8 query heads, 856 MB of
+    // slabs: 8 x 5 x 2 (113 registers) 205 us; 8 x 3 x 3 and 4 x 3 x 6 (80 registers) 203 / 199; 4 x 4 x 5
+    // (96 registers, 20 warps per SM) 191.  Groups of 8 run the last one; the smaller groups, which reach this
+    // kernel only as a measurement variant, keep the shape their profile was taken with.
+    // TWL_EST_TILES_SHAPE = 1..4 picks a shape, for measurement.
+    constexpr int GG = G > 1 ? G : 2;
+    static const int shape = [] { const char* e = getenv("TWL_EST_TILES_SHAPE"); return e ? atoi(e) : 0; }();
+    int rc = TWL_OK;
+    switch (shape != 0 ? shape : (GG == 8 ? 3 : 4)) {
+      case 1: rc = launch_two_tiles<T, GG, 8, 3, 3>(p, rows, max_row_pages, st); break;
+      case 2: rc = launch_two_tiles<T, GG, 4, 3, 6>(p, rows, max_row_pages, st); break;
+      case 3: rc = launch_two_tiles<T, GG, 4, 4, 5>(p, rows, max_row_pages, st); break;
+      default: rc = launch_two_tiles<T, GG, 8, 5, 2>(p, rows, max_row_pages, st); break;
+    }
+    if (rc != TWL_OK) return rc;
   } else if (G > 1 && VARIANT == VAR_DP4A && !p.force_ring && !p.simt_group) {
     constexpr int kBytes = kEstWarps * kRingDepth * kWarpStageBytes;
     auto kern = estimate_int4_mma_group_kernel<T, (G > 1 ? G : 2)>;
