@@ -187,7 +187,9 @@ TWL_API int twl_threshold_prune(const float* scores, int32_t score_stride, const
  * heads per KV head, a (sequence, KV head) row whose heads keep, together, at least as many tokens
  * as the sequence has is served by a second kernel that reads every K/V page once for the whole
  * group and computes all its heads on tensor cores (softmax weights rounded to the model dtype
- * before P.V, as attention.py:302-304 does); the choice is made per row on the device.
+ * before P.V, as attention.py:302-304 does); the choice is made per row on the device.  That kernel
+ * reads the index lists in 16-byte pieces: it is used only when `indices` is 16-byte aligned and
+ * index_stride is a multiple of 4 (otherwise every row goes to the per-head kernel).
  * Limit: batch*num_q_heads <= 65536 (TWL_ERR_TOO_LARGE above).
  * workspace: twl_sparse_attn_workspace_bytes(...) bytes, 16-byte aligned; its first
  * batch*num_q_heads int32 words are arrival counters that must be zero on entry and are

@@ -882,6 +882,17 @@ def test_group_attention_of_dense_heads(hq, hkv, dt):
     assert torch.isfinite(out.float()).all()
     assert float(err.max()) <= ATOL_MAX and float(err.mean()) <= ATOL_MEAN
     assert (out[budget == 0].float() == 0).all()         # rows without kept tokens give zeros
+    # index lists that do not start on a 16-byte boundary: the group kernel (which reads them in 16-byte
+    # pieces) must not be chosen; the per-head kernel serves every row and gives the same result as it
+    # gives on the expanded cache
+    flat = torch.zeros(indices.numel() + 4, dtype=torch.int32, device=DEV)
+    shifted = flat[1: 1 + indices.numel()].view_as(indices)
+    shifted.copy_(indices)
+    assert shifted.data_ptr() % 16 != 0
+    out_shifted = ops.sparse_decode_attn(q, cache.k_pages, cache.v_pages, cache.kv_indptr, cache.kv_indices, shifted,
+                                         budget, chunk=256, status=status)
+    assert int(status.item()) == 0
+    assert torch.equal(out_shifted, per_head)
     errs = []
     for (b, h) in [(1, 0), (3, hq - 1), (4, 1), (5, g - 1), (5, hq - 1), (2, 0)]:
         kd, vd = cache.dense_kv(b, h // g)
