@@ -292,19 +292,28 @@ quest_page_scores_kernel(const ScoreParams p) {
 // NW warps per block, PPB pages per block: a warp should stream many steps per block it belongs
 // to, because a block's set-up (page table look-ups, a barrier) moves no metadata.
 // PIPE: two steps of loads in flight per warp instead of one (193 registers instead of 120).
-template <typename T, int G, int NW, int PPB, bool PIPE>
+// HPB: KV heads per block.  With HPB > 1 the block's warps take HPB neighbouring KV heads of the same
+// pages (warp w: head w % HPB), so the HPB slabs of a page record - HPB * 512 contiguous bytes - are
+// fetched by one SM at about the same time.  Scattered 512-byte reads over a metadata array of a
+// gigabyte or more are bound by address translation, not by DRAM (128 sequences x 4096 shuffled pages x
+// 4 KV heads, 1.07 GB: 344 us against 170 us with consecutive physical pages, while the same bytes
+// as four launches over 268 MB arrays take 4 x 50 us); sharing a page record among the warps of a
+// block divides the translations per byte by HPB.
+template <typename T, int G, int NW, int PPB, bool PIPE, int HPB = 1>
 __global__ void __launch_bounds__(NW * 32, (PIPE ? 256 : 512) / (NW * 32))
 quest_page_scores_mma_kernel(const ScoreParams p) {
   static_assert(G == 4 || G == 8, "one n8 tile holds the group");
+  static_assert(NW % HPB == 0, "whole warps per KV head");
   constexpr int kThreads = NW * 32;
-  const int row = blockIdx.x;  // (b, kv head), kv head fastest
-  const int b = row / p.Hkv, kvh = row % p.Hkv;
+  const int row = blockIdx.x;  // (b, group of HPB kv heads), kv heads fastest
+  const int b = row / (p.Hkv / HPB);
+  const int kvh = (row % (p.Hkv / HPB)) * HPB + (int)(threadIdx.x >> 5) % HPB;
   pdl_wait();  // q and the page table may come from the kernel launched just before
   const int page_base = p.indptr[b];
   const int n_pages = min(p.indptr[b + 1] - page_base, p.max_pages);
   const int first = blockIdx.y * PPB;
   if (first >= n_pages) return;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) / HPB;  // this head's warps: 0 .. NW / HPB - 1
   const int g = lane >> 2, t = lane & 3;
   const int h0 = kvh * G;
 
@@ -384,7 +393,7 @@ quest_page_scores_mma_kernel(const ScoreParams p) {
       }
     }
   };
-  constexpr int kStride = NW * 16;
+  constexpr int kStride = (NW / HPB) * 16;
   if constexpr (PIPE) {
     // two register sets: the loads of the next step are in flight while this one is multiplied
     Step s0, s1;
@@ -578,12 +587,12 @@ static int launch_scores(const ScoreParams& p, cudaStream_t st) {
   return TWL_OK;
 }
 
-template <typename T, int G, int NW, int PPB, bool PIPE>
+template <typename T, int G, int NW, int PPB, bool PIPE, int HPB = 1>
 static int launch_scores_mma_shape(const ScoreParams& p, cudaStream_t st) {
-  const int rows = p.B * p.Hkv;
+  const int rows = p.B * (p.Hkv / HPB);
   const int chunks = (p.max_pages + PPB - 1) / PPB;
   if (chunks > 65535) return TWL_ERR_TOO_LARGE;
-  TWL_CUDA_TRY(launch_chain(quest_page_scores_mma_kernel<T, G, NW, PPB, PIPE>, dim3(rows, chunks), dim3(NW * 32), 0, st, p));
+  TWL_CUDA_TRY(launch_chain(quest_page_scores_mma_kernel<T, G, NW, PPB, PIPE, HPB>, dim3(rows, chunks), dim3(NW * 32), 0, st, p));
   TWL_CHECK_LAUNCH();
   return TWL_OK;
 }
@@ -601,7 +610,8 @@ static int launch_scores_mma(const ScoreParams& p, cudaStream_t st) {
   // (58.9 us with runs of 128 pages, 59.9 us with 256).  Pages per block: 256 while that still
   // fills the GPU once, else 128 so that small problems spread out.
   // TWL_SCORES_MMA_SHAPE (for measurement): 1 = 8 warps x 256 pages, 5 = 2 x 512, 6 = 4 x 512, all
-  // with one step in flight; 7 = 2 x 512 with two steps in flight.
+  // with one step in flight; 7 = 2 x 512 with two steps in flight; 8 = one KV head per block even when
+  // the GPU holds several.
   static const int forced = [] {
     const char* e = getenv("TWL_SCORES_MMA_SHAPE");
     return e ? atoi(e) : 0;
@@ -610,6 +620,12 @@ static int launch_scores_mma(const ScoreParams& p, cudaStream_t st) {
   if (forced == 5) return launch_scores_mma_shape<T, G, 2, 512, false>(p, st);
   if (forced == 6) return launch_scores_mma_shape<T, G, 4, 512, false>(p, st);
   if (forced == 7) return launch_scores_mma_shape<T, G, 2, 512, true>(p, st);
+  // Several KV heads per GPU: the warps of a block take neighbouring heads of the same 128 pages (the same
+  // 8 steps per warp as two warps sharing 256 pages).  TWL_SCORES_MMA_SHAPE=8 keeps one head per block.
+  if (forced != 8) {
+    if (p.Hkv % 4 == 0) return launch_scores_mma_shape<T, G, 4, 128, false, 4>(p, st);
+    if (p.Hkv % 2 == 0) return launch_scores_mma_shape<T, G, 2, 128, false, 2>(p, st);
+  }
   const long rows = (long)p.B * p.Hkv, one_wave = 8L * num_sms();
   if (rows * ((p.max_pages + 255) / 256) >= one_wave) return launch_scores_mma_shape<T, G, 2, 256, false>(p, st);
   return launch_scores_mma_shape<T, G, 2, 128, false>(p, st);
