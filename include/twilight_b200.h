@@ -260,6 +260,10 @@ TWL_API int twl_sparse_decode_attn_static(const void* q, int dtype, const void* 
  * TWL_PRUNER_THRESHOLD with pruner_value = the threshold, TWL_PRUNER_NONE) and the sparse
  * attention, as three launches (five with Quest; one more where 2, 4 or 8 query heads share a KV head:
  * the group attention kernel runs before the per-head one) on `stream`.
+ * TWL_PRUNER_NONE keeps every candidate whose estimated probability is not zero in fp32 (the
+ * reference's mask keeps all candidates, state.py:151-159 counts them all in the budget; the ones
+ * dropped here weigh nothing in the attention, so the output is the same, but `budget` can be
+ * smaller than the candidate count on rows with logit gaps beyond 87).
  * flags: TWL_STEP_ESTIMATED_WEIGHTS = attend with the estimated weights (attention.py:295-296);
  *        TWL_STEP_ROUND_TO_DTYPE = round the Quest page scores and the estimated logits to the model
  *        dtype where the reference's matmuls return that dtype (quest.py:76-84; attention.py:252-254,
