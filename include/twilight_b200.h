@@ -139,7 +139,7 @@ TWL_API int twl_quest_select(const void* q, int dtype, const void* kmeta, const 
  * split into a high and a low byte (the integer dot product is exact; q is rounded to 2^-13 of the
  * head's largest element, as in the single-head kernel).  Groups of 2 and 4 heads put both bytes of
  * every head into the eight columns of ONE m16n8k32 tile per page and 32-channel quantisation
- * group; groups of 8 heads use one tile for the high and one for the low bytes (add 512 to use
+ * group (and round q to 2^-15 of the head's largest element: each byte's sum has an accumulator of its own); groups of 8 heads use one tile for the high and one for the low bytes (add 512 to use
  * that form for the smaller groups too).  The non-default variants exist for measurement. */
 TWL_API int twl_estimate_int4(const void* q, int dtype, const uint8_t* k4_pages,
                       const int32_t* kv_indptr, const int32_t* kv_indices,

@@ -1464,8 +1464,8 @@ estimate_int4_imma_group_kernel(const EstParams p) {
 // ---- groups of up to four query heads: both digits of q in one integer tile --------------------
 // With G <= 4 the eight columns of a m16n8k32 tile hold the hi digits of the G heads (columns 0..3)
 // and their lo digits (columns 4..7): q_d ~= (256*hi_d + lo_d) * 2^-e with lo in [-128, 127] and
-// |hi| <= 32, both signed bytes, so one tile per (page, group) does what the kernel above needs two
-// for.  Lanes t = 0, 1 of a quad then own hi-digit columns and lanes t = 2, 3 the lo-digit columns
+// |hi| <= 127, both signed bytes (q rounded to 15 bits), so one tile per (page, group) does what
+// the kernel above needs two for.  Lanes t = 0, 1 of a quad then own hi-digit columns and lanes t = 2, 3 the lo-digit columns
 // of the same heads; each lane sums scale * dot over the page's four groups for its own columns,
 // and the two digits meet once per page (one exchange across the quad) instead of once per group:
 // the lane with the hi digits finishes token g, its partner token g + 8, and each stores its own.
@@ -1595,8 +1595,12 @@ estimate_int4_imma_digits_kernel(const EstParams p) {
     }
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));  // over the head's 128 channels
-    int e = (amax > 0.f && amax < INFINITY) ? (12 - ilogbf(amax)) : 0;  // amax * 2^e in [2^12, 2^13)
+    // 15 bits where the kernel above has 13: each digit has a tile column of its own here, so both digit
+    // sums stay below 2^16 whatever the digits.  amax * 2^e in [2^14, 2^15), one bit less when the hi
+    // digit of the largest element would not fit a signed byte (256 * 127 + 127 = 32639).
+    int e = (amax > 0.f && amax < INFINITY) ? (14 - ilogbf(amax)) : 0;
     e = max(-100, min(100, e));
+    if (amax * ldexpf(1.f, e) > 32639.f) e -= 1;
     const float up = ldexpf(1.f, e);
     const float undo = p.sm_scale * ldexpf(1.f, -e);
     const float os_a = __shfl_sync(0xffffffffu, undo, (2 * (t & 1)) * 4);      // head 2(t&1)
@@ -1627,9 +1631,9 @@ estimate_int4_imma_digits_kernel(const EstParams p) {
       gsum[grp] = sum;
     }
     const int mine = t == 0 ? gsum[0] : t == 1 ? gsum[1] : t == 2 ? gsum[2] : gsum[3];
-    const float sf = (float)mine * (1.f / 256.f);      // |sum| < 2^18: exact
+    const float sf = (float)mine * (1.f / 256.f);      // |sum| < 2^20: exact
     const __half s_hi = __float2half_rn(sf);
-    const __half s_lo = __float2half_rn(sf - __half2float(s_hi));  // a multiple of 2^-8 below 2^-1: exact
+    const __half s_lo = __float2half_rn(sf - __half2float(s_hi));  // a multiple of 2^-8, at most 1: exact
     const __half2 pair = __halves2half2(s_hi, s_lo);
     bmin = (gq < G) ? *reinterpret_cast<const uint32_t*>(&pair) : 0u;
   }
