@@ -952,24 +952,36 @@ group_decode_attn_kernel(const AttParams p) {
   __syncthreads();
   if (tid < G) sm_ticket[tid] = atomicAdd(&p.counters[row0 + tid], 1);
   __syncthreads();
-  for (int hh = 0; hh < G; ++hh) {
-    if (sm_ticket[hh] != n_chunks - 1) continue;  // the same for the whole block
+  // a warp per head (the heads' tickets agree for the whole block): lane c holds chunk c's (max, sum), the
+  // weights go round by shuffles, every lane sums four channels over the chunks (kMaxChunksPerRow <= 32)
+  static_assert(kMaxChunksPerRow <= 32, "one lane per chunk");
+  for (int hh = warp; hh < G; hh += kGrpWarps) {
+    if (sm_ticket[hh] != n_chunks - 1) continue;
     __threadfence();
     const int row = row0 + hh;
-    float gm = kNegBig;
-    for (int cc = 0; cc < n_chunks; ++cc)
-      gm = fmaxf(gm, __ldcg(&p.part_ml[((size_t)row * kMaxChunksPerRow + cc) * 2]));
-    for (int d = tid; d < kD; d += kGrpThreads) {
-      float gl = 0.f, go = 0.f;
-      for (int cc = 0; cc < n_chunks; ++cc) {
-        const size_t s2 = (size_t)row * kMaxChunksPerRow + cc;
-        const float f = __expf(__ldcg(&p.part_ml[s2 * 2]) - gm);
-        gl += f * __ldcg(&p.part_ml[s2 * 2 + 1]);
-        go += f * __ldcg(&p.part_o[s2 * kD + d]);
-      }
-      reinterpret_cast<T*>(p.out)[(size_t)row * kD + d] = Elem<T>::from_f(gl > 0.f ? go / gl : 0.f);
+    const size_t s_base = (size_t)row * kMaxChunksPerRow;
+    float m_c = kNegBig, l_c = 0.f;
+    if (lane < n_chunks) {
+      m_c = __ldcg(&p.part_ml[(s_base + lane) * 2]);
+      l_c = __ldcg(&p.part_ml[(s_base + lane) * 2 + 1]);
     }
-    if (tid == 0) p.counters[row] = 0;  // leave the workspace ready for the next call
+    const float gm = warp_max(m_c);
+    const float f_c = lane < n_chunks ? __expf(m_c - gm) : 0.f;
+    const float gl = warp_sum(f_c * l_c);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4* po = reinterpret_cast<const float4*>(p.part_o + s_base * kD) + lane;
+    for (int cc = 0; cc < n_chunks; ++cc) {
+      const float f = __shfl_sync(0xffffffffu, f_c, cc);
+      const float4 v = __ldcg(po + (size_t)cc * (kD / 4));
+      acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
+    }
+    const float inv = gl > 0.f ? 1.f / gl : 0.f;
+    T* const o = reinterpret_cast<T*>(p.out) + (size_t)row * kD + lane * 4;
+    o[0] = Elem<T>::from_f(acc.x * inv);
+    o[1] = Elem<T>::from_f(acc.y * inv);
+    o[2] = Elem<T>::from_f(acc.z * inv);
+    o[3] = Elem<T>::from_f(acc.w * inv);
+    if (lane == 0) p.counters[row] = 0;  // leave the workspace ready for the next call
   }
 }
 
